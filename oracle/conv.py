@@ -1,0 +1,68 @@
+"""Depthwise causal convolution and KV-cache scatter on the CPU - checkers.
+
+TEST INFRASTRUCTURE: see the package docstring.
+
+y_t[c] = sum_{j=0}^{K-1} w[c, j] * x_{t-(K-1)+j}[c], zero (or carried-state) left
+context, no bias (model/reference.py:43-47; model/blocks.py:501,526-528).  The
+recurrent state is the last K-1 inputs, oldest first
+(inference/models/atma.py:137,186; kernel/causal_conv1d_triton.py:36-41).
+"""
+
+import torch
+
+
+def causal_conv1d_prefill(x, weight, state_in=None):
+    """x (T, C); weight (C, K); state_in (C, K-1) or None (fresh prompt).
+    Returns out (T, C) fp32 and the final state (C, K-1) in x.dtype
+    (inference/models/atma.py:128-137)."""
+    T, C = x.shape
+    K = weight.shape[1]
+    left = x.new_zeros(K - 1, C) if state_in is None else state_in.to(x.dtype).transpose(0, 1)
+    padded = torch.cat([left, x], dim=0)                                        # (T+K-1, C)
+    out = torch.zeros(T, C, dtype=torch.float32)
+    wf = weight.float()
+    for j in range(K):
+        out += padded[j:j + T].float() * wf[:, j][None, :]
+    return out, padded[-(K - 1):].transpose(0, 1).contiguous()
+
+
+def causal_conv1d_step(x, weight, slots, state_table):
+    """One decode step, in place on state_table[slots]
+    (kernel/causal_conv1d_triton.py:17-42; inference/models/atma.py:181-187).
+    x (B, C); weight (C, K); state_table (max_seqs, C, K-1) - MUTATED.  Returns fp32."""
+    K = weight.shape[1]
+    st = state_table[slots.long()]                                              # (B, C, K-1)
+    out = (st.float() * weight.float()[None, :, :K - 1]).sum(-1) + x.float() * weight.float()[None, :, K - 1]
+    state_table[slots.long()] = torch.cat([st[:, :, 1:], x.to(st.dtype)[:, :, None]], dim=2)
+    return out
+
+
+def packed_causal_conv1d_oracle(x, weight, state_table, token_seq_starts, token_seq_ends,
+                                token_seq_slots):
+    """Fresh-prompt conv over packed ragged sequences plus the final-state write
+    (kernel/inference_ops_triton.py:17-63).  x (tokens, C); the three maps are
+    per-token int32.  state_table (max_seqs, C, K-1) - MUTATED.  Returns fp32."""
+    total = x.shape[0]
+    out = torch.zeros(total, x.shape[1], dtype=torch.float32)
+    seen = set()
+    for t in range(total):
+        s, e, slot = int(token_seq_starts[t]), int(token_seq_ends[t]), int(token_seq_slots[t])
+        if (s, e) in seen:
+            continue
+        seen.add((s, e))
+        o, st = causal_conv1d_prefill(x[s:e], weight, None)
+        out[s:e] = o
+        state_table[slot] = st.to(state_table.dtype)
+    return out
+
+
+def store_kvcache_oracle(key, value, k_cache, v_cache, slot_mapping):
+    """Scatter rows into flat cache slots, skipping slot -1
+    (inference/layers/attention.py:39-47).  Caches are MUTATED."""
+    N, h, d = key.shape
+    kf, vf = k_cache.view(-1, h, d), v_cache.view(-1, h, d)
+    for i in range(N):
+        s = int(slot_mapping[i])
+        if s >= 0:
+            kf[s] = key[i]
+            vf[s] = value[i]
