@@ -1,0 +1,23 @@
+"""atma_b200: hand-written sm_100a kernels for ATMA's global-mixing hot path.
+
+Polar Attention prefill / paged decode, the gated-delta memory chunked scan and decode
+step, the depthwise causal convolutions and the small decode fusions, behind the call
+signatures of the reference's kernel modules.  Host code is Python/PyTorch (device memory,
+streams, torch.distributed); all device work goes through the C ABI of libatma_b200.so.
+There is no CPU or PyTorch fallback: a missing library raises on first use.
+"""
+
+from .polar import (polar_attention_fwd, polar_attention_packed_fwd, polar_attention_decode,
+                    polar_prefill_raw)
+from .gated_delta import gated_delta_decode_step, chunk_gated_delta_rule
+from .causal_conv1d import causal_conv1d_decode_step, causal_conv1d_fn
+from .inference_ops import squared_relu_gate, packed_causal_conv1d, softcap_logits, linear_head_rms
+from .kvcache import store_kvcache
+
+__all__ = [
+    "polar_attention_fwd", "polar_attention_packed_fwd", "polar_attention_decode", "polar_prefill_raw",
+    "gated_delta_decode_step", "chunk_gated_delta_rule",
+    "causal_conv1d_decode_step", "causal_conv1d_fn",
+    "squared_relu_gate", "packed_causal_conv1d", "softcap_logits", "linear_head_rms",
+    "store_kvcache",
+]

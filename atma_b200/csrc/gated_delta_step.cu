@@ -1,0 +1,162 @@
+// Gated-delta decode step: one token per sequence, state [dk][dv] fp32 read and written
+// once, in place, through a slot table.
+//
+//   Sd = gamma * S;  pred_v = sum_k kn_k Sd[k,v];  u_v = beta (v_v - pred_v)
+//   S' = Sd + kn u^T (stored);  r_v = sum_k qn_k S'[k,v]
+//
+// One CTA owns a [dk] x [32] column slice of one (sequence, head) state, held entirely in
+// registers between the read and the write: 8 lanes x float4 span the 32 columns, the
+// other 4 lane groups x NWARPS warps stride the dk rows, so every warp-level access is
+// four full 128-byte rows.  HBM traffic is exactly one read and one write of the state.
+#include "common.cuh"
+
+namespace atma {
+
+constexpr int kStepCols = 32;     // state columns per CTA
+constexpr int kStepWarps = 4;
+constexpr int kStepMaxRowsPerThread = 16;   // dk <= 16 * 4 * kStepWarps = 256
+
+template <typename T>
+__global__ void __launch_bounds__(kStepWarps * 32)
+gated_delta_step_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
+                        int64_t q_sb, int64_t q_sh, int64_t k_sb, int64_t k_sh, int64_t v_sb,
+                        int64_t v_sh, const float* __restrict__ gamma,
+                        const float* __restrict__ beta, float* __restrict__ state, int64_t state_ss,
+                        int64_t state_sh, const int64_t* __restrict__ slots, float* __restrict__ r,
+                        int H, int dk, int dv, float eps) {
+  const int bh = blockIdx.x;
+  const int b = bh / H, h = bh % H;
+  const int col0 = blockIdx.y * kStepCols;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int cg = lane & 7;          // float4 column group inside the slice
+  const int rg = (lane >> 3) + 4 * warp;   // row group: rows rg, rg + 4*NW, ...
+  constexpr int RSTRIDE = 4 * kStepWarps;
+
+  __shared__ float s_q[256], s_k[256];
+  __shared__ float s_red[kStepWarps][kStepCols];
+  __shared__ float s_norm[2];
+
+  const int64_t slot = slots[b];
+  const int col = col0 + cg * 4;
+  const bool col_ok = col < dv;     // dv % 4 == 0 is required by the host wrapper
+  if (slot < 0) {                   // padded batch row: no state, defined output
+    if (tid < kStepCols && col0 + tid < dv) r[((int64_t)b * H + h) * dv + col0 + tid] = 0.f;
+    return;
+  }
+
+  // q, k -> shared, with their L2 norms (F.normalize: x / max(||x||, eps))
+  float qs = 0.f, ks = 0.f;
+  for (int i = tid; i < dk; i += blockDim.x) {
+    float qv = to_f32(q[b * q_sb + h * q_sh + i]);
+    float kv = to_f32(k[b * k_sb + h * k_sh + i]);
+    s_q[i] = qv; s_k[i] = kv;
+    qs += qv * qv; ks += kv * kv;
+  }
+  qs = warp_sum(qs); ks = warp_sum(ks);
+  if (lane == 0) { s_red[warp][0] = qs; s_red[warp][1] = ks; }
+  __syncthreads();
+  if (tid == 0) {
+    float a = 0.f, c = 0.f;
+    for (int w = 0; w < kStepWarps; ++w) { a += s_red[w][0]; c += s_red[w][1]; }
+    s_norm[0] = 1.f / fmaxf(sqrtf(a), eps);
+    s_norm[1] = 1.f / fmaxf(sqrtf(c), eps);
+  }
+  __syncthreads();
+  const float qinv = s_norm[0], kinv = s_norm[1];
+  const float gm = gamma[b * H + h], bt = beta[b * H + h];
+
+  float* sp = state + slot * state_ss + h * state_sh;
+  float4 S[kStepMaxRowsPerThread];
+  float4 pred = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int i = 0; i < kStepMaxRowsPerThread; ++i) {
+    const int row = rg + i * RSTRIDE;
+    if (row < dk && col_ok) {
+      float4 s = *reinterpret_cast<const float4*>(sp + (int64_t)row * dv + col);
+      s.x *= gm; s.y *= gm; s.z *= gm; s.w *= gm;
+      const float kn = s_k[row] * kinv;
+      pred.x = fmaf(kn, s.x, pred.x); pred.y = fmaf(kn, s.y, pred.y);
+      pred.z = fmaf(kn, s.z, pred.z); pred.w = fmaf(kn, s.w, pred.w);
+      S[i] = s;
+    } else {
+      S[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
+  // reduce pred over the 4 row groups of the warp (lane bits 3,4), then over warps
+#pragma unroll
+  for (int o = 8; o <= 16; o <<= 1) {
+    pred.x += __shfl_xor_sync(0xffffffffu, pred.x, o); pred.y += __shfl_xor_sync(0xffffffffu, pred.y, o);
+    pred.z += __shfl_xor_sync(0xffffffffu, pred.z, o); pred.w += __shfl_xor_sync(0xffffffffu, pred.w, o);
+  }
+  __syncthreads();                  // s_red reuse
+  if (lane < 8) *reinterpret_cast<float4*>(&s_red[warp][cg * 4]) = pred;
+  __syncthreads();
+  float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (col_ok) {
+    float4 p = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int w = 0; w < kStepWarps; ++w) {
+      float4 t = *reinterpret_cast<const float4*>(&s_red[w][cg * 4]);
+      p.x += t.x; p.y += t.y; p.z += t.z; p.w += t.w;
+    }
+    const T* vp = v + b * v_sb + h * v_sh + col;
+    u.x = bt * (to_f32(vp[0]) - p.x); u.y = bt * (to_f32(vp[1]) - p.y);
+    u.z = bt * (to_f32(vp[2]) - p.z); u.w = bt * (to_f32(vp[3]) - p.w);
+  }
+  float4 rd = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int i = 0; i < kStepMaxRowsPerThread; ++i) {
+    const int row = rg + i * RSTRIDE;
+    if (row < dk && col_ok) {
+      const float kn = s_k[row] * kinv, qn = s_q[row] * qinv;
+      float4 s = S[i];
+      s.x = fmaf(kn, u.x, s.x); s.y = fmaf(kn, u.y, s.y); s.z = fmaf(kn, u.z, s.z); s.w = fmaf(kn, u.w, s.w);
+      *reinterpret_cast<float4*>(sp + (int64_t)row * dv + col) = s;
+      rd.x = fmaf(qn, s.x, rd.x); rd.y = fmaf(qn, s.y, rd.y); rd.z = fmaf(qn, s.z, rd.z); rd.w = fmaf(qn, s.w, rd.w);
+    }
+  }
+#pragma unroll
+  for (int o = 8; o <= 16; o <<= 1) {
+    rd.x += __shfl_xor_sync(0xffffffffu, rd.x, o); rd.y += __shfl_xor_sync(0xffffffffu, rd.y, o);
+    rd.z += __shfl_xor_sync(0xffffffffu, rd.z, o); rd.w += __shfl_xor_sync(0xffffffffu, rd.w, o);
+  }
+  __syncthreads();
+  if (lane < 8) *reinterpret_cast<float4*>(&s_red[warp][cg * 4]) = rd;
+  __syncthreads();
+  if (tid < 8 && col0 + tid * 4 < dv) {
+    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int w = 0; w < kStepWarps; ++w) {
+      float4 t = *reinterpret_cast<const float4*>(&s_red[w][tid * 4]);
+      o.x += t.x; o.y += t.y; o.z += t.z; o.w += t.w;
+    }
+    *reinterpret_cast<float4*>(r + ((int64_t)b * H + h) * dv + col0 + tid * 4) = o;
+  }
+}
+
+}  // namespace atma
+
+using namespace atma;
+
+extern "C" int atma_gated_delta_decode_step(const void* q, const void* k, const void* v,
+                                            int64_t q_sb, int64_t q_sh, int64_t k_sb, int64_t k_sh,
+                                            int64_t v_sb, int64_t v_sh, int dtype,
+                                            const float* gamma, const float* beta, float* state,
+                                            int64_t state_ss, int64_t state_sh,
+                                            const int64_t* slots, float* r, int B, int H, int dk,
+                                            int dv, float eps, void* stream) {
+  ATMA_REQUIRE(dtype_ok(dtype), "gated_delta_decode_step: unsupported dtype %d", dtype);
+  ATMA_REQUIRE(dk >= 1 && dk <= 256, "gated_delta_decode_step: dk=%d outside 1..256", dk);
+  ATMA_REQUIRE(dv >= 4 && dv % 4 == 0, "gated_delta_decode_step: dv=%d must be a multiple of 4", dv);
+  ATMA_REQUIRE(((uintptr_t)state % 16 == 0) && (state_ss % 4 == 0) && (state_sh % 4 == 0) &&
+                   ((uintptr_t)r % 16 == 0),
+               "gated_delta_decode_step: state / r must be 16-byte aligned");
+  if (B <= 0 || H <= 0) return ATMA_OK;
+  dim3 grid(B * H, (dv + kStepCols - 1) / kStepCols), block(kStepWarps * 32);
+  ATMA_DISPATCH_DTYPE(dtype, T, {
+    gated_delta_step_kernel<T><<<grid, block, 0, (cudaStream_t)stream>>>(
+        (const T*)q, (const T*)k, (const T*)v, q_sb, q_sh, k_sb, k_sh, v_sb, v_sh, gamma, beta,
+        state, state_ss, state_sh, slots, r, H, dk, dv, eps);
+  });
+  return launch_status("gated_delta_decode_step");
+}

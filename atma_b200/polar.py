@@ -1,0 +1,221 @@
+"""Polar Attention entry points with the reference's call signatures.
+
+Drop-in for the forward-only functions of the reference's ``kernel/polar_triton.py``:
+``polar_attention_fwd`` (:594-609), ``polar_attention_packed_fwd`` (:613-669) and
+``polar_attention_decode`` (:796-858).  Same argument names, meaning, return values and
+error behaviour; the work is done by hand-written sm_100a kernels behind the C ABI.
+
+One extension that is not a signature change: ``k`` and ``v`` may carry the un-expanded
+``Hkv`` KV heads (``Hkv`` dividing ``H``); the reference always expands them to ``H`` first
+(inference/models/atma.py:417-420), which quadruples K/V traffic.
+"""
+
+import math
+from ctypes import byref
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+
+HAS_TRITON = torch.cuda.is_available()     # the flag the reference's callers gate on
+HAS_CUDA_EXT = HAS_TRITON
+
+
+def _params(v_null, null_base, null_slope_raw, len_gain_raw, mag_beta_raw, device):
+    """softplus on the host, as kernel/polar_triton.py:540-544 does."""
+    return dict(
+        spg=F.softplus(len_gain_raw.detach().float()).contiguous().to(device),
+        sps=F.softplus(null_slope_raw.detach().float()).contiguous().to(device),
+        beta=F.softplus(mag_beta_raw.detach().float()).contiguous().to(device),
+        null_base=null_base.detach().float().contiguous().to(device),
+        v_null=v_null.detach().float().contiguous().to(device),
+    )
+
+
+def _inner_contiguous(t):
+    return t if t.stride(-1) == 1 else t.contiguous()
+
+
+def _fill_common(a, p, eps, window, dtype_code):
+    a.v_null, a.spg, a.null_base = _lib.ptr(p["v_null"]), _lib.ptr(p["spg"]), _lib.ptr(p["null_base"])
+    a.sps, a.beta = _lib.ptr(p["sps"]), _lib.ptr(p["beta"])
+    a.eps = float(eps)
+    a.window = 0 if window is None else int(window)
+    a.dtype = dtype_code
+
+
+def polar_prefill_raw(q, k, v, n_keys, params, *, eps=1e-6, window=None, key_offset=0,
+                      stats_in=None, finalize=True, n_base=None):
+    """Lower-level form used by ``polar_attention_fwd`` and by the ring (context-parallel)
+    prefill: q (B,H,Tq,dk) and k, v (B,Hkv,Tk,dk) as strided views with a contiguous last
+    dimension.  ``stats_in`` = (m, L, Q2, S) fp32 from earlier key blocks; with
+    ``finalize=False`` the updated statistics are returned instead of (c, mag)."""
+    _lib.require_cuda(q, "polar_attention_fwd")
+    lib = _lib.load()
+    B, H, Tq, dk = q.shape
+    Hkv, Tk = k.shape[1], k.shape[2]
+    q, k, v = _inner_contiguous(q), _inner_contiguous(k), _inner_contiguous(v)
+    a = _lib.PolarPrefillArgs()
+    a.q, a.k, a.v = _lib.ptr(q), _lib.ptr(k), _lib.ptr(v)
+    a.q_sb, a.q_sh, a.q_st = q.stride(0), q.stride(1), q.stride(2)
+    a.k_sb, a.k_sh, a.k_st = k.stride(0), k.stride(1), k.stride(2)
+    a.v_sb, a.v_sh, a.v_st = v.stride(0), v.stride(1), v.stride(2)
+    a.B, a.H, a.Hkv, a.Tq, a.Tk, a.dk = B, H, Hkv, Tq, Tk, dk
+    a.key_offset = int(key_offset)
+    if n_keys is not None:
+        n_keys = n_keys.to(device=q.device, dtype=torch.float32).contiguous()
+        a.n_keys = _lib.ptr(n_keys)
+    else:
+        a.n_keys, a.n_base = None, float(n_base)
+    _fill_common(a, params, eps, window, _lib.dtype_code(q))
+    keep = [q, k, v, n_keys, params]
+    if stats_in is not None:
+        m, L, Q2, S = (t.contiguous() for t in stats_in)
+        a.stats_in_m, a.stats_in_l, a.stats_in_q2, a.stats_in_s = map(_lib.ptr, (m, L, Q2, S))
+        keep += [m, L, Q2, S]
+    a.finalize = 1 if finalize else 0
+    a.n_tiles = 0
+    if finalize:
+        c = torch.empty((B, H, Tq, dk), device=q.device, dtype=q.dtype)
+        mag = torch.empty((B, H, Tq), device=q.device, dtype=q.dtype)
+        a.c, a.c_sb, a.c_sh, a.c_st = _lib.ptr(c), c.stride(0), c.stride(1), c.stride(2)
+        a.mag, a.mag_sb, a.mag_sh, a.mag_st = _lib.ptr(mag), mag.stride(0), mag.stride(1), mag.stride(2)
+        _lib.check(lib.atma_polar_prefill(byref(a), _lib.stream_ptr()))
+        return c, mag
+    om = torch.empty((B, H, Tq), device=q.device, dtype=torch.float32)
+    ol, oq2 = torch.empty_like(om), torch.empty_like(om)
+    os_ = torch.empty((B, H, Tq, dk), device=q.device, dtype=torch.float32)
+    a.stats_out_m, a.stats_out_l, a.stats_out_q2, a.stats_out_s = map(_lib.ptr, (om, ol, oq2, os_))
+    _lib.check(lib.atma_polar_prefill(byref(a), _lib.stream_ptr()))
+    return om, ol, oq2, os_
+
+
+@torch.no_grad()
+def polar_attention_fwd(q, k, v, n_keys, *, v_null, null_base, null_slope_raw,
+                        len_gain_raw, mag_beta_raw, eps=1e-6, is_causal=True,
+                        input_precision="ieee", window=None):
+    """Forward-only Polar attention.  q (B,H,Tq,dk); k, v (B,H or Hkv,Tk,dk); n_keys (Tq,)
+    valid-key count per query.  Returns (c (B,H,Tq,dk), mag (B,H,Tq)) in q's dtype.
+
+    ``is_causal`` only asserts the standard self-attention layout (Tq == Tk), as in the
+    reference; masking always comes from ``n_keys`` and key tiles no query can see are
+    skipped either way.  ``input_precision`` is accepted for signature parity: fp32 inputs
+    are always multiplied in full fp32."""
+    B, H, Tq, dk = q.shape
+    Tk = k.shape[2]
+    if is_causal and Tq != Tk:
+        raise ValueError(
+            f"is_causal=True requires Tq == Tk (standard causal self-attention); got "
+            f"Tq={Tq}, Tk={Tk}. Use is_causal=False with an explicit n_keys for "
+            f"decode / offset-prefill layouts.")
+    if dk & (dk - 1) != 0:
+        raise ValueError(f"head_dim (dk={dk}) must be a power of two.")
+    params = _params(v_null, null_base, null_slope_raw, len_gain_raw, mag_beta_raw, q.device)
+    return polar_prefill_raw(q, k, v, n_keys, params, eps=eps, window=window)
+
+
+@torch.no_grad()
+def polar_attention_packed_fwd(q, k, v, tile_seq_starts, tile_q_starts, tile_seq_lens, *,
+                               v_null, null_base, null_slope_raw, len_gain_raw, mag_beta_raw,
+                               eps=1e-6, input_precision="ieee", window=None):
+    """Fresh causal Polar attention over a packed ragged batch.  q (tokens,H,dk); k, v
+    (tokens,H or Hkv,dk); one tile-map entry per 128-row query tile.  Returns c like q and
+    mag (tokens,H)."""
+    if not q.is_cuda:
+        raise RuntimeError("packed Polar attention requires CUDA")
+    if q.ndim != 3 or k.ndim != 3 or k.shape != v.shape or k.shape[0] != q.shape[0] or k.shape[2] != q.shape[2]:
+        raise ValueError("q, k, and v must have [tokens, heads, dim] shapes with equal tokens and dim")
+    total, heads, dk = q.shape
+    if heads % k.shape[1] != 0:
+        raise ValueError("the number of query heads must be a multiple of the KV heads")
+    if q.dtype not in (torch.bfloat16, torch.float16):
+        raise ValueError("packed Polar route is enabled only for 16-bit inference")
+    if dk & (dk - 1):
+        raise ValueError(f"head_dim (dk={dk}) must be a power of two")
+    if not (tile_seq_starts.numel() == tile_q_starts.numel() == tile_seq_lens.numel()):
+        raise ValueError("packed Polar tile-map tensors must have equal lengths")
+    lib = _lib.load()
+    params = _params(v_null, null_base, null_slope_raw, len_gain_raw, mag_beta_raw, q.device)
+    q, k, v = _inner_contiguous(q), _inner_contiguous(k), _inner_contiguous(v)
+    maps = [t.to(device=q.device, dtype=torch.int32).contiguous()
+            for t in (tile_seq_starts, tile_q_starts, tile_seq_lens)]
+    c = torch.empty_like(q, memory_format=torch.contiguous_format)
+    mag = torch.empty((total, heads), device=q.device, dtype=q.dtype)
+    a = _lib.PolarPrefillArgs()
+    a.q, a.k, a.v = _lib.ptr(q), _lib.ptr(k), _lib.ptr(v)
+    a.q_sb, a.q_sh, a.q_st = 0, q.stride(1), q.stride(0)
+    a.k_sb, a.k_sh, a.k_st = 0, k.stride(1), k.stride(0)
+    a.v_sb, a.v_sh, a.v_st = 0, v.stride(1), v.stride(0)
+    a.c, a.c_sb, a.c_sh, a.c_st = _lib.ptr(c), 0, c.stride(1), c.stride(0)
+    a.mag, a.mag_sb, a.mag_sh, a.mag_st = _lib.ptr(mag), 0, mag.stride(1), mag.stride(0)
+    a.B, a.H, a.Hkv, a.Tq, a.Tk, a.dk = 1, heads, k.shape[1], total, total, dk
+    a.n_keys, a.n_base, a.key_offset, a.finalize = None, 0.0, 0, 1
+    a.tile_seq_start, a.tile_q_start, a.tile_seq_len = map(_lib.ptr, maps)
+    a.n_tiles = maps[0].numel()
+    _fill_common(a, params, eps, window, _lib.dtype_code(q))
+    if a.n_tiles:
+        _lib.check(lib.atma_polar_prefill(byref(a), _lib.stream_ptr()))
+    return c, mag
+
+
+def decode_num_splits(B, Hkv, max_context, sm_count=148):
+    """Key ranges per (sequence, KV head): enough CTAs for ~4 waves over the SMs, at least
+    512 keys per range.  Depends only on launch-time shapes (CUDA-graph safe)."""
+    want = max(1, (4 * sm_count + B * Hkv - 1) // (B * Hkv))
+    return int(max(1, min(want, max(1, max_context // 512), 64)))
+
+
+_scratch_cache = {}
+
+
+def _decode_scratch(device, nfloats):
+    """Per-device scratch for the split partials, grown on demand and reused across calls
+    (stable address once warm, which is what CUDA-graph replay needs)."""
+    key = (device.type, device.index)
+    buf = _scratch_cache.get(key)
+    if buf is None or buf.numel() < nfloats:
+        buf = torch.empty(int(nfloats), device=device, dtype=torch.float32)
+        _scratch_cache[key] = buf
+    return buf
+
+
+@torch.no_grad()
+def polar_attention_decode(q, k_cache, v_cache, block_tables, context_lens, *,
+                           v_null, null_base, null_slope_raw, len_gain_raw, mag_beta_raw,
+                           eps=1e-6, block_n=None, num_warps=None, num_stages=None, window=None,
+                           num_splits=None):
+    """Paged Polar decode.  q (B,H,dk); caches (num_blocks, block_size, Hkv, dk) contiguous;
+    block_tables (B,max_blocks) int32; context_lens (B,) int32 including the current token.
+    Returns c (B,H,dk), mag (B,H) in q's dtype.  ``block_n``, ``num_warps``, ``num_stages``
+    are the reference's Triton launch knobs, accepted and ignored."""
+    _lib.require_cuda(q, "polar_attention_decode")
+    lib = _lib.load()
+    B, H, dk = q.shape
+    num_blocks, block_size, Hkv, _ = k_cache.shape
+    if not (k_cache.is_contiguous() and v_cache.is_contiguous()):
+        raise ValueError("k_cache and v_cache must be contiguous")
+    if k_cache.dtype != q.dtype or v_cache.dtype != q.dtype:
+        raise ValueError("q and the KV cache must share a dtype")
+    max_blocks = block_tables.shape[1]
+    q = q.contiguous()
+    if block_tables.dtype != torch.int32 or block_tables.stride(1) != 1:
+        block_tables = block_tables.to(torch.int32).contiguous()
+    if context_lens.dtype != torch.int32 or not context_lens.is_contiguous():
+        context_lens = context_lens.to(torch.int32).contiguous()
+    params = _params(v_null, null_base, null_slope_raw, len_gain_raw, mag_beta_raw, q.device)
+    n_splits = num_splits or decode_num_splits(B, Hkv, max_blocks * block_size)
+    scratch = _decode_scratch(q.device, lib.atma_polar_decode_scratch_floats(B, H, dk, n_splits))
+    c = torch.empty((B, H, dk), device=q.device, dtype=q.dtype)
+    mag = torch.empty((B, H), device=q.device, dtype=q.dtype)
+    a = _lib.PolarDecodeArgs()
+    a.q, a.k_cache, a.v_cache = _lib.ptr(q), _lib.ptr(k_cache), _lib.ptr(v_cache)
+    a.block_tables, a.bt_stride, a.context_lens = _lib.ptr(block_tables), block_tables.stride(0), _lib.ptr(context_lens)
+    a.v_null, a.spg, a.null_base = _lib.ptr(params["v_null"]), _lib.ptr(params["spg"]), _lib.ptr(params["null_base"])
+    a.sps, a.beta = _lib.ptr(params["sps"]), _lib.ptr(params["beta"])
+    a.c, a.mag, a.scratch = _lib.ptr(c), _lib.ptr(mag), _lib.ptr(scratch)
+    a.B, a.H, a.Hkv, a.dk, a.block_size = B, H, Hkv, dk, block_size
+    a.max_blocks, a.num_blocks, a.n_splits = max_blocks, num_blocks, n_splits
+    a.dtype, a.window, a.eps = _lib.dtype_code(q), (0 if window is None else int(window)), float(eps)
+    _lib.check(lib.atma_polar_decode(byref(a), _lib.stream_ptr()))
+    return c, mag

@@ -1,0 +1,394 @@
+"""Benchmark of ATMA's global-layer mixing hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Metric (BASELINE.json): global-layer prefill tok/s at a 64K-token context, with decode tok/s
+at batch 64 x 32K context reported beside it, each against its roofline.
+
+A "step" is one pass of one global layer's mixing over one 65,536-token sequence:
+Polar prefill (H=8, Hkv=2, dk=128, bf16, full causal context) followed by the gated-delta
+chunked scan (H=8, d=128, chunk 64, fp32 state).  Inputs are seeded synthetic tensors with
+the value distributions BASELINE.json names.  `value` times the kernels with the inputs
+resident in HBM; `e2e` times the same public API calls with pinned-host inputs copied in and
+the results copied out inside the timed region.  With N > 1 ranks every rank processes its
+own sequence (weak scaling, no data-path collective).
+
+`--impl reference` times the CPU oracle (a restatement of the reference's pure-PyTorch
+implementation, the only implementation of this path the reference can run without a GPU)
+on the host cores, on a bounded sample of the same workload.
+"""
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import torch
+import torch.nn.functional as F
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+H, HKV, DK, CHUNK = 8, 2, 128, 64
+T_PREFILL = 65536
+DEC_B, DEC_CTX, DEC_BLOCK = 64, 32768, 256
+METRIC = "global_layer_prefill_tok_s_at_64k"
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(hbm=d["hbm_gbs"], tf_burst=d["bf16_tflops"], tf_sustained=d["bf16_tflops_sustained"],
+                    source="measured")
+    return dict(hbm=6650.0, tf_burst=1590.0, tf_sustained=1400.0, source="fallback")
+
+
+def polar_flops(T):
+    return 4.0 * H * DK * T * (T + 1) / 2.0          # QK^T + PV over the causal triangle
+
+
+def scan_flops(T):
+    return 155648.0 * H * T                           # per token per head: 4C dk + 6 dk dv + 3C dv
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons, sampled while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu, self.proc, self.path = gpu_index, None, None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path):
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(n)
+        os.unlink(self.path)
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+def make_prefill_inputs(seed, device=None, pinned=False):
+    """One 64K-token sequence for one global layer: q ~ N(0,1) bf16 (B,T,H,dk), k/v with the
+    2 un-expanded KV heads for Polar; the memory branch sees the same q and the expanded k, v
+    (inference/models/atma.py:416-420), gates as BASELINE config 3 names them."""
+    g = torch.Generator().manual_seed(seed)
+    T = T_PREFILL
+    t = dict(
+        q=torch.randn(1, T, H, DK, generator=g).to(torch.bfloat16),
+        k=torch.randn(1, T, HKV, DK, generator=g).to(torch.bfloat16),
+        v=torch.randn(1, T, HKV, DK, generator=g).to(torch.bfloat16),
+        g=(-F.softplus(torch.randn(1, T, H, generator=g))).float(),
+        beta=torch.sigmoid(torch.randn(1, T, H, generator=g)).float(),
+    )
+    if pinned:
+        t = {n: x.pin_memory() for n, x in t.items()}
+    if device is not None:
+        t = {n: x.to(device) for n, x in t.items()}
+    return t
+
+
+def default_polar_params(device):
+    return dict(v_null=torch.zeros(H, DK, device=device), null_base=torch.full((H,), 2.0, device=device),
+                null_slope_raw=torch.full((H,), 0.5, device=device), len_gain_raw=torch.full((H,), -1.0, device=device),
+                mag_beta_raw=torch.full((H,), -1.5, device=device))
+
+
+def prefill_step(ab, t, n_keys, params, events=None):
+    """Polar prefill + gated-delta scan through the public API.  Returns (c, mag, o, S)."""
+    if events is not None:
+        events[0].record()
+    c, mag = ab.polar_attention_fwd(t["q"].transpose(1, 2), t["k"].transpose(1, 2), t["v"].transpose(1, 2),
+                                    n_keys, **params)
+    if events is not None:
+        events[1].record()
+    if events is not None:
+        events[2].record()
+    o, S = ab.chunk_gated_delta_rule(q=t["q"], k=t["k"], v=t["v"], g=t["g"], beta=t["beta"], scale=1.0,
+                                     output_final_state=True, use_qk_l2norm_in_kernel=True)
+    if events is not None:
+        events[3].record()
+    return c, mag, o, S
+
+
+def bench_decode(ab, device, steps, warmup, peaks):
+    """Decode of one global layer's mixing at batch 64 x 32K context: KV scatter of the new
+    token, paged Polar decode, gated-delta state step.  Context larger than L2 by 17x."""
+    g = torch.Generator().manual_seed(3)
+    nblk_seq = DEC_CTX // DEC_BLOCK
+    num_blocks = DEC_B * nblk_seq
+    k_cache = torch.randn(num_blocks, DEC_BLOCK, HKV, DK, device=device, dtype=torch.bfloat16)
+    v_cache = torch.randn(num_blocks, DEC_BLOCK, HKV, DK, device=device, dtype=torch.bfloat16)
+    bt = torch.randperm(num_blocks, generator=g).to(torch.int32).view(DEC_B, nblk_seq).to(device)
+    cl = torch.full((DEC_B,), DEC_CTX, dtype=torch.int32, device=device)
+    q = torch.randn(DEC_B, H, DK, device=device, dtype=torch.bfloat16)
+    kn = torch.randn(DEC_B, HKV, DK, device=device, dtype=torch.bfloat16)
+    vn = torch.randn(DEC_B, HKV, DK, device=device, dtype=torch.bfloat16)
+    slot_map = (bt[:, -1].long() * DEC_BLOCK + DEC_BLOCK - 1).to(torch.int32)
+    state = torch.randn(DEC_B, H, DK, DK, device=device) * 0.1
+    gamma = torch.rand(DEC_B, H, device=device) * 0.1 + 0.9
+    beta = torch.rand(DEC_B, H, device=device)
+    slots = torch.arange(DEC_B, device=device)
+    params = default_polar_params(device)
+
+    def step():
+        ab.store_kvcache(kn, vn, k_cache, v_cache, slot_map)
+        c, mag = ab.polar_attention_decode(q, k_cache, v_cache, bt, cl, **params)
+        ke = kn.repeat_interleave(H // HKV, dim=1)
+        ve = vn.repeat_interleave(H // HKV, dim=1)
+        r = ab.gated_delta_decode_step(q, ke, ve, gamma, beta, state, slots)
+        return c, mag, r
+
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    pe = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    e0.record()
+    for i in range(steps):
+        ab.store_kvcache(kn, vn, k_cache, v_cache, slot_map)
+        pe[i][0].record()
+        ab.polar_attention_decode(q, k_cache, v_cache, bt, cl, **params)
+        pe[i][1].record()
+        ab.gated_delta_decode_step(q, kn.repeat_interleave(H // HKV, dim=1), vn.repeat_interleave(H // HKV, dim=1),
+                                   gamma, beta, state, slots)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    polar_ms = sum(a.elapsed_time(b) for a, b in pe) / steps
+    kv_bytes = 2.0 * DEC_B * DEC_CTX * HKV * DK * 2
+    state_bytes = 2.0 * DEC_B * H * DK * DK * 4
+    return {
+        "metric": "global_layer_decode_tok_s_at_b64_ctx32k", "value": DEC_B / (ms * 1e-3), "unit": "tok/s",
+        "ms_per_step": ms, "config": {"batch": DEC_B, "context": DEC_CTX, "block_size": DEC_BLOCK, "layers": 1},
+        "roofline": {"kernel": "polar_decode (split + merge)", "bound": "hbm",
+                     "achieved": kv_bytes / (polar_ms * 1e-3) / 1e9, "peak": peaks["hbm"], "unit": "GB/s",
+                     "frac": kv_bytes / (polar_ms * 1e-3) / 1e9 / peaks["hbm"], "traffic": None,
+                     "algorithmic_bytes": kv_bytes, "kernel_ms": polar_ms, "peak_source": peaks["source"]},
+        "step_bytes": kv_bytes + state_bytes,
+        "step_hbm_frac": (kv_bytes + state_bytes) / (ms * 1e-3) / 1e9 / peaks["hbm"],
+    }
+
+
+def cpu_baseline(sample_T, threads):
+    """The oracle (restating the reference's polar_reduce + gated_delta_chunked CPU path) on
+    one global layer at `sample_T` tokens.  Returns seconds."""
+    import oracle
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(0)
+    q = torch.randn(1, H, sample_T, DK, generator=g)
+    k = torch.randn(1, HKV, sample_T, DK, generator=g)
+    v = torch.randn(1, HKV, sample_T, DK, generator=g)
+    params = {n: x.cpu() for n, x in default_polar_params("cpu").items()}
+    n_keys = torch.arange(1, sample_T + 1, dtype=torch.float32)
+    glog = -F.softplus(torch.randn(1, sample_T, H, generator=g))
+    beta = torch.sigmoid(torch.randn(1, sample_T, H, generator=g))
+    t0 = time.perf_counter()
+    oracle.polar_prefill_oracle(q, k, v, n_keys, params)
+    ke, ve = k.repeat_interleave(H // HKV, 1), v.repeat_interleave(H // HKV, 1)
+    oracle.chunk_gated_delta_rule_oracle(q.transpose(1, 2), ke.transpose(1, 2), ve.transpose(1, 2), glog, beta, chunk=CHUNK)
+    return time.perf_counter() - t0
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    t_probe = cpu_baseline(512, threads)
+    budget = 150.0 / max(1, args.steps + args.warmup)
+    sample_T = 512
+    for cand in (1024, 2048, 4096):
+        if t_probe * (cand / 512.0) ** 2 < budget:      # materialised Polar is quadratic
+            sample_T = cand
+    for _ in range(args.warmup):
+        cpu_baseline(sample_T, threads)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_baseline(sample_T, threads)
+    sec = (time.perf_counter() - t0) / max(1, args.steps)
+    val = sample_T / sec
+    sample = (f"one global layer (Polar materialised + gated-delta chunked, fp32) at T={sample_T} tokens; "
+              f"Polar cost is quadratic, so tok/s at 64K would be ~{T_PREFILL // sample_T}x lower")
+    line = {"impl": "reference", "metric": METRIC, "value": val, "unit": "tok/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "global-layer mixing prefill (Polar + gated-delta scan), CPU sample",
+                       "tokens": sample_T, "heads": H, "kv_heads": HKV, "head_dim": DK, "chunk": CHUNK},
+            "cpu_baseline": {"value": val, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": val, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline leg (profiling runs)")
+    ap.add_argument("--skip-decode", action="store_true", help="omit the decode leg (profiling runs)")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    args.warmup = max(args.warmup, 3)
+
+    import atma_b200 as ab
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+    peaks = measured_peaks()
+
+    host = make_prefill_inputs(seed=4 + rank, pinned=True)
+    dev_in = {n: x.to(device) for n, x in host.items()}
+    params = default_polar_params(device)
+    n_keys = torch.arange(1, T_PREFILL + 1, dtype=torch.float32, device=device)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- kernel-resident timing ("value") -------------------------------------------------------
+    for _ in range(args.warmup):
+        prefill_step(ab, dev_in, n_keys, params)
+    sampler = ClockSampler(local_rank)
+    barrier()
+    sampler.start()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        prefill_step(ab, dev_in, n_keys, params, ev[i])
+    e1.record()
+    barrier()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / args.steps
+    polar_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / args.steps
+    scan_ms = sum(e[2].elapsed_time(e[3]) for e in ev) / args.steps
+
+    # ---- end to end: pinned host inputs in, results out, inside the timed region ------------------
+    out_host = None
+
+    def e2e_step():
+        nonlocal out_host
+        t = {n: x.to(device, non_blocking=True) for n, x in host.items()}
+        c, mag, o, S = prefill_step(ab, t, n_keys, params)
+        if out_host is None:
+            out_host = [torch.empty(x.shape, dtype=x.dtype, pin_memory=True) for x in (c, mag, o, S)]
+        for dst, src in zip(out_host, (c, mag, o, S)):
+            dst.copy_(src, non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    s1.record()
+    barrier()
+    e2e_ms = s0.elapsed_time(s1) / args.steps
+    h2d = sum(x.numel() * x.element_size() for x in host.values())
+    d2h = sum(x.numel() * x.element_size() for x in out_host)
+
+    times = torch.tensor([ms, e2e_ms, polar_ms, scan_ms], device=device, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms, e2e_ms, polar_ms, scan_ms = times.tolist()
+
+    decode = None
+    if rank == 0 and not args.skip_decode:
+        del dev_in
+        torch.cuda.empty_cache()
+        decode = bench_decode(ab, device, max(args.steps, 10), args.warmup, peaks)
+    cpu = None
+    if rank == 0 and world == 1 and not args.skip_cpu:
+        threads = os.cpu_count() or 1
+        sample_T = 4096
+        sec = cpu_baseline(sample_T, threads)
+        cpu = {"value": sample_T / sec, "unit": "tok/s", "cores": threads, "kind": "port",
+               "sample": f"one global layer (Polar materialised + gated-delta chunked, fp32) at T={sample_T}: "
+                         f"{sec:.2f} s; Polar cost is quadratic, so tok/s at 64K would be ~16x lower"}
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+
+    from atma_b200 import _lib
+    from ctypes import byref
+    probe = _lib.PolarPrefillArgs()
+    probe.dtype, probe.dk, probe.H, probe.Hkv, probe.n_tiles, probe.finalize = 1, DK, H, HKV, 0, 1
+    tensor_path = bool(_lib.load().atma_polar_prefill_path(byref(probe)))
+    peak_tf = peaks["tf_sustained"] if ms > 1000 else peaks["tf_burst"]
+    achieved_tf = polar_flops(T_PREFILL) / (polar_ms * 1e-3) / 1e12
+    line = {
+        "metric": METRIC, "value": world * T_PREFILL / (ms * 1e-3), "unit": "tok/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "global-layer mixing prefill: Polar attention + gated-delta scan, one 65536-token sequence per GPU",
+                   "tokens": T_PREFILL, "heads": H, "kv_heads": HKV, "head_dim": DK, "chunk": CHUNK,
+                   "window": None, "l2": "inputs (268 MB) larger than L2 (126 MB)",
+                   "polar_kernel": "tcgen05" if tensor_path else "cuda-core fp32"},
+        "e2e": {"value": world * T_PREFILL / (e2e_ms * 1e-3), "unit": "tok/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": 3 * args.steps,
+        "clocks": clocks,
+        "roofline": {"kernel": "polar_prefill", "bound": "tensor", "achieved": achieved_tf, "peak": peak_tf,
+                     "unit": "TFLOP/s", "frac": achieved_tf / peak_tf, "traffic": None,
+                     "algorithmic_flops": polar_flops(T_PREFILL), "kernel_ms": polar_ms,
+                     "peak_source": peaks["source"] + (" sustained" if ms > 1000 else " burst")},
+        "scan": {"kernel_ms": scan_ms, "tflops": scan_flops(T_PREFILL) / (scan_ms * 1e-3) / 1e12,
+                 "algorithmic_flops": scan_flops(T_PREFILL)},
+        "cpu_baseline": cpu,
+        "decode": decode,
+    }
+    print(json.dumps(line))
+
+
+if __name__ == "__main__":
+    main()

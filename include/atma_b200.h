@@ -1,0 +1,215 @@
+/*
+ * atma_b200 - C ABI of the B200 (sm_100a) kernels for ATMA's global-mixing hot path.
+ *
+ * Every entry point takes plain device pointers, sizes, element strides and a CUDA
+ * stream (passed as void*; NULL = the legacy default stream).  Nothing here allocates
+ * or synchronises unless its comment says so; outputs and scratch are caller-owned.
+ * All calls return ATMA_OK (0) or a negative atma_status; atma_last_error() returns a
+ * message for the calling thread's last failure.
+ *
+ * Each declaration names the function of the reference (akbar2habibullah/atma) whose
+ * device work it replaces, by path:line inside that project.
+ */
+#ifndef ATMA_B200_H_
+#define ATMA_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum { ATMA_OK = 0, ATMA_ERR_INVALID = -1, ATMA_ERR_CUDA = -2, ATMA_ERR_UNSUPPORTED = -3 } atma_status;
+
+/* Element types of activations / caches.  Statistics and recurrent state are always fp32. */
+typedef enum { ATMA_F32 = 0, ATMA_BF16 = 1, ATMA_F16 = 2 } atma_dtype;
+
+const char* atma_last_error(void);
+int atma_abi_version(void);
+
+/* ------------------------------------------------------------------------------------
+ * Polar Attention prefill.
+ * Replaces kernel/polar_triton.py:49-191 (_polar_fwd_kernel) as launched by
+ * _polar_forward (:505-590) behind polar_attention_fwd (:594-609), and - with a tile map
+ * - kernel/polar_triton.py:194-309 / :613-669 (polar_attention_packed_fwd).
+ *
+ * q is [B][H][Tq][dk], k and v are [B][Hkv][Tk][dk] addressed through element strides
+ * (innermost dimension contiguous), so both (B,H,T,dk) and (B,T,H,dk) storage work and
+ * K/V need NOT be expanded to H heads (Hkv must divide H; head h reads KV head
+ * h / (H/Hkv)).  Key j (absolute position key_offset + j) is visible to query i iff
+ * pos < n_i and (window > 0) pos >= n_i - window.  n_i comes from n_keys[i] (fp32,
+ * length Tq) or, when n_keys is NULL, n_i = n_base + i + 1.
+ *
+ * spg, sps, beta are softplus(len_gain_raw), softplus(null_slope_raw),
+ * softplus(mag_beta_raw) - the host applies softplus as polar_triton.py:540-542 does.
+ *
+ * Streaming statistics (all fp32): m, L, Q2 are [B][H][Tq], S is [B][H][Tq][dk], dense.
+ * stats_in  != NULL: continue from the statistics of earlier key blocks (ring pass).
+ * finalize  != 0   : fold the null sink and write c [B][H][Tq][dk] (strided, dtype) and
+ *                    mag [B][H][Tq] (strided, dtype).
+ * finalize  == 0   : write the running statistics to stats_out instead (c, mag unused).
+ *
+ * Packed mode (n_tiles > 0): B must be 1 and q, k, v are the packed [tokens][heads][dk]
+ * arrays (pass their strides as h- and t-strides); tile t covers query rows
+ * tile_q_start[t] .. +127 of the sequence that starts at packed row tile_seq_start[t]
+ * and has tile_seq_len[t] tokens; n_i = local query index + 1.
+ * ---------------------------------------------------------------------------------- */
+typedef struct {
+  const void* q; const void* k; const void* v;
+  int64_t q_sb, q_sh, q_st;          /* element strides; innermost stride must be 1 */
+  int64_t k_sb, k_sh, k_st;
+  int64_t v_sb, v_sh, v_st;
+  void* c; int64_t c_sb, c_sh, c_st;
+  void* mag; int64_t mag_sb, mag_sh, mag_st;
+  const float* n_keys;               /* [Tq] or NULL */
+  float n_base;                      /* used when n_keys == NULL */
+  int64_t key_offset;                /* absolute position of key row 0 */
+  const float* v_null;               /* [H][dk] fp32 */
+  const float* spg; const float* null_base; const float* sps; const float* beta;  /* [H] fp32 */
+  const float* stats_in_m; const float* stats_in_l; const float* stats_in_q2; const float* stats_in_s;
+  float* stats_out_m; float* stats_out_l; float* stats_out_q2; float* stats_out_s;
+  int finalize;
+  int B, H, Hkv, Tq, Tk, dk;
+  int dtype;                         /* atma_dtype of q, k, v, c, mag */
+  int window;                        /* 0 = full context */
+  float eps;
+  const int32_t* tile_seq_start; const int32_t* tile_q_start; const int32_t* tile_seq_len;
+  int n_tiles;                       /* 0 = dense mode */
+} atma_polar_prefill_args;
+
+int atma_polar_prefill(const atma_polar_prefill_args* args, void* stream);
+
+/* Which implementation atma_polar_prefill would run for these arguments:
+ * 1 = tcgen05/TMEM/TMA tile kernel (16-bit, dk = 128), 0 = fp32 CUDA-core kernel. */
+int atma_polar_prefill_path(const atma_polar_prefill_args* args);
+
+/* ------------------------------------------------------------------------------------
+ * Paged Polar decode.  Replaces kernel/polar_triton.py:681-792 (_polar_decode_kernel)
+ * behind polar_attention_decode (:796-858).
+ * q [B][H][dk] (dense); k_cache, v_cache [num_blocks][block_size][Hkv][dk] (dense);
+ * block_tables int32 [B][max_blocks] (row stride bt_stride); context_lens int32 [B].
+ * c [B][H][dk], mag [B][H] in `dtype`.
+ * The context of each (sequence, KV head) is cut into n_splits key ranges that run as
+ * separate CTAs; their partial statistics go through `scratch` (fp32, at least
+ * atma_polar_decode_scratch_floats(B, H, dk, n_splits) floats) and a second kernel
+ * merges them and folds the null sink.  Launch shapes depend only on the arguments
+ * passed here, never on device data, so the call can be captured in a CUDA graph.
+ * ---------------------------------------------------------------------------------- */
+typedef struct {
+  const void* q; const void* k_cache; const void* v_cache;
+  const int32_t* block_tables; int64_t bt_stride;
+  const int32_t* context_lens;
+  const float* v_null; const float* spg; const float* null_base; const float* sps; const float* beta;
+  void* c; void* mag;
+  float* scratch;
+  int B, H, Hkv, dk, block_size, max_blocks, num_blocks;
+  int n_splits;
+  int dtype;
+  int window;
+  float eps;
+} atma_polar_decode_args;
+
+int64_t atma_polar_decode_scratch_floats(int B, int H, int dk, int n_splits);
+int atma_polar_decode(const atma_polar_decode_args* args, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * Gated-delta decode step, in place on a slot-indexed state table.
+ * Replaces kernel/gated_delta_triton.py:36-75 behind gated_delta_decode_step (:79-117).
+ * q, k, v [B][H][d] with element strides (sb, sh), innermost contiguous, dtype `dtype`;
+ * gamma, beta fp32 [B][H] dense; state fp32 [max_seqs][H][dk][dv] with strides
+ * (state_ss, state_sh), [dk][dv] dense, UPDATED IN PLACE; slots int64 [B];
+ * r fp32 [B][H][dv] dense.  A negative slot skips the row (its r is zeroed).
+ * ---------------------------------------------------------------------------------- */
+int atma_gated_delta_decode_step(const void* q, const void* k, const void* v,
+                                 int64_t q_sb, int64_t q_sh, int64_t k_sb, int64_t k_sh,
+                                 int64_t v_sb, int64_t v_sh, int dtype,
+                                 const float* gamma, const float* beta,
+                                 float* state, int64_t state_ss, int64_t state_sh,
+                                 const int64_t* slots, float* r,
+                                 int B, int H, int dk, int dv, float eps, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * Gated-delta chunked scan.  Replaces the third-party flash-linear-attention call
+ * chunk_gated_delta_rule(q,k,v,g,beta,scale=1,initial_state,output_final_state,
+ * use_qk_l2norm_in_kernel=True) made at inference/models/atma.py:285-287,318-322 and
+ * model/blocks.py:48-49; semantics are those of model/blocks.py:375-423.
+ * q [B][T][H][dk], k [B][T][Hkv][dk], v [B][T][Hkv][dv] dense, dtype `dtype` (Hkv divides H;
+ * head h reads KV head h / (H/Hkv); the reference passes Hkv == H); g (log decay <= 0) and
+ * beta fp32 [B][T][H]; initial_state fp32 [B][H][dk][dv] or NULL (zeros); o [B][T][H][dv] in
+ * `dtype`; final_state fp32 [B][H][dk][dv] or NULL.  `scratch` holds the chunk-local
+ * factors: at least atma_gated_delta_scan_scratch_bytes(B,T,H,dk,dv) bytes.
+ * `normalize_qk` != 0 L2-normalises q and k rows in-kernel (x / max(||x||, 1e-12), as
+ * F.normalize does); `scale` multiplies q.
+ * ---------------------------------------------------------------------------------- */
+int64_t atma_gated_delta_scan_scratch_bytes(int B, int T, int H, int dk, int dv);
+int atma_gated_delta_scan(const void* q, const void* k, const void* v, int dtype,
+                          const float* g, const float* beta,
+                          const float* initial_state, void* o, float* final_state,
+                          void* scratch, int B, int T, int H, int Hkv, int dk, int dv,
+                          int normalize_qk, float scale, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * Depthwise causal conv, one decode step, in place on a slot-indexed state table.
+ * Replaces kernel/causal_conv1d_triton.py:17-42 behind causal_conv1d_decode_step (:46-63).
+ * x, out [B][D] (row strides x_sb / out_sb), weight [D][K] dense, state [max_seqs][D][K-1]
+ * with slot stride state_ss, all of dtype `dtype`; slots int64 [B].  K in 2..8.
+ * ---------------------------------------------------------------------------------- */
+int atma_causal_conv1d_decode_step(const void* x, int64_t x_sb, const void* weight,
+                                   const int64_t* slots, void* state, int64_t state_ss,
+                                   void* out, int64_t out_sb, int B, int D, int K,
+                                   int dtype, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * Depthwise causal conv over packed ragged prompts + final-state write.
+ * Replaces kernel/inference_ops_triton.py:17-63 behind packed_causal_conv1d (:139-160),
+ * and the per-sequence conv of inference/models/atma.py:104-157.
+ * x, out [tokens][C] (row strides), weight [C][K] dense, K in 2..4; per-token int32 maps
+ * token_seq_start / token_seq_end / token_seq_slot.  state [max_seqs][C][K-1] receives the
+ * last K-1 inputs of every sequence (zeros where the prompt is shorter).  init_state, if
+ * not NULL, is a table of the same shape whose rows supply the left context instead of
+ * zeros (a continuation chunk); it must not alias `state`.  residual != 0 adds x to the
+ * result (the Canon form q + conv(q)).
+ * ---------------------------------------------------------------------------------- */
+int atma_packed_causal_conv1d(const void* x, int64_t x_st, const void* weight,
+                              void* out, int64_t out_st,
+                              void* state, const void* init_state, int64_t state_ss,
+                              const int32_t* token_seq_start, const int32_t* token_seq_end,
+                              const int32_t* token_seq_slot,
+                              int total, int C, int K, int dtype, int residual, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * Scatter new K/V rows into the paged cache.  Replaces inference/layers/attention.py:7-27
+ * behind store_kvcache (:30-56).  key, value [N][D] with row strides (D = Hkv*dk
+ * contiguous); caches are flat [slots][D]; slot_mapping int32 [N], -1 skips the row.
+ * ---------------------------------------------------------------------------------- */
+int atma_store_kvcache(const void* key, int64_t key_stride, const void* value, int64_t value_stride,
+                       void* k_cache, void* v_cache, const int32_t* slot_mapping,
+                       int N, int D, int elem_size, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * gate * relu(x)^2 with eager-bf16 rounding of the square.
+ * Replaces kernel/inference_ops_triton.py:102-120 behind squared_relu_gate (:124-135).
+ * x, gate [rows][width] with row strides (columns contiguous); out dense.
+ * ---------------------------------------------------------------------------------- */
+int atma_squared_relu_gate(const void* x, int64_t x_stride, const void* gate, int64_t gate_stride,
+                           void* out, int rows, int width, int dtype, void* stream);
+
+/* 15 x / sqrt(x^2 + 225) with eager-bf16 rounding after each op.
+ * Replaces kernel/inference_ops_triton.py:194-211 behind softcap_logits (:215-223). */
+int atma_softcap_logits(const void* x, void* out, int64_t n, int dtype, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * Projection + affine-free per-head RMSNorm.  Replaces the prototype
+ * kernel/inference_ops_triton.py:65-100 behind linear_head_rms (:164-189).
+ * x [M][K] dense, weight [heads*width][K] dense, bias [heads*width] or NULL, out
+ * [M][heads*width]; width = head_dim * (gated ? 2 : 1); only the first head_dim columns
+ * of each head are normalised.
+ * ---------------------------------------------------------------------------------- */
+int atma_linear_head_rms(const void* x, const void* weight, const void* bias, void* out,
+                         int M, int K, int heads, int head_dim, int gated, float eps,
+                         int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ATMA_B200_H_ */

@@ -1,0 +1,120 @@
+"""GPU parity: paged Polar decode (through the C ABI) against the CPU oracle."""
+
+import pytest
+import torch
+
+import atma_b200
+import oracle
+from conftest import max_abs, max_rel
+from gpu_util import polar_params, rand
+
+pytestmark = pytest.mark.gpu
+
+
+def make_paged(B, Hkv, dk, block_size, lens, dtype, seed, extra_blocks=3):
+    """Random K/V per sequence laid out in a paged cache through a random page permutation."""
+    max_blocks = max(1, max((n + block_size - 1) // block_size for n in lens))
+    need = sum((n + block_size - 1) // block_size for n in lens)
+    num_blocks = need + extra_blocks
+    g = torch.Generator().manual_seed(seed)
+    perm = torch.randperm(num_blocks, generator=g)
+    k_cache = torch.randn(num_blocks, block_size, Hkv, dk, generator=g).to(dtype)   # stale data in unused rows
+    v_cache = torch.randn(num_blocks, block_size, Hkv, dk, generator=g).to(dtype)
+    bt = torch.full((B, max_blocks), -1, dtype=torch.int32)
+    used = 0
+    for b, n in enumerate(lens):
+        nb = (n + block_size - 1) // block_size
+        bt[b, :nb] = perm[used:used + nb].int()
+        used += nb
+    return k_cache, v_cache, bt, torch.tensor(lens, dtype=torch.int32)
+
+
+def run_decode(B, H, Hkv, dk, block_size, lens, dtype, seed, window=None, num_splits=None):
+    k_cache, v_cache, bt, cl = make_paged(B, Hkv, dk, block_size, lens, dtype, seed)
+    q = rand((B, H, dk), seed + 5, dtype)
+    pc, pg = polar_params(H, dk, seed)
+    c_ref, m_ref = oracle.polar_decode_oracle(q, k_cache, v_cache, bt, cl, pc, window=window)
+    c, m = atma_b200.polar_attention_decode(q.cuda(), k_cache.cuda(), v_cache.cuda(), bt.cuda(), cl.cuda(),
+                                            window=window, num_splits=num_splits, **pg)
+    assert c.shape == (B, H, dk) and m.shape == (B, H) and c.dtype == dtype
+    if dtype == torch.float32:
+        assert max_abs(c, c_ref) < 1e-4 and max_abs(m, m_ref) < 1e-4
+    else:
+        assert max_rel(c, c_ref) < 2e-2 and max_abs(m, m_ref) < 2e-2
+    return c, m
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_ragged_batch(dtype):
+    run_decode(5, 8, 2, 128, 16, [1, 15, 16, 17, 200], dtype, seed=1)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dk,H,Hkv", [(64, 4, 2), (128, 8, 8), (128, 4, 1), (32, 2, 1), (128, 16, 2)])
+def test_head_layouts(dtype, dk, H, Hkv):
+    run_decode(3, H, Hkv, dk, 32, [40, 129, 77], dtype, seed=dk + H)
+
+
+@pytest.mark.parametrize("window", [4, 64])
+def test_window(window):
+    run_decode(4, 8, 2, 128, 16, [3, 64, 65, 300], torch.float32, seed=2, window=window)
+    run_decode(4, 8, 2, 128, 16, [3, 64, 65, 300], torch.bfloat16, seed=2, window=window)
+
+
+def test_empty_and_padded_rows():
+    """context_len 0 (a padded CUDA-graph row): everything drains to the null sink; the
+    -1 page ids of unused table entries are never dereferenced."""
+    c, m = run_decode(3, 4, 2, 128, 16, [0, 5, 0], torch.float32, seed=3)
+    assert float(m[0].abs().max()) < 1e-6
+
+
+@pytest.mark.parametrize("splits", [1, 2, 7, 32])
+def test_split_count_does_not_change_the_result(splits):
+    c1, m1 = run_decode(2, 8, 2, 128, 256, [2048, 777], torch.bfloat16, seed=4, num_splits=1)
+    c2, m2 = run_decode(2, 8, 2, 128, 256, [2048, 777], torch.bfloat16, seed=4, num_splits=splits)
+    assert max_abs(c1, c2) < 4e-3 and max_abs(m1, m2) < 4e-3
+
+
+def test_decode_equals_last_prefill_row():
+    """Engine invariant: decoding token T over a cache holding the prompt == row T-1 of prefill."""
+    B, H, Hkv, T, dk, bs = 2, 8, 2, 700, 128, 256
+    q = rand((B, H, T, dk), 31, torch.bfloat16).cuda()
+    k = rand((B, Hkv, T, dk), 32, torch.bfloat16).cuda()
+    v = rand((B, Hkv, T, dk), 33, torch.bfloat16).cuda()
+    _, pg = polar_params(H, dk, 31)
+    n = torch.arange(1, T + 1, dtype=torch.float32).cuda()
+    c_pre, m_pre = atma_b200.polar_attention_fwd(q, k, v, n, **pg)
+    nb = (T + bs - 1) // bs
+    k_cache = torch.zeros(B * nb, bs, Hkv, dk, dtype=torch.bfloat16, device="cuda")
+    v_cache = torch.zeros_like(k_cache)
+    slots = torch.arange(B * nb * bs, device="cuda", dtype=torch.int32).view(B, nb * bs)[:, :T].reshape(-1)
+    atma_b200.store_kvcache(k.transpose(1, 2).reshape(B * T, Hkv, dk), v.transpose(1, 2).reshape(B * T, Hkv, dk),
+                            k_cache, v_cache, slots)
+    bt = torch.arange(B * nb, device="cuda", dtype=torch.int32).view(B, nb)
+    cl = torch.full((B,), T, device="cuda", dtype=torch.int32)
+    c, m = atma_b200.polar_attention_decode(q[:, :, -1].contiguous(), k_cache, v_cache, bt, cl, **pg)
+    assert max_rel(c, c_pre[:, :, -1]) < 2e-2 and max_abs(m, m_pre[:, :, -1]) < 2e-2
+
+
+def test_cuda_graph_capture_and_replay():
+    """The decode call has fixed launch shapes and reads lengths on the device, so it can be
+    captured once and replayed with new lengths (inference/engine/model_runner.py:254-310)."""
+    B, H, Hkv, dk, bs = 4, 8, 2, 128, 64
+    lens = [100, 64, 1, 250]
+    k_cache, v_cache, bt, cl = make_paged(B, Hkv, dk, bs, [256] * B, torch.bfloat16, 5)
+    q = rand((B, H, dk), 6, torch.bfloat16).cuda()
+    pc, pg = polar_params(H, dk, 5)
+    kc, vc, btg = k_cache.cuda(), v_cache.cuda(), bt.cuda()
+    clg = torch.tensor([256] * B, dtype=torch.int32, device="cuda")
+    atma_b200.polar_attention_decode(q, kc, vc, btg, clg, **pg)          # warm scratch outside capture
+    graph = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        with torch.cuda.graph(graph, stream=s):
+            c, m = atma_b200.polar_attention_decode(q, kc, vc, btg, clg, **pg)
+    clg.copy_(torch.tensor(lens, dtype=torch.int32))
+    graph.replay()
+    torch.cuda.synchronize()
+    c_ref, m_ref = oracle.polar_decode_oracle(q.cpu(), k_cache, v_cache, bt, torch.tensor(lens, dtype=torch.int32), pc)
+    assert max_rel(c, c_ref) < 2e-2 and max_abs(m, m_ref) < 2e-2
