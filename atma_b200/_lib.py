@@ -61,6 +61,8 @@ _SIGNATURES = {
     "atma_polar_prefill_path": (c_int, [POINTER(PolarPrefillArgs)]),
     "atma_polar_decode_scratch_floats": (c_int64, [c_int, c_int, c_int, c_int]),
     "atma_polar_decode": (c_int, [POINTER(PolarDecodeArgs), c_void_p]),
+    "atma_polar_decode_static_max_floats": (c_int64, []),
+    "atma_polar_decode_static": (c_int, [POINTER(PolarDecodeArgs), c_void_p]),
     "atma_gated_delta_decode_step": (c_int, [c_void_p] * 3 + [c_int64] * 6 + [c_int, c_void_p, c_void_p,
                                              c_void_p, c_int64, c_int64, c_void_p, c_void_p,
                                              c_int, c_int, c_int, c_int, c_float, c_void_p]),

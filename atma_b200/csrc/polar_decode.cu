@@ -353,3 +353,45 @@ extern "C" int atma_polar_decode(const atma_polar_decode_args* args, void* strea
   ATMA_DISPATCH_DTYPE(a.dtype, T, { rc = launch_decode<T>(a, (cudaStream_t)stream); });
   return rc;
 }
+
+// ---- decode without caller scratch ---------------------------------------------------------
+// Some hosts of this library may not allocate device memory at the point where they decode:
+// an inference engine that sizes its KV cache to fill the GPU and hands every remaining byte
+// to the cache has nothing left to ask cudaMalloc for, and a serving loop that runs inside a
+// pre-planned memory arena is not allowed to.  For them the split partials live in a
+// fixed-size array that is part of the library image; every GPU that loads the library holds
+// these 4 MiB until the process exits.
+constexpr int64_t kStaticScratchFloats = 1 << 20;            // 4 MiB
+static __device__ __align__(256) float g_decode_scratch[kStaticScratchFloats];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_scratch_ptr[kMaxDevices] = {nullptr};               // device address of the array, per GPU
+}  // namespace
+
+extern "C" int64_t atma_polar_decode_static_max_floats(void) { return kStaticScratchFloats; }
+
+extern "C" int atma_polar_decode_static(const atma_polar_decode_args* args, void* stream) {
+  ATMA_REQUIRE(args != nullptr, "polar_decode_static: null args");
+  const int64_t need = atma_polar_decode_scratch_floats(args->B, args->H, args->dk, args->n_splits);
+  ATMA_REQUIRE(args->B >= 0 && args->H > 0 && args->dk > 0 && args->n_splits >= 1,
+               "polar_decode_static: bad shape");
+  ATMA_REQUIRE(need <= kStaticScratchFloats,
+               "polar_decode_static: B*H*n_splits*(4+dk) = %lld floats exceeds the built-in scratch of "
+               "%lld floats; lower n_splits or the batch, or call atma_polar_decode with caller scratch",
+               (long long)need, (long long)kStaticScratchFloats);
+  int dev = 0;
+  ATMA_CUDA_OK(cudaGetDevice(&dev));
+  ATMA_REQUIRE(dev >= 0 && dev < kMaxDevices, "polar_decode_static: device ordinal %d out of range", dev);
+  if (g_scratch_ptr[dev] == nullptr) {
+    // In host code the array's name is only a handle for the runtime; the address a kernel can
+    // use has to be asked for, once per device, with that device current.
+    float* p = nullptr;
+    ATMA_CUDA_OK(cudaGetSymbolAddress((void**)&p, g_decode_scratch));
+    ATMA_REQUIRE(p != nullptr, "polar_decode_static: no device address for the built-in scratch");
+    g_scratch_ptr[dev] = p;
+  }
+  atma_polar_decode_args a = *args;
+  a.scratch = g_scratch_ptr[dev];
+  return atma_polar_decode(&a, stream);
+}

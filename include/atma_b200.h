@@ -113,6 +113,28 @@ int64_t atma_polar_decode_scratch_floats(int B, int H, int dk, int n_splits);
 int atma_polar_decode(const atma_polar_decode_args* args, void* stream);
 
 /* ------------------------------------------------------------------------------------
+ * Paged Polar decode for callers that cannot allocate device memory.  (No counterpart in
+ * the reference, whose Python wrapper allocates freely.)
+ * Same arguments and results as atma_polar_decode, except that args->scratch is ignored:
+ * the split partials go to an array built into the library image (4 MiB per GPU, held by
+ * every GPU that loads the library until the process exits).  Meant for a host that has
+ * given all free device memory to its KV cache, or that runs inside a fixed memory plan,
+ * and so has no way to provide scratch at decode time.  The call makes no cudaMalloc,
+ * cudaFree or other allocating call.
+ *  - Limit: B*H*n_splits*(4+dk) must not exceed atma_polar_decode_static_max_floats()
+ *    (1,048,576 floats; e.g. B=64, H=8, dk=128 allows n_splits <= 15).  Larger requests
+ *    fail with ATMA_ERR_INVALID and a message; nothing is launched.
+ *  - The first call on each device looks up the array's device address (with that device
+ *    current); make that first call before any stream capture begins.
+ *  - All calls on a device share the one array, which keeps the previous call's partials.
+ *    Nothing in it has to start at zero: each call rewrites every entry it later reads.
+ *    Two calls whose kernels overlap on the GPU (different streams) race on it - keep
+ *    calls on one device ordered.
+ * ---------------------------------------------------------------------------------- */
+int64_t atma_polar_decode_static_max_floats(void);
+int atma_polar_decode_static(const atma_polar_decode_args* args, void* stream);
+
+/* ------------------------------------------------------------------------------------
  * Gated-delta decode step, in place on a slot-indexed state table.
  * Replaces kernel/gated_delta_triton.py:36-75 behind gated_delta_decode_step (:79-117).
  * q, k, v [B][H][d] with element strides (sb, sh), innermost contiguous, dtype `dtype`;
