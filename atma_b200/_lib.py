@@ -59,6 +59,7 @@ _SIGNATURES = {
     "atma_abi_version": (c_int, []),
     "atma_polar_prefill": (c_int, [POINTER(PolarPrefillArgs), c_void_p]),
     "atma_polar_prefill_path": (c_int, [POINTER(PolarPrefillArgs)]),
+    "atma_device_status": (c_int, [POINTER(c_int)]),
     "atma_polar_decode_scratch_floats": (c_int64, [c_int, c_int, c_int, c_int]),
     "atma_polar_decode": (c_int, [POINTER(PolarDecodeArgs), c_void_p]),
     "atma_polar_decode_static_max_floats": (c_int64, []),

@@ -83,6 +83,11 @@ int atma_polar_prefill(const atma_polar_prefill_args* args, void* stream);
  * 1 = tcgen05/TMEM/TMA tile kernel (16-bit, dk = 128), 0 = fp32 CUDA-core kernel. */
 int atma_polar_prefill_path(const atma_polar_prefill_args* args);
 
+/* Every wait inside the tensor-core kernels is bounded; a CTA whose wait ran out returns
+ * early and sets a device status word.  This call synchronises the device, writes the word
+ * (0 = no wait ever ran out) to *status and clears it.  (Diagnostic; no reference counterpart.) */
+int atma_device_status(int* status);
+
 /* ------------------------------------------------------------------------------------
  * Paged Polar decode.  Replaces kernel/polar_triton.py:681-792 (_polar_decode_kernel)
  * behind polar_attention_decode (:796-858).

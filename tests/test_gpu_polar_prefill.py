@@ -206,3 +206,19 @@ def test_full_size_config_rows_against_oracle():
     # size-independent property: c is a unit vector wherever any mass exists, mag in [0, 1)
     norms = c.float().norm(dim=-1)
     assert norms.max() < 1.01 and norms.min() > 0.98
+
+
+def test_tensor_core_path_is_taken_and_no_wait_ran_out():
+    """16-bit dk=128 inputs must run on the tcgen05 kernel, and none of its bounded waits may
+    have expired during this test session."""
+    from ctypes import byref, c_int
+    from atma_b200 import _lib
+    lib = _lib.load()
+    probe = _lib.PolarPrefillArgs()
+    probe.dtype, probe.dk, probe.H, probe.Hkv, probe.finalize = 1, 128, 8, 2, 1
+    assert lib.atma_polar_prefill_path(byref(probe)) == 1
+    probe.dtype = 0
+    assert lib.atma_polar_prefill_path(byref(probe)) == 0
+    status = c_int(-1)
+    _lib.check(lib.atma_device_status(byref(status)))
+    assert status.value == 0
