@@ -54,6 +54,11 @@ struct Params {
 };
 
 __device__ int g_sm100_status = 0;
+#ifdef ATMA_SM100_DEBUG
+__device__ float g_dbg_s[2][128][128];      // raw S of the first key tile, CTA (0,0,0)
+__device__ float g_dbg_o[2][128][128];      // final O
+__device__ float g_dbg_st[2][128][8];
+#endif
 
 struct Barriers {
   uint64_t q_full[2];
@@ -63,13 +68,13 @@ struct Barriers {
 
 __device__ __forceinline__ void tma_tile(void* dst, const CUtensorMap* m, uint64_t* bar, const int (&pos)[3],
                                          int row, int head, int b) {
-  int c[4];
-  c[pos[0]] = row; c[pos[1]] = head; c[pos[2]] = b;
+  // coordinate slot k (1..3) holds whichever of (row, head, b) the host sorted into it
+  const int c1 = pos[0] == 1 ? row : (pos[1] == 1 ? head : b);
+  const int c2 = pos[0] == 2 ? row : (pos[1] == 2 ? head : b);
+  const int c3 = pos[0] == 3 ? row : (pos[1] == 3 ? head : b);
 #pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    c[0] = half * 64;
-    tma_load_4d(static_cast<uint8_t*>(dst) + half * (kTileBytes / 2), m, bar, c[0], c[1], c[2], c[3]);
-  }
+  for (int half = 0; half < 2; ++half)
+    tma_load_4d(static_cast<uint8_t*>(dst) + half * (kTileBytes / 2), m, bar, half * 64, c1, c2, c3);
 }
 
 template <bool kBf16>
@@ -158,7 +163,7 @@ polar_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
   bool row_ok = false;
   int my_row = 0;
   if (warp >= 2) {
-    my_row = row0[sm_tile] + r_in_tile;
+    my_row = (sm_tile ? row0[1] : row0[0]) + r_in_tile;
     row_ok = my_row < q_limit;
     if (row_ok) n_i = packed ? (float)(my_row + 1) : (p.n_keys ? p.n_keys[my_row] : p.n_base + (float)(my_row + 1));
     float mn = row_ok ? n_i : 3.0e38f, mx = row_ok ? n_i : -1.0f;
@@ -196,12 +201,14 @@ polar_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
     jmin = a0 ? (a1 ? min(lo[0], lo[1]) : lo[0]) : (a1 ? lo[1] : 0);
     jmax = a0 ? (a1 ? max(hi[0], hi[1]) : hi[0]) : (a1 ? hi[1] : 0);
   }
-  auto active = [&](int t, int j) { return j >= lo[t] && j < hi[t]; };
+  // all per-tile scalars are selected with ternaries so that they stay in registers
+  auto active = [&](int t, int j) { return t ? (j >= lo[1] && j < hi[1]) : (j >= lo[0] && j < hi[0]); };
   volatile int* abort_flag = &s_abort;
 
   if (warp == 0) {
     // =============================== TMA producer ================================================
     if (lane == 0) {
+#pragma unroll
       for (int t = 0; t < 2; ++t) {
         if (hi[t] > lo[t]) {
           mbar_arrive_expect_tx(&bar.q_full[t], kTileBytes);
@@ -243,12 +250,14 @@ polar_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
                  (kk > 0 || acc) ? 1u : 0u);
       };
       if (jmax > jmin) {
-        for (int t = 0; t < 2 && ok; ++t)
-          if (hi[t] > lo[t]) ok = mbar_wait(&bar.q_full[t], 0, abort_flag);
+#pragma unroll
+        for (int t = 0; t < 2; ++t)
+          if (ok && hi[t] > lo[t]) ok = mbar_wait(&bar.q_full[t], 0, abort_flag);
         // prologue: S for the first key tile
         if (ok) ok = mbar_wait(&bar.k_full[0], 0, abort_flag);
         if (ok) {
           tc_fence_after();
+#pragma unroll
           for (int t = 0; t < 2; ++t)
             if (active(t, jmin)) { issue_qk(t, 0); tc_commit(&bar.s_full[t]); }
           tc_commit(&bar.k_empty[0]);
@@ -257,21 +266,24 @@ polar_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
           const int it = j - jmin, s = it % kStages, s1 = (it + 1) % kStages;
           const uint32_t ph = (uint32_t)(it / kStages) & 1u, ph1 = (uint32_t)((it + 1) / kStages) & 1u;
           bool v_ready = false, k1_ready = false;
-          for (int t = 0; t < 2 && ok; ++t) {
-            if (active(t, j)) {
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            if (ok && active(t, j)) {
               ok = mbar_wait(&bar.p_full[t], (uint32_t)(j - lo[t]) & 1u, abort_flag);
               if (ok && !v_ready) { ok = mbar_wait(&bar.v_full[s], ph, abort_flag); v_ready = true; }
-              if (!ok) break;
-              tc_fence_after();
-              issue_pv(t, s, carry_in || j > lo[t]);
-              if (!active(t, j + 1)) tc_commit(&bar.o_final[t]);
+              if (ok) {
+                tc_fence_after();
+                issue_pv(t, s, carry_in || j > lo[t]);
+                if (!active(t, j + 1)) tc_commit(&bar.o_final[t]);
+              }
             }
-            if (active(t, j + 1)) {
+            if (ok && active(t, j + 1)) {
               if (!k1_ready) { ok = mbar_wait(&bar.k_full[s1], ph1, abort_flag); k1_ready = true; }
-              if (!ok) break;
-              tc_fence_after();
-              issue_qk(t, s1);
-              tc_commit(&bar.s_full[t]);
+              if (ok) {
+                tc_fence_after();
+                issue_qk(t, s1);
+                tc_commit(&bar.s_full[t]);
+              }
             }
           }
           // keep the stage barriers in step even when no tile used this stage
@@ -287,19 +299,20 @@ polar_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
   } else {
     // =============================== softmax + epilogue ===========================================
     const int t = sm_tile;
-    const int h = head[t];
+    const int h = t ? head[1] : head[0];
+    const int my_lo = t ? lo[1] : lo[0], my_hi = t ? hi[1] : hi[0], my_row0 = t ? row0[1] : row0[0];
     const uint32_t lane_base = tbase + (uint32_t(32 * (warp & 3)) << 16);
     const uint32_t tS = lane_base + t * 128, tO = lane_base + 256 + t * 128;
     const float n_clamped = fmaxf(p.window > 0 ? fminf(n_i, (float)p.window) : n_i, 1.0f);
     const float temp = 1.0f + p.spg[h] * logf(n_clamped);
     const float sc2 = temp * rsqrtf((float)kDK) * kLog2e;
-    const int n_iter = hi[t] - lo[t];
+    const int n_iter = my_hi - my_lo;
     const int64_t srow = ((int64_t)b * p.H + h) * p.Tq + my_row;     // dense statistics index
 
     float m_used = kNegInit, m_run = kNegInit, L = 0.f, Q2 = 0.f;
     bool ok = true;
     bool o_live = false;                                            // O_t holds data (warp-uniform)
-    if (carry_in && row0[t] < q_limit) {
+    if (carry_in && my_row0 < q_limit) {
       if (row_ok) {
         const float mi = p.si_m[srow];
         m_used = m_run = (mi <= -1.0e37f) ? kNegInit : mi * kLog2e;
@@ -316,8 +329,8 @@ polar_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
       o_live = true;
     }
 
-    for (int j = lo[t]; j < hi[t]; ++j) {
-      ok = mbar_wait(&bar.s_full[t], (uint32_t)(j - lo[t]) & 1u, abort_flag);
+    for (int j = my_lo; j < my_hi; ++j) {
+      ok = mbar_wait(&bar.s_full[t], (uint32_t)(j - my_lo) & 1u, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
@@ -334,6 +347,10 @@ polar_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
       for (int ch = 0; ch < 4; ++ch) {
         uint32_t r[32];
         tmem_ld32(tS + ch * 32, r);
+#ifdef ATMA_SM100_DEBUG
+        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && j == my_lo)
+          for (int i = 0; i < 32; ++i) g_dbg_s[t][r_in_tile][ch * 32 + i] = __uint_as_float(r[i]);
+#endif
         if (full) {
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
@@ -403,7 +420,7 @@ polar_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
       ok = __all_sync(0xffffffffu, ok);
       tc_fence_after();
     }
-    if (ok && row0[t] < q_limit) {
+    if (ok && my_row0 < q_limit) {
       const bool have_o = o_live;                                   // else O is all zero
       if (!p.finalize) {
         if (row_ok) {
@@ -432,11 +449,21 @@ polar_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
         const float p_n = ex2(a_n - m_fin);
         const float Z = Lf + p_n;
         const float* vn = p.v_null + h * kDK;
+#ifdef ATMA_SM100_DEBUG
+        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+          float* d = g_dbg_st[t][r_in_tile];
+          d[0] = m_used; d[1] = L; d[2] = Q2; d[3] = sc2; d[4] = (float)h; d[5] = alpha; d[6] = (float)my_row + (row_ok ? 0.5f : 0.f); d[7] = (float)(b * p.c_sb + h * p.c_sh + (int64_t)(seq_row0 + my_row) * p.c_st);
+        }
+#endif
         float sq = 0.f;
 #pragma unroll 1
         for (int ch = 0; ch < 4; ++ch) {
           uint32_t r[32];
           if (have_o) tmem_ld32(tO + ch * 32, r);
+#ifdef ATMA_SM100_DEBUG
+          if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0)
+            for (int i = 0; i < 32; ++i) g_dbg_o[t][r_in_tile][ch * 32 + i] = have_o ? __uint_as_float(r[i]) : -777.f;
+#endif
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const float s = (have_o ? __uint_as_float(r[i]) * alpha : 0.f) + p_n * vn[ch * 32 + i];
@@ -566,6 +593,20 @@ int sm100_status_fetch_and_clear(int* out) {
 }
 
 }  // namespace atma
+
+#ifdef ATMA_SM100_DEBUG
+extern "C" int atma_debug_fetch(float* s_out, float* o_out) {
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(s_out, atma::g_dbg_s, sizeof(float) * 2 * 128 * 128);
+  cudaMemcpyFromSymbol(o_out, atma::g_dbg_o, sizeof(float) * 2 * 128 * 128);
+  return 0;
+}
+extern "C" int atma_debug_fetch_stats(float* st_out) {
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(st_out, atma::g_dbg_st, sizeof(float) * 2 * 128 * 8);
+  return 0;
+}
+#endif
 
 // Non-zero if a tensor-core kernel gave up on a bounded wait since the last call (synchronises
 // the device; clears the flag).
