@@ -216,6 +216,13 @@ scan_sequential_kernel(const float* __restrict__ scratch, const float* __restric
     for (int kk = warp; kk < dk; kk += NW) final_state[sbase + (int64_t)kk * dv + col] = S[kk * kScanSlice + lane];
 }
 
+// tensor-core version for 16-bit inputs with d_k = d_v = 128 (gated_delta_scan_mma.cu)
+bool gated_delta_scan_mma_supported(int dtype, int dk, int dv);
+int64_t gated_delta_scan_mma_scratch_bytes(int B, int T, int H);
+int gated_delta_scan_mma(const void* q, const void* k, const void* v, int dtype, const float* g, const float* beta,
+                         const float* initial_state, void* o, float* final_state, void* scratch, int B, int T, int H,
+                         int Hkv, int normalize_qk, float scale, cudaStream_t st);
+
 }  // namespace atma
 
 using namespace atma;
@@ -223,7 +230,9 @@ using namespace atma;
 extern "C" int64_t atma_gated_delta_scan_scratch_bytes(int B, int T, int H, int dk, int dv) {
   const int NC = (T + kScanC - 1) / kScanC;
   const ScanScratch lay{dk, dv};
-  return (int64_t)B * H * NC * lay.stride() * (int64_t)sizeof(float);
+  const int64_t fp32_path = (int64_t)B * H * NC * lay.stride() * (int64_t)sizeof(float);
+  const int64_t mma_path = gated_delta_scan_mma_scratch_bytes(B, T, H);
+  return fp32_path > mma_path ? fp32_path : mma_path;
 }
 
 extern "C" int atma_gated_delta_scan(const void* q, const void* k, const void* v, int dtype,
@@ -246,6 +255,10 @@ extern "C" int atma_gated_delta_scan(const void* q, const void* k, const void* v
       ATMA_CUDA_OK(cudaMemsetAsync(final_state, 0, sizeof(float) * (size_t)B * H * dk * dv, st));
     return ATMA_OK;
   }
+  if (gated_delta_scan_mma_supported(dtype, dk, dv) && ((uintptr_t)q % 16 == 0) && ((uintptr_t)k % 16 == 0) &&
+      ((uintptr_t)v % 16 == 0) && ((uintptr_t)scratch % 256 == 0))
+    return gated_delta_scan_mma(q, k, v, dtype, g, beta, initial_state, o, final_state, scratch, B, T, H, Hkv,
+                                normalize_qk, scale, st);
   const int NC = (T + kScanC - 1) / kScanC;
   const int ldq = (dk > dv ? dk : dv) + 1;
   const size_t smem1 = sizeof(float) * ((size_t)kScanC * (dk + 1) + (size_t)kScanC * ldq +

@@ -1,0 +1,477 @@
+// Gated-delta chunked scan for 16-bit inputs, d_k = d_v = 128, chunk = 64: tensor-core version.
+//
+// Same factorisation as the fp32 kernel (gated_delta_scan.cu):
+//   per chunk, independent of the state:  -W = -T diag(beta g) K,  U0 = T diag(beta) V,
+//       Qg = diag(g) Q,  Kt = diag(g_C/g) K,  Rq = tril((g_p/g_s) q_p.k_s),  T = (I + A)^-1
+//   per chunk, on the state S [dk][dv]:    U = U0 - W S;  O = Qg S + Rq U;  S <- g_C S + Kt^T U
+// Kernel A (one CTA per chunk) forms K K^T and Q K^T with mma.sync, inverts the unit lower
+// triangular 64x64 system in fp32 (16x16 diagonal blocks by substitution, then two levels of
+// block merges), and forms W and U0 with mma.sync; all factors go to scratch as 16-bit tiles.
+// Kernel B (one CTA per (sequence, head, 64-column half of S)) walks the chunks in order: the
+// fp32 state lives in the mma accumulators of its 4 warps for the whole sequence, a 16-bit copy
+// in shared memory serves as the B operand of the two state products, and the per-chunk factors
+// stream in through a 2-stage cp.async ring.  The recurrence is latency-bound, which is why it
+// uses warp-level mma (operands and results stay in the issuing warp's registers) rather than
+// the asynchronous tcgen05 path.
+#include "common.cuh"
+#include "mma_sync.cuh"
+
+namespace atma {
+
+using namespace mma;
+
+namespace {
+
+constexpr int kC = 64, kD = 128;
+constexpr int kRecW = 0, kRecQg = kC * kD * 2, kRecKt = 2 * kC * kD * 2, kRecU0 = 3 * kC * kD * 2,
+              kRecRq = 4 * kC * kD * 2, kRecBytes = 4 * kC * kD * 2 + kC * kC * 2;    // 73,728 B per chunk
+
+// ------------------------------------------------------------------------------------------------
+// Kernel A: chunk-local factors
+// ------------------------------------------------------------------------------------------------
+template <bool kBf16>
+__global__ void __launch_bounds__(128)
+scan_local_mma_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ k, const uint16_t* __restrict__ v,
+                      const float* __restrict__ g, const float* __restrict__ beta, uint8_t* __restrict__ rec_base,
+                      float* __restrict__ gc_base, int Tlen, int H, int Hkv, int NC, int normalize_qk, float scale) {
+  extern __shared__ __align__(128) uint8_t sm[];
+  uint8_t* Ks = sm;                         // [64][128] 16-bit, swizzled
+  uint8_t* Qs = Ks + kC * kD * 2;
+  uint8_t* Vs = Qs + kC * kD * 2;
+  float* Af = reinterpret_cast<float*>(Vs + kC * kD * 2);      // [64][65]
+  float* Tf = Af + kC * 65;                                     // [64][65]
+  float* Mf = Tf + kC * 65;                                     // [32][33]
+  uint8_t* Tb = reinterpret_cast<uint8_t*>(Mf + 32 * 33);       // [64][64] 16-bit, swizzled
+  float* lg = reinterpret_cast<float*>(Tb + kC * kC * 2);       // [64] inclusive log decay
+  float* bt = lg + kC;                                          // [64] beta
+  float* kinv = bt + kC;                                        // [64]
+  float* qinv = kinv + kC;                                      // [64]
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int t0 = c * kC;
+  const int rows = min(kC, Tlen - t0);
+  const int hk = h / (H / Hkv);
+  uint8_t* rec = rec_base + (((int64_t)b * H + h) * NC + c) * (int64_t)kRecBytes;
+
+  // ---- stage K, Q, V rows (zero beyond the sequence end) -----------------------------------------
+  for (int i = tid; i < kC * 16; i += 128) {
+    const int r = i >> 4, ch = i & 15;
+    const bool ok = r < rows;
+    const int64_t tok = (int64_t)b * Tlen + t0 + (ok ? r : 0);
+    cp_async16(smem_u32(Ks) + tile_off(r, ch * 8, kD), k + (tok * Hkv + hk) * kD + ch * 8, ok);
+    cp_async16(smem_u32(Qs) + tile_off(r, ch * 8, kD), q + (tok * H + h) * kD + ch * 8, ok);
+    cp_async16(smem_u32(Vs) + tile_off(r, ch * 8, kD), v + (tok * Hkv + hk) * kD + ch * 8, ok);
+  }
+  cp_async_commit();
+  if (tid == 0) {
+    float run = 0.f;
+    for (int r = 0; r < kC; ++r) {
+      const int64_t gi = ((int64_t)b * Tlen + t0 + r) * H + h;
+      run += (r < rows) ? g[gi] : 0.f;
+      lg[r] = run;
+      bt[r] = (r < rows) ? beta[gi] : 0.f;
+    }
+    gc_base[((int64_t)b * H + h) * NC + c] = __expf(run);
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+
+  // ---- row norms: thread i handles row i%64 of K (i < 64) or Q ----------------------------------------
+  {
+    const int r = tid & 63;
+    const uint8_t* src = (tid < 64) ? Ks : Qs;
+    float ss = 0.f;
+#pragma unroll
+    for (int ch = 0; ch < 16; ++ch) {
+      const uint4 u = *reinterpret_cast<const uint4*>(src + tile_off(r, ch * 8, kD));
+      const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { const float2 f = unpack2<kBf16>(w4[e]); ss = fmaf(f.x, f.x, fmaf(f.y, f.y, ss)); }
+    }
+    const float inv = normalize_qk ? 1.0f / fmaxf(sqrtf(ss), 1e-12f) : 1.0f;
+    if (tid < 64) kinv[r] = inv; else qinv[r] = inv * scale;
+  }
+  __syncthreads();
+
+  // ---- K K^T and Q K^T for rows 16w..16w+15 (only key tiles at or below the diagonal) ---------------
+  {
+    float kk[8][4], qk[8][4];
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { kk[nt][e] = 0.f; qk[nt][e] = 0.f; }
+    int am, ak, bn, bk;
+    a_rowmajor_lane(lane, am, ak);
+    b_nk_lane(lane, bn, bk);
+    const int npairs = warp + 1;                                 // key-tile pairs 0..warp cover s <= 16w+15
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      uint32_t ak_[4], aq_[4];
+      ldsm_x4(smem_u32(Ks) + tile_off(16 * warp + am, 16 * ks + ak, kD), ak_);
+      ldsm_x4(smem_u32(Qs) + tile_off(16 * warp + am, 16 * ks + ak, kD), aq_);
+#pragma unroll
+      for (int pr = 0; pr < 4; ++pr) {
+        if (pr < npairs) {
+          uint32_t bf[4];
+          ldsm_x4(smem_u32(Ks) + tile_off(16 * pr + bn, 16 * ks + bk, kD), bf);
+          mma16816<kBf16>(kk[2 * pr], ak_, bf[0], bf[1]);
+          mma16816<kBf16>(kk[2 * pr + 1], ak_, bf[2], bf[3]);
+          mma16816<kBf16>(qk[2 * pr], aq_, bf[0], bf[1]);
+          mma16816<kBf16>(qk[2 * pr + 1], aq_, bf[2], bf[3]);
+        }
+      }
+    }
+    // decay ratios, masks; A -> smem fp32, Rq -> scratch (16-bit)
+    uint16_t* rq_out = reinterpret_cast<uint16_t*>(rec + kRecRq);
+    const int gq = lane >> 2, tq = lane & 3;
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int p = 16 * warp + gq + 8 * half;
+        float a2[2], r2[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int s = 8 * nt + 2 * tq + e;
+          float av = 0.f, rv = 0.f;
+          if (s <= p) {
+            const float ratio = __expf(lg[p] - lg[s]);
+            rv = ratio * qk[nt][2 * half + e] * qinv[p] * kinv[s];
+            if (s < p) av = bt[p] * ratio * kk[nt][2 * half + e] * kinv[p] * kinv[s];
+          }
+          a2[e] = av; r2[e] = rv;
+          Af[p * 65 + s] = av;
+        }
+        *reinterpret_cast<uint32_t*>(rq_out + p * kC + 8 * nt + 2 * tq) = pack2<kBf16>(r2[0], r2[1]);
+      }
+    }
+  }
+  __syncthreads();
+
+  // ---- T = (I + A)^-1, fp32 -------------------------------------------------------------------------
+  for (int i = tid; i < kC * kC; i += 128) Tf[(i >> 6) * 65 + (i & 63)] = 0.f;
+  __syncthreads();
+  if (tid < 64) {                                               // 16x16 diagonal blocks by substitution
+    const int blk = tid >> 4, j = tid & 15;
+    float x[16];
+#pragma unroll
+    for (int p = 0; p < 16; ++p) {
+      float acc = (p == j) ? 1.f : 0.f;
+#pragma unroll
+      for (int s = 0; s < p; ++s) acc = fmaf(-Af[(16 * blk + p) * 65 + 16 * blk + s], x[s], acc);
+      x[p] = acc;
+      Tf[(16 * blk + p) * 65 + 16 * blk + j] = acc;
+    }
+  }
+  __syncthreads();
+  // merge: for a block matrix [[A11,0],[A21,A22]], T21 = -T22 (A21 T11)
+  for (int level = 0; level < 2; ++level) {
+    const int n = 16 << level;                                  // size of the diagonal blocks being merged
+    const int groups = kC / (2 * n);
+    for (int i = tid; i < groups * n * n; i += 128) {           // M = A21 T11
+      const int gidx = i / (n * n), rr = (i / n) % n, cc = i % n;
+      const int base = gidx * 2 * n;
+      float acc = 0.f;
+      for (int s = cc; s < n; ++s) acc = fmaf(Af[(base + n + rr) * 65 + base + s], Tf[(base + s) * 65 + base + cc], acc);
+      Mf[(gidx * n + rr) * 33 + cc] = acc;
+    }
+    __syncthreads();
+    for (int i = tid; i < groups * n * n; i += 128) {           // T21 = -T22 M
+      const int gidx = i / (n * n), rr = (i / n) % n, cc = i % n;
+      const int base = gidx * 2 * n;
+      float acc = 0.f;
+      for (int s = 0; s <= rr; ++s) acc = fmaf(Tf[(base + n + rr) * 65 + base + n + s], Mf[(gidx * n + s) * 33 + cc], acc);
+      Tf[(base + n + rr) * 65 + base + cc] = -acc;
+    }
+    __syncthreads();
+  }
+  for (int i = tid; i < kC * kC / 2; i += 128) {                // 16-bit copy of T (A operand)
+    const int p = i >> 5, s = (i & 31) * 2;
+    *reinterpret_cast<uint32_t*>(Tb + tile_off(p, s, kC)) = pack2<kBf16>(Tf[p * 65 + s], Tf[p * 65 + s + 1]);
+  }
+
+  // ---- emit Qg and Kt; turn K into -beta g K and V into beta V in place (B operands) -----------------
+  {
+    const float lgC = lg[kC - 1];
+    uint4* qg_out = reinterpret_cast<uint4*>(rec + kRecQg);
+    uint4* kt_out = reinterpret_cast<uint4*>(rec + kRecKt);
+    for (int i = tid; i < kC * 16; i += 128) {
+      const int r = i >> 4, ch = i & 15;
+      const float eg = __expf(lg[r]);
+      const float sq = eg * qinv[r], sk = __expf(lgC - lg[r]) * kinv[r];
+      const float sbk = -bt[r] * eg * kinv[r], sbv = bt[r];
+      uint4 uq = *reinterpret_cast<const uint4*>(Qs + tile_off(r, ch * 8, kD));
+      uint4* pk = reinterpret_cast<uint4*>(Ks + tile_off(r, ch * 8, kD));
+      uint4* pv = reinterpret_cast<uint4*>(Vs + tile_off(r, ch * 8, kD));
+      uint4 uk = *pk, uv = *pv, oq, okt, obk, obv;
+      const uint32_t *wq = &uq.x, *wk = &uk.x, *wv = &uv.x;
+      uint32_t *xq = &oq.x, *xkt = &okt.x, *xbk = &obk.x, *xbv = &obv.x;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 fq = unpack2<kBf16>(wq[e]), fk = unpack2<kBf16>(wk[e]), fv = unpack2<kBf16>(wv[e]);
+        xq[e] = pack2<kBf16>(fq.x * sq, fq.y * sq);
+        xkt[e] = pack2<kBf16>(fk.x * sk, fk.y * sk);
+        xbk[e] = pack2<kBf16>(fk.x * sbk, fk.y * sbk);
+        xbv[e] = pack2<kBf16>(fv.x * sbv, fv.y * sbv);
+      }
+      qg_out[i] = oq; kt_out[i] = okt;
+      *pk = obk; *pv = obv;
+    }
+  }
+  __syncthreads();
+
+  // ---- -W = T (-beta g K) and U0 = T (beta V): rows 16w.., k-steps 0..w (T is lower triangular) -------
+  {
+    int am, ak, bk, bn;
+    a_rowmajor_lane(lane, am, ak);
+    b_kn_lane(lane, bk, bn);
+    const int gq = lane >> 2, tq = lane & 3;
+#pragma unroll 1
+    for (int which = 0; which < 2; ++which) {
+      const uint8_t* Bs = which ? Vs : Ks;
+      float acc[16][4];
+#pragma unroll
+      for (int nt = 0; nt < 16; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[nt][e] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) {
+        if (ks <= warp) {
+          uint32_t af[4];
+          ldsm_x4(smem_u32(Tb) + tile_off(16 * warp + am, 16 * ks + ak, kC), af);
+#pragma unroll
+          for (int pr = 0; pr < 8; ++pr) {
+            uint32_t bf[4];
+            ldsm_x4_trans(smem_u32(Bs) + tile_off(16 * ks + bk, 16 * pr + bn, kD), bf);
+            mma16816<kBf16>(acc[2 * pr], af, bf[0], bf[1]);
+            mma16816<kBf16>(acc[2 * pr + 1], af, bf[2], bf[3]);
+          }
+        }
+      }
+      uint16_t* out = reinterpret_cast<uint16_t*>(rec + (which ? kRecU0 : kRecW));
+#pragma unroll
+      for (int nt = 0; nt < 16; ++nt) {
+        *reinterpret_cast<uint32_t*>(out + (16 * warp + gq) * kD + 8 * nt + 2 * tq) = pack2<kBf16>(acc[nt][0], acc[nt][1]);
+        *reinterpret_cast<uint32_t*>(out + (16 * warp + gq + 8) * kD + 8 * nt + 2 * tq) = pack2<kBf16>(acc[nt][2], acc[nt][3]);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Kernel B: the recurrence over chunks
+// ------------------------------------------------------------------------------------------------
+constexpr int kStageBytes = 3 * kC * kD * 2 + kC * 64 * 2 + kC * kC * 2;      // W, Qg, Kt, U0 half, Rq = 65,536 B
+constexpr int kSeqSmem = 2 * kStageBytes + kD * 64 * 2 + kC * 64 * 2;         // + S copy + U copy = 155,648 B
+
+template <bool kBf16>
+__global__ void __launch_bounds__(128)
+scan_seq_mma_kernel(const uint8_t* __restrict__ rec_base, const float* __restrict__ gc_base,
+                    const float* __restrict__ initial_state, uint16_t* __restrict__ o,
+                    float* __restrict__ final_state, int Tlen, int H, int NC) {
+  extern __shared__ __align__(128) uint8_t sm[];
+  uint8_t* Sb = sm + 2 * kStageBytes;                // [128 k][64 v] 16-bit, swizzled (rows of 128 B)
+  uint8_t* Ub = Sb + kD * 64 * 2;                    // [64 s][64 v]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int half = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int gq = lane >> 2, tq = lane & 3;
+  const uint8_t* recs = rec_base + ((int64_t)b * H + h) * NC * (int64_t)kRecBytes;
+  const float* gcs = gc_base + ((int64_t)b * H + h) * NC;
+
+  auto stage_ptr = [&](int s) { return sm + s * kStageBytes; };
+  auto load_stage = [&](int c, int s) {
+    const uint8_t* rec = recs + (int64_t)c * kRecBytes;
+    uint8_t* dst = stage_ptr(s);
+    for (int i = tid; i < 3 * kC * 16; i += 128) {             // W, Qg, Kt: three [64][128] tiles
+      const int tile = i / (kC * 16), r = (i >> 4) & 63, ch = i & 15;
+      cp_async16(smem_u32(dst) + tile * (kC * kD * 2) + tile_off(r, ch * 8, kD), rec + tile * (kC * kD * 2) + r * 256 + ch * 16, true);
+    }
+    for (int i = tid; i < kC * 8; i += 128) {                  // U0 columns [64*half, +64), Rq
+      const int r = i >> 3, ch = i & 7;
+      cp_async16(smem_u32(dst) + 3 * kC * kD * 2 + tile_off(r, ch * 8, 64), rec + kRecU0 + r * 256 + half * 128 + ch * 16, true);
+      cp_async16(smem_u32(dst) + 3 * kC * kD * 2 + kC * 64 * 2 + tile_off(r, ch * 8, 64), rec + kRecRq + r * 128 + ch * 16, true);
+    }
+  };
+
+  // fp32 state: warp w owns rows k = 32w .. 32w+31 (two 16-row tiles) x 64 columns
+  float S[2][8][4];
+  const int64_t sbase = ((int64_t)b * H + h) * kD * kD + half * 64;
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        const int kr = 32 * warp + 16 * mt + gq + 8 * hh, col = 8 * nt + 2 * tq;
+        float2 v2 = make_float2(0.f, 0.f);
+        if (initial_state) v2 = *reinterpret_cast<const float2*>(initial_state + sbase + (int64_t)kr * kD + col);
+        S[mt][nt][2 * hh] = v2.x; S[mt][nt][2 * hh + 1] = v2.y;
+        *reinterpret_cast<uint32_t*>(Sb + tile_off(kr, col, 64)) = pack2<kBf16>(v2.x, v2.y);
+      }
+  load_stage(0, 0);
+  cp_async_commit();
+
+  int am, ak, bk, bn, tk, tm;
+  a_rowmajor_lane(lane, am, ak);
+  b_kn_lane(lane, bk, bn);
+  a_km_lane(lane, tk, tm);
+
+  for (int c = 0; c < NC; ++c) {
+    const int s = c & 1;
+    if (c + 1 < NC) load_stage(c + 1, s ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();                                           // stage s landed; Sb from the previous chunk visible
+    const uint32_t Wsm = smem_u32(stage_ptr(s)), Qsm = Wsm + kC * kD * 2, Ksm = Qsm + kC * kD * 2;
+    const uint8_t* U0s = stage_ptr(s) + 3 * kC * kD * 2;
+    const uint32_t Rsm = Wsm + 3 * kC * kD * 2 + kC * 64 * 2;
+    const float gC = gcs[c];
+
+    // U = U0 - W S ; O = Qg S   (rows 16w..16w+15 of the chunk)
+    float U[8][4], O[8][4];
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        const float2 u2 = unpack2<kBf16>(*reinterpret_cast<const uint32_t*>(U0s + tile_off(16 * warp + gq + 8 * hh, 8 * nt + 2 * tq, 64)));
+        U[nt][2 * hh] = u2.x; U[nt][2 * hh + 1] = u2.y;
+        O[nt][2 * hh] = 0.f; O[nt][2 * hh + 1] = 0.f;
+      }
+    }
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      uint32_t aw[4], aq[4];
+      ldsm_x4(Wsm + tile_off(16 * warp + am, 16 * ks + ak, kD), aw);
+      ldsm_x4(Qsm + tile_off(16 * warp + am, 16 * ks + ak, kD), aq);
+#pragma unroll
+      for (int pr = 0; pr < 4; ++pr) {
+        uint32_t bf[4];
+        ldsm_x4_trans(smem_u32(Sb) + tile_off(16 * ks + bk, 16 * pr + bn, 64), bf);
+        mma16816<kBf16>(U[2 * pr], aw, bf[0], bf[1]);
+        mma16816<kBf16>(U[2 * pr + 1], aw, bf[2], bf[3]);
+        mma16816<kBf16>(O[2 * pr], aq, bf[0], bf[1]);
+        mma16816<kBf16>(O[2 * pr + 1], aq, bf[2], bf[3]);
+      }
+    }
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+      *reinterpret_cast<uint32_t*>(Ub + tile_off(16 * warp + gq, 8 * nt + 2 * tq, 64)) = pack2<kBf16>(U[nt][0], U[nt][1]);
+      *reinterpret_cast<uint32_t*>(Ub + tile_off(16 * warp + gq + 8, 8 * nt + 2 * tq, 64)) = pack2<kBf16>(U[nt][2], U[nt][3]);
+    }
+    __syncthreads();                                           // U of every warp visible; all reads of Sb done
+
+    // O += Rq U  (s <= 16w+15 -> k-steps 0..w) and store
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+      if (ks <= warp) {
+        uint32_t ar[4];
+        ldsm_x4(Rsm + tile_off(16 * warp + am, 16 * ks + ak, 64), ar);
+#pragma unroll
+        for (int pr = 0; pr < 4; ++pr) {
+          uint32_t bf[4];
+          ldsm_x4_trans(smem_u32(Ub) + tile_off(16 * ks + bk, 16 * pr + bn, 64), bf);
+          mma16816<kBf16>(O[2 * pr], ar, bf[0], bf[1]);
+          mma16816<kBf16>(O[2 * pr + 1], ar, bf[2], bf[3]);
+        }
+      }
+    }
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      const int t = c * kC + 16 * warp + gq + 8 * hh;
+      if (t < Tlen) {
+        uint16_t* orow = o + (((int64_t)b * Tlen + t) * H + h) * kD + half * 64;
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt)
+          *reinterpret_cast<uint32_t*>(orow + 8 * nt + 2 * tq) = pack2<kBf16>(O[nt][2 * hh], O[nt][2 * hh + 1]);
+      }
+    }
+
+    // S <- gC S + Kt^T U   (rows k = 32w.., A = Kt^T from the [s][k] tile with a transposing load)
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) S[mt][nt][e] *= gC;
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+      uint32_t bfr[4][4];
+#pragma unroll
+      for (int pr = 0; pr < 4; ++pr) ldsm_x4_trans(smem_u32(Ub) + tile_off(16 * ks + bk, 16 * pr + bn, 64), bfr[pr]);
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) {
+        uint32_t at[4];
+        ldsm_x4_trans(Ksm + tile_off(16 * ks + tk, 32 * warp + 16 * mt + tm, kD), at);
+#pragma unroll
+        for (int pr = 0; pr < 4; ++pr) {
+          mma16816<kBf16>(S[mt][2 * pr], at, bfr[pr][0], bfr[pr][1]);
+          mma16816<kBf16>(S[mt][2 * pr + 1], at, bfr[pr][2], bfr[pr][3]);
+        }
+      }
+    }
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh)
+          *reinterpret_cast<uint32_t*>(Sb + tile_off(32 * warp + 16 * mt + gq + 8 * hh, 8 * nt + 2 * tq, 64)) =
+              pack2<kBf16>(S[mt][nt][2 * hh], S[mt][nt][2 * hh + 1]);
+    __syncthreads();                                           // stage s and Ub free; new Sb complete
+  }
+  cp_async_wait<0>();
+  if (final_state) {
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          const int kr = 32 * warp + 16 * mt + gq + 8 * hh, col = 8 * nt + 2 * tq;
+          *reinterpret_cast<float2*>(final_state + sbase + (int64_t)kr * kD + col) =
+              make_float2(S[mt][nt][2 * hh], S[mt][nt][2 * hh + 1]);
+        }
+  }
+}
+
+}  // namespace
+
+bool gated_delta_scan_mma_supported(int dtype, int dk, int dv) {
+  return (dtype == ATMA_BF16 || dtype == ATMA_F16) && dk == kD && dv == kD;
+}
+
+int64_t gated_delta_scan_mma_scratch_bytes(int B, int T, int H) {
+  const int64_t NC = (T + kC - 1) / kC;
+  return (int64_t)B * H * NC * kRecBytes + (int64_t)B * H * NC * sizeof(float) + 256;
+}
+
+int gated_delta_scan_mma(const void* q, const void* k, const void* v, int dtype, const float* g, const float* beta,
+                         const float* initial_state, void* o, float* final_state, void* scratch, int B, int T, int H,
+                         int Hkv, int normalize_qk, float scale, cudaStream_t st) {
+  const int NC = (T + kC - 1) / kC;
+  uint8_t* recs = static_cast<uint8_t*>(scratch);
+  float* gcs = reinterpret_cast<float*>(recs + (((int64_t)B * H * NC * kRecBytes + 255) / 256) * 256);
+  const int smemA = 3 * kC * kD * 2 + (2 * kC * 65 + 32 * 33) * 4 + kC * kC * 2 + 4 * kC * 4;
+  const bool bf = dtype == ATMA_BF16;
+  if (bf) {
+    ATMA_CUDA_OK(cudaFuncSetAttribute(scan_local_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smemA));
+    ATMA_CUDA_OK(cudaFuncSetAttribute(scan_seq_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSeqSmem));
+    scan_local_mma_kernel<true><<<dim3(NC, H, B), 128, smemA, st>>>((const uint16_t*)q, (const uint16_t*)k, (const uint16_t*)v, g,
+                                                                   beta, recs, gcs, T, H, Hkv, NC, normalize_qk, scale);
+  } else {
+    ATMA_CUDA_OK(cudaFuncSetAttribute(scan_local_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smemA));
+    ATMA_CUDA_OK(cudaFuncSetAttribute(scan_seq_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSeqSmem));
+    scan_local_mma_kernel<false><<<dim3(NC, H, B), 128, smemA, st>>>((const uint16_t*)q, (const uint16_t*)k, (const uint16_t*)v, g,
+                                                                    beta, recs, gcs, T, H, Hkv, NC, normalize_qk, scale);
+  }
+  int rc = launch_status("gated_delta_scan (chunk-local, mma)");
+  if (rc != ATMA_OK) return rc;
+  if (bf)
+    scan_seq_mma_kernel<true><<<dim3(2, H, B), 128, kSeqSmem, st>>>(recs, gcs, initial_state, (uint16_t*)o, final_state, T, H, NC);
+  else
+    scan_seq_mma_kernel<false><<<dim3(2, H, B), 128, kSeqSmem, st>>>(recs, gcs, initial_state, (uint16_t*)o, final_state, T, H, NC);
+  return launch_status("gated_delta_scan (recurrence, mma)");
+}
+
+}  // namespace atma
