@@ -300,10 +300,22 @@ __global__ void polar_decode_merge_kernel(const float* __restrict__ scratch,
   }
 }
 
+// tensor-core split kernel for 16-bit caches (polar_decode_mma.cu)
+bool polar_decode_mma_supported(const atma_polar_decode_args& a);
+int polar_decode_split_mma(const atma_polar_decode_args& a, cudaStream_t st);
+
 template <typename T>
 int launch_decode(const atma_polar_decode_args& a, cudaStream_t st) {
   dim3 grid(a.n_splits, a.Hkv, a.B), block(kDecWarps * 32);
   const int G = a.H / a.Hkv;
+  if (polar_decode_mma_supported(a)) {
+    int rc = polar_decode_split_mma(a, st);
+    if (rc != ATMA_OK) return rc;
+    polar_decode_merge_kernel<T><<<a.B * a.H, 64, 0, st>>>(
+        a.scratch, a.context_lens, a.v_null, a.spg, a.null_base, a.sps, a.beta, (T*)a.c, (T*)a.mag,
+        a.B, a.H, a.dk, a.n_splits, a.window, a.max_blocks * a.block_size, a.eps);
+    return launch_status("polar_decode (merge)");
+  }
 #define ATMA_LAUNCH(DKK, GM)                                                                    \
   polar_decode_split_kernel<T, DKK, GM><<<grid, block, 0, st>>>(                                \
       (const T*)a.q, (const T*)a.k_cache, (const T*)a.v_cache, a.block_tables, a.bt_stride,     \
@@ -341,7 +353,8 @@ extern "C" int atma_polar_decode(const atma_polar_decode_args* args, void* strea
   const atma_polar_decode_args& a = *args;
   ATMA_REQUIRE(dtype_ok(a.dtype), "polar_decode: unsupported dtype %d", a.dtype);
   ATMA_REQUIRE(a.Hkv > 0 && a.H % a.Hkv == 0, "polar_decode: H=%d not a multiple of Hkv=%d", a.H, a.Hkv);
-  ATMA_REQUIRE(a.H / a.Hkv <= kDecMaxG, "polar_decode: GQA group size %d > %d", a.H / a.Hkv, kDecMaxG);
+  ATMA_REQUIRE(a.H / a.Hkv <= kDecMaxG || polar_decode_mma_supported(a),
+               "polar_decode: GQA group size %d > %d", a.H / a.Hkv, kDecMaxG);
   ATMA_REQUIRE(a.n_splits >= 1 && a.n_splits <= 1024, "polar_decode: n_splits=%d", a.n_splits);
   ATMA_REQUIRE(a.block_size > 0 && a.max_blocks > 0 && a.num_blocks > 0, "polar_decode: empty cache geometry");
   ATMA_REQUIRE(a.scratch != nullptr, "polar_decode: scratch is required");
