@@ -9,8 +9,11 @@
 //
 //   warp 0      TMA producer: Q tiles once, then K and V tiles through 2-stage rings
 //   warp 1      MMA issuer (one lane): S_t = Q_t K_j^T (SS), O_t += P_t V_j (P read from TMEM)
-//   warps 2-5   softmax + epilogue of tile 0, one thread per query row (= one TMEM lane)
-//   warps 6-9   softmax + epilogue of tile 1
+//   warps 2-3   idle (they complete the first warpgroup, whose registers are handed over)
+//   warps 4-7   softmax + epilogue of tile 0, one thread per query row (= one TMEM lane)
+//   warps 8-11  softmax + epilogue of tile 1
+// The first warpgroup shrinks to 40 registers per thread (setmaxnreg) so that each softmax
+// thread can hold its whole 128-column S row in registers.
 //
 // TMEM (512 columns): S_0 [0,128) S_1 [128,256) O_0 [256,384) O_1 [384,512); P_t (16-bit,
 // two values per column) overwrites the first 64 columns of S_t once the row has been read.
@@ -32,7 +35,7 @@ namespace {
 constexpr int kBM = 128, kBN = 128, kDK = 128;
 constexpr int kStages = 2;
 constexpr int kTileBytes = kBM * kDK * 2;             // 32 KiB: two 64-column swizzled boxes
-constexpr int kThreads = 320;
+constexpr int kThreads = 384;                        // 3 warpgroups: (TMA, MMA, 2 idle) + 2 x softmax
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kNegInit = -1.0e30f;                  // "no key seen yet" in the log2 domain
@@ -157,12 +160,12 @@ polar_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
   }
 
   // ---- per-row scalars (softmax threads) and the key range of each tile ---------------------------
-  const int sm_tile = (warp >= 6) ? 1 : 0;             // meaningful for warps >= 2
+  const int sm_tile = (warp >= 8) ? 1 : 0;             // meaningful for warps >= 4
   const int r_in_tile = 32 * (warp & 3) + lane;        // TMEM lane of this thread
   float n_i = 0.f;
   bool row_ok = false;
   int my_row = 0;
-  if (warp >= 2) {
+  if (warp >= 4) {
     my_row = (sm_tile ? row0[1] : row0[0]) + r_in_tile;
     row_ok = my_row < q_limit;
     if (row_ok) n_i = packed ? (float)(my_row + 1) : (p.n_keys ? p.n_keys[my_row] : p.n_base + (float)(my_row + 1));
@@ -205,6 +208,8 @@ polar_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
   auto active = [&](int t, int j) { return t ? (j >= lo[1] && j < hi[1]) : (j >= lo[0] && j < hi[0]); };
   volatile int* abort_flag = &s_abort;
 
+  if (warp < 4) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
   if (warp == 0) {
     // =============================== TMA producer ================================================
     if (lane == 0) {
@@ -234,20 +239,27 @@ polar_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
       constexpr uint32_t idesc_pv = make_idesc(kBM, kDK, kBf16 ? 1 : 0, 0, 1);
       const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
       bool ok = true;
+      // Descriptors are rebuilt from the loop counter inside rolled loops: one thread issues an
+      // MMA every ~64 tensor cycles, so a few integer instructions per MMA cost nothing, while
+      // unrolled loops would keep dozens of loop-invariant 64-bit descriptors in registers.
+      const uint64_t desc_hi_k = (uint64_t(1024 >> 4) << 32) | (uint64_t(1) << 46) | (uint64_t(2) << 61) | (uint64_t(16 >> 4) << 16);
+      const uint64_t desc_hi_v = (uint64_t(1024 >> 4) << 32) | (uint64_t(1) << 46) | (uint64_t(2) << 61) |
+                                 (uint64_t((kTileBytes / 2) >> 4) << 16);
       auto issue_qk = [&](int t, int s) {
-#pragma unroll
+        const uint32_t qa = (q_addr + t * kTileBytes) >> 4, ka = (k_addr + s * kTileBytes) >> 4;
+#pragma unroll 1
         for (int kk = 0; kk < kDK / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * (kTileBytes / 2) + (kk & 3) * 32;
-          mma_ss(tbase + t * 128, make_sdesc_sw128(q_addr + t * kTileBytes + off, 16, 1024),
-                 make_sdesc_sw128(k_addr + s * kTileBytes + off, 16, 1024), idesc_qk, kk > 0);
+          const uint32_t off = ((kk >> 2) * (kTileBytes / 2) + (kk & 3) * 32) >> 4;
+          mma_ss(tbase + t * 128, desc_hi_k | uint64_t((qa + off) & 0x3FFFu), desc_hi_k | uint64_t((ka + off) & 0x3FFFu),
+                 idesc_qk, kk > 0);
         }
       };
       auto issue_pv = [&](int t, int s, bool acc) {
-#pragma unroll
+        const uint32_t va = (v_addr + s * kTileBytes) >> 4;
+#pragma unroll 1
         for (int kk = 0; kk < kBN / 16; ++kk)
-          mma_ts(tbase + 256 + t * 128, tbase + t * 128 + kk * 8,
-                 make_sdesc_sw128(v_addr + s * kTileBytes + kk * 2048, kTileBytes / 2, 1024), idesc_pv,
-                 (kk > 0 || acc) ? 1u : 0u);
+          mma_ts(tbase + 256 + t * 128, tbase + t * 128 + kk * 8, desc_hi_v | uint64_t((va + kk * (2048 >> 4)) & 0x3FFFu),
+                 idesc_pv, (kk > 0 || acc) ? 1u : 0u);
       };
       if (jmax > jmin) {
 #pragma unroll
@@ -296,7 +308,9 @@ polar_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
       }
     }
     __syncwarp();
+  }
   } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
     // =============================== softmax + epilogue ===========================================
     const int t = sm_tile;
     const int h = t ? head[1] : head[0];
@@ -341,32 +355,33 @@ polar_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
       const bool full = row_ok && c_hi >= (float)kBN && c_lo <= 0.0f;
       const float c_hi_eff = row_ok ? c_hi : 0.0f;
 
-      // pass 1: row maximum of the raw scores
-      float mx0 = -INFINITY, mx1 = -INFINITY;
-#pragma unroll 1
-      for (int ch = 0; ch < 4; ++ch) {
-        uint32_t r[32];
-        tmem_ld32(tS + ch * 32, r);
+      // the whole S row in registers: four loads in flight, one wait
+      uint32_t r[kBN];
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) tmem_ld32_nowait(tS + ch * 32, &r[ch * 32]);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < kBN; ++i) reg_fence(r[i]);
 #ifdef ATMA_SM100_DEBUG
-        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && j == my_lo)
-          for (int i = 0; i < 32; ++i) g_dbg_s[t][r_in_tile][ch * 32 + i] = __uint_as_float(r[i]);
+      if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && j == my_lo)
+        for (int i = 0; i < kBN; ++i) g_dbg_s[t][r_in_tile][i] = __uint_as_float(r[i]);
 #endif
-        if (full) {
+      if (!full) {                                                  // diagonal / window-edge / ragged tile
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            mx0 = fmaxf(mx0, __uint_as_float(r[i]));
-            mx1 = fmaxf(mx1, __uint_as_float(r[i + 1]));
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float cc = (float)(ch * 32 + i);
-            const float v = (cc >= c_lo && cc < c_hi_eff) ? __uint_as_float(r[i]) : -INFINITY;
-            mx0 = fmaxf(mx0, v);
-          }
+        for (int i = 0; i < kBN; ++i) {
+          const float cc = (float)i;
+          if (!(cc >= c_lo && cc < c_hi_eff)) r[i] = 0xff800000u;   // -inf
         }
       }
-      const float m_cand = fmaxf(mx0, mx1) * sc2;                   // -inf if nothing visible
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < kBN; i += 4) {
+        mx0 = fmaxf(mx0, __uint_as_float(r[i]));
+        mx1 = fmaxf(mx1, __uint_as_float(r[i + 1]));
+        mx2 = fmaxf(mx2, __uint_as_float(r[i + 2]));
+        mx3 = fmaxf(mx3, __uint_as_float(r[i + 3]));
+      }
+      const float m_cand = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sc2;   // -inf if nothing visible
       const float m_new = fmaxf(m_run, m_cand);
       m_run = m_new;
       if (__any_sync(0xffffffffu, (m_new - m_used) > kLazyThreshold)) {
@@ -375,32 +390,25 @@ polar_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
         if (o_live) {
 #pragma unroll 1
           for (int ch = 0; ch < 4; ++ch) {
-            uint32_t r[32];
-            tmem_ld32(tO + ch * 32, r);
+            uint32_t o[32];
+            tmem_ld32(tO + ch * 32, o);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st32(tO + ch * 32, r);
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st32(tO + ch * 32, o);
           }
         }
         m_used = m_new;
       }
-      // pass 2: p = 2^(s*sc2 - m_used), statistics, P tile (16-bit) over the S columns
+      // p = 2^(s*sc2 - m_used), statistics, P tile (16-bit) over the first 64 S columns
       const float neg_m = -m_used;
       float l0 = 0.f, l1 = 0.f, q0 = 0.f, q1 = 0.f;
-#pragma unroll 1
+#pragma unroll
       for (int ch = 0; ch < 4; ++ch) {
-        uint32_t r[32], pk[16];
-        tmem_ld32(tS + ch * 32, r);
+        uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float x0 = fmaf(__uint_as_float(r[i]), sc2, neg_m);
-          float x1 = fmaf(__uint_as_float(r[i + 1]), sc2, neg_m);
-          if (!full) {
-            const float c0 = (float)(ch * 32 + i), c1 = c0 + 1.0f;
-            if (!(c0 >= c_lo && c0 < c_hi_eff)) x0 = -INFINITY;
-            if (!(c1 >= c_lo && c1 < c_hi_eff)) x1 = -INFINITY;
-          }
-          const float p0 = ex2(x0), p1 = ex2(x1);
+          const float p0 = ex2(fmaf(__uint_as_float(r[ch * 32 + i]), sc2, neg_m));
+          const float p1 = ex2(fmaf(__uint_as_float(r[ch * 32 + i + 1]), sc2, neg_m));
           l0 += p0; l1 += p1;
           q0 = fmaf(p0, p0, q0); q1 = fmaf(p1, p1, q1);
           pk[i >> 1] = pack2<kBf16>(p0, p1);

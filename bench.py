@@ -255,6 +255,52 @@ def run_reference(args, rank):
     print(json.dumps(line))
 
 
+def profile_case(which):
+    """A small case of one kernel for an ncu capture: inputs larger than L2, well under 1 GB,
+    five launches.  Prints the shape so that per-launch figures can be scaled."""
+    import atma_b200 as ab
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(0)
+    if which == "prefill":
+        B, T = 1, 16384
+        q = torch.randn(B, T, H, DK, generator=g).bfloat16().to(dev)
+        k = torch.randn(B, T, HKV, DK, generator=g).bfloat16().to(dev)
+        v = torch.randn(B, T, HKV, DK, generator=g).bfloat16().to(dev)
+        n = torch.arange(1, T + 1, dtype=torch.float32, device=dev)
+        P = default_polar_params(dev)
+        for _ in range(5):
+            ab.polar_attention_fwd(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), n, **P)
+        info = {"kernel": "polar_prefill_sm100_kernel", "B": B, "T": T, "flops_per_launch": polar_flops(T)}
+    elif which == "decode":
+        Bd, ctx = 16, 16384
+        nblk = ctx // DEC_BLOCK
+        kc = torch.randn(Bd * nblk, DEC_BLOCK, HKV, DK, device=dev, dtype=torch.bfloat16)
+        vc = torch.randn(Bd * nblk, DEC_BLOCK, HKV, DK, device=dev, dtype=torch.bfloat16)
+        bt = torch.randperm(Bd * nblk, generator=g).int().view(Bd, nblk).to(dev)
+        cl = torch.full((Bd,), ctx, dtype=torch.int32, device=dev)
+        q = torch.randn(Bd, H, DK, device=dev, dtype=torch.bfloat16)
+        P = default_polar_params(dev)
+        for _ in range(5):
+            ab.polar_attention_decode(q, kc, vc, bt, cl, **P)
+        info = {"kernel": "polar_decode_split_mma_kernel", "B": Bd, "context": ctx,
+                "bytes_per_launch": 2.0 * Bd * ctx * HKV * DK * 2}
+    else:
+        B, T = 2, 16384
+        q = torch.randn(B, T, H, DK, generator=g).bfloat16().to(dev)
+        k = torch.randn(B, T, HKV, DK, generator=g).bfloat16().to(dev)
+        v = torch.randn(B, T, HKV, DK, generator=g).bfloat16().to(dev)
+        gl = (-F.softplus(torch.randn(B, T, H, generator=g))).to(dev)
+        be = torch.sigmoid(torch.randn(B, T, H, generator=g)).to(dev)
+        for _ in range(5):
+            ab.chunk_gated_delta_rule(q=q, k=k, v=v, g=gl, beta=be, scale=1.0, output_final_state=True,
+                                      use_qk_l2norm_in_kernel=True)
+        info = {"kernel": "scan_local_mma_kernel + scan_seq_mma_kernel", "B": B, "T": T,
+                "flops_per_launch": scan_flops(T) * B}
+    torch.cuda.synchronize()
+    print(json.dumps({"profile": which, **info}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -263,12 +309,18 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline leg (profiling runs)")
     ap.add_argument("--skip-decode", action="store_true", help="omit the decode leg (profiling runs)")
+    ap.add_argument("--profile", default=None, choices=["prefill", "decode", "scan"],
+                    help="run a few launches of ONE kernel on a small case (a few hundred MB, larger than L2) "
+                         "and exit; meant to be wrapped in ncu")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.profile:
+        profile_case(args.profile)
         return
     args.warmup = max(args.warmup, 3)
 
