@@ -97,6 +97,12 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 template <bool kBf16>
 __global__ void __launch_bounds__(kThreads, 1)
 polar_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -375,11 +381,11 @@ polar_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
       }
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < kBN; i += 4) {
-        mx0 = fmaxf(mx0, __uint_as_float(r[i]));
-        mx1 = fmaxf(mx1, __uint_as_float(r[i + 1]));
-        mx2 = fmaxf(mx2, __uint_as_float(r[i + 2]));
-        mx3 = fmaxf(mx3, __uint_as_float(r[i + 3]));
+      for (int i = 0; i < kBN; i += 8) {
+        mx0 = max3(mx0, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+        mx1 = max3(mx1, __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+        mx2 = max3(mx2, __uint_as_float(r[i + 4]), __uint_as_float(r[i + 5]));
+        mx3 = max3(mx3, __uint_as_float(r[i + 6]), __uint_as_float(r[i + 7]));
       }
       const float m_cand = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sc2;   // -inf if nothing visible
       const float m_new = fmaxf(m_run, m_cand);
@@ -401,20 +407,27 @@ polar_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
       }
       // p = 2^(s*sc2 - m_used), statistics, P tile (16-bit) over the first 64 S columns
       const float neg_m = -m_used;
-      float l0 = 0.f, l1 = 0.f, q0 = 0.f, q1 = 0.f;
+      // Two columns per instruction with the packed fp32x2 FMA/ADD of sm_100: per pair of
+      // elements one FFMA2 (exponent argument), two ex2, one FADD2 (L), one FFMA2 (Q2), one pack.
+      const float2 sc2v = make_float2(sc2, sc2), negv = make_float2(neg_m, neg_m);
+      float2 la = make_float2(0.f, 0.f), lb = la, qa = la, qb = la;
 #pragma unroll
       for (int ch = 0; ch < 4; ++ch) {
         uint32_t pk[16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float p0 = ex2(fmaf(__uint_as_float(r[ch * 32 + i]), sc2, neg_m));
-          const float p1 = ex2(fmaf(__uint_as_float(r[ch * 32 + i + 1]), sc2, neg_m));
-          l0 += p0; l1 += p1;
-          q0 = fmaf(p0, p0, q0); q1 = fmaf(p1, p1, q1);
-          pk[i >> 1] = pack2<kBf16>(p0, p1);
+        for (int i = 0; i < 32; i += 4) {
+          const float2 x0 = __ffma2_rn(make_float2(__uint_as_float(r[ch * 32 + i]), __uint_as_float(r[ch * 32 + i + 1])), sc2v, negv);
+          const float2 x1 = __ffma2_rn(make_float2(__uint_as_float(r[ch * 32 + i + 2]), __uint_as_float(r[ch * 32 + i + 3])), sc2v, negv);
+          const float2 p0 = make_float2(ex2(x0.x), ex2(x0.y));
+          const float2 p1 = make_float2(ex2(x1.x), ex2(x1.y));
+          la = __fadd2_rn(la, p0); lb = __fadd2_rn(lb, p1);
+          qa = __ffma2_rn(p0, p0, qa); qb = __ffma2_rn(p1, p1, qb);
+          pk[i >> 1] = pack2<kBf16>(p0.x, p0.y);
+          pk[(i >> 1) + 1] = pack2<kBf16>(p1.x, p1.y);
         }
         tmem_st16(tS + ch * 16, pk);
       }
+      const float l0 = la.x + la.y, l1 = lb.x + lb.y, q0 = qa.x + qa.y, q1 = qb.x + qb.y;
       L += l0 + l1; Q2 += q0 + q1;
       tmem_st_wait();
       tc_fence_before();
