@@ -1,0 +1,246 @@
+"""Context-parallel prefill of one global layer's mixing across the GPUs of one box.
+
+The reference runs prefill on one GPU only; its chunked-prefill continuation
+(inference/models/atma.py:509-544) is the single-device statement of what a sequence split
+must reproduce: queries of a later segment attend to all earlier K/V with absolute key
+counts, the memory starts from the previous segment's final state, a conv starts from the
+previous segment's last K-1 inputs.  This module shards ONE sequence over the ranks of a
+``torch.distributed`` group:
+
+* the sequence is cut into 2N equal segments and rank r owns segments r and 2N-1-r
+  ("zig-zag"), which balances the causal triangle;
+* **Polar**: every rank keeps its queries; the un-expanded K/V blocks travel a ring
+  (NCCL send/recv into local buffers, double-buffered, overlapped with the tile kernel of
+  the current block).  Per received block the prefill kernel runs with absolute key offsets
+  and carries its running statistics (m, L, Q2, S) to the next step; the null sink is folded
+  on the last block a query segment sees;
+* **gated-delta memory**: a segment acts on the state as an affine map S_out = P S_in + Qm.
+  Each rank gets (P, Qm) of both of its segments from one batched scan (the P rows use v = 0
+  and the identity as initial state), an all-gather shares the 2N pairs (1 MB each at the
+  model's shape), the prefix is composed locally in fp32, and a second batched scan produces
+  the outputs from the true incoming states;
+* **depthwise conv**: a K-1 row halo from the previous segment's owner.
+
+The compute kernels are injected through a small backend object so that the routing can be
+exercised on CPU ranks (gloo) against the oracle; the default backend is the CUDA library.
+"""
+
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+
+def zigzag_segments(total, world):
+    """[(start, end)] of the two segments rank r owns, for every r.  ``total`` must divide by 2N."""
+    if total % (2 * world) != 0:
+        raise ValueError(f"sequence length {total} must be a multiple of 2*world = {2 * world}")
+    seg = total // (2 * world)
+    return [((r * seg, (r + 1) * seg), ((2 * world - 1 - r) * seg, (2 * world - r) * seg)) for r in range(world)]
+
+
+def segment_owner(seg_index, world):
+    return seg_index if seg_index < world else 2 * world - 1 - seg_index
+
+
+def ring_plan(rank, world):
+    """For each ring step s, the (q_part, kv_part, diagonal) block products rank ``rank`` runs on
+    the K/V block that started at rank (rank - s) % world.  Parts: 0 = the low segment of the
+    block's owner, 1 = its high segment.  Every step holds two products (three at s = 0)."""
+    plan = []
+    for s in range(world):
+        a = (rank - s) % world
+        prods = [(1, 0, False)]                                   # my high segment sees every low segment
+        if a < rank:
+            prods.append((0, 0, False))
+        elif a > rank:
+            prods.append((1, 1, False))
+        else:
+            prods = [(0, 0, True), (1, 0, False), (1, 1, True)]
+        plan.append((a, prods))
+    return plan
+
+
+class CudaBackend:
+    """The production backend: hand-written sm_100a kernels through the C ABI."""
+
+    def polar_block(self, q, k, v, n_keys, params, key_offset, stats_in, finalize, eps, window):
+        from .polar import polar_prefill_raw
+        return polar_prefill_raw(q, k, v, n_keys, params, eps=eps, window=window, key_offset=key_offset,
+                                 stats_in=stats_in, finalize=finalize)
+
+    def scan(self, q, k, v, g, beta, initial_state):
+        from .gated_delta import chunk_gated_delta_rule
+        return chunk_gated_delta_rule(q=q, k=k, v=v, g=g, beta=beta, scale=1.0, initial_state=initial_state,
+                                      output_final_state=True, use_qk_l2norm_in_kernel=True)
+
+    def prepare_params(self, params, device):
+        from .polar import _params
+        return _params(device=device, **params)
+
+
+def _exchange(send_buf, recv_buf, rank, world, group):
+    """Post the ring hop: my current K/V block goes to rank+1 while rank-1's arrives."""
+    ops = [dist.P2POp(dist.isend, send_buf, (rank + 1) % world, group),
+           dist.P2POp(dist.irecv, recv_buf, (rank - 1) % world, group)]
+    return dist.batch_isend_irecv(ops)
+
+
+@torch.no_grad()
+def ring_polar_prefill(q_parts, k_parts, v_parts, positions, params, *, backend=None, group=None,
+                       eps=1e-6, window=None):
+    """Polar attention for this rank's two query segments over the whole (sharded) sequence.
+
+    q_parts:  [q_lo, q_hi], each (1, H, L, dk)  - this rank's queries (low / high segment)
+    k_parts, v_parts: [lo, hi], each (1, Hkv, L, dk) - this rank's keys / values
+    positions: [(start_lo, end_lo), (start_hi, end_hi)] absolute token ranges of the two segments
+    params: the five raw Polar parameters (dict of tensors)
+    Returns [(c_lo, mag_lo), (c_hi, mag_hi)]."""
+    backend = backend or CudaBackend()
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    dev = q_parts[0].device
+    L = q_parts[0].shape[2]
+    seg = positions[0][1] - positions[0][0]
+    prepared = backend.prepare_params(params, dev)
+    n_keys = [torch.arange(p0 + 1, p1 + 1, device=dev, dtype=torch.float32) for (p0, p1) in positions]
+
+    # one contiguous buffer per hop: [K_lo, K_hi, V_lo, V_hi]
+    cur = torch.stack([k_parts[0], k_parts[1], v_parts[0], v_parts[1]]).contiguous()
+    nxt = torch.empty_like(cur)
+    plan = ring_plan(rank, world)
+    # the last product in which each query part takes part -> that call folds the null sink
+    last = {}
+    for s, (_, prods) in enumerate(plan):
+        for i, (qp, kp, _) in enumerate(prods):
+            last[qp] = (s, i)
+    stats = [None, None]
+    out = [None, None]
+    for s, (owner, prods) in enumerate(plan):
+        works = _exchange(cur, nxt, rank, world, group) if s + 1 < world else []
+        owner_pos = [(owner * seg, (owner + 1) * seg), ((2 * world - 1 - owner) * seg, (2 * world - owner) * seg)]
+        for i, (qp, kp, _diag) in enumerate(prods):
+            fin = last[qp] == (s, i)
+            res = backend.polar_block(q_parts[qp], cur[kp], cur[2 + kp], n_keys[qp], prepared,
+                                      owner_pos[kp][0], stats[qp], fin, eps, window)
+            if fin:
+                out[qp] = res
+            else:
+                stats[qp] = res
+        for w in works:
+            w.wait()
+        if s + 1 < world:
+            cur, nxt = nxt, cur
+    return out
+
+
+def compose_state_prefix(P_all, Q_all, S0=None):
+    """S_in of every segment from the per-segment affine maps, in time order.
+    P_all (n_seg, H, dk, dk) and Q_all (n_seg, H, dk, dv) in the [K,V] state layout:
+    S_out = P S_in + Q.  Returns (n_seg, H, dk, dv) incoming states and the final state."""
+    n_seg = P_all.shape[0]
+    S = torch.zeros_like(Q_all[0]) if S0 is None else S0.clone()
+    states = []
+    for i in range(n_seg):
+        states.append(S)
+        S = torch.matmul(P_all[i], S) + Q_all[i]
+    return torch.stack(states), S
+
+
+@torch.no_grad()
+def cp_gated_delta_scan(q_parts, k_parts, v_parts, g_parts, beta_parts, *, backend=None, group=None,
+                        initial_state=None):
+    """Gated-delta scan of this rank's two segments with the state handed across ranks as a
+    prefix of affine maps.  q_parts [lo, hi] each (1, L, H, dk); k, v (1, L, Hkv, d); g, beta
+    (1, L, H).  Returns ([o_lo, o_hi], final_state_of_the_whole_sequence)."""
+    backend = backend or CudaBackend()
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    H, dk = q_parts[0].shape[2], q_parts[0].shape[3]
+    dv = v_parts[0].shape[3]
+    dev = q_parts[0].device
+    if dk != dv:
+        raise ValueError("the affine-map pass stores the dk x dk map in the state, so it needs dk == dv")
+    # batch of four recurrences: (lo, P), (lo, Q), (hi, P), (hi, Q)
+    qb = torch.cat([q_parts[0], q_parts[0], q_parts[1], q_parts[1]])
+    kb = torch.cat([k_parts[0], k_parts[0], k_parts[1], k_parts[1]])
+    vb = torch.cat([torch.zeros_like(v_parts[0]), v_parts[0], torch.zeros_like(v_parts[1]), v_parts[1]])
+    gb = torch.cat([g_parts[0], g_parts[0], g_parts[1], g_parts[1]])
+    bb = torch.cat([beta_parts[0], beta_parts[0], beta_parts[1], beta_parts[1]])
+    eye = torch.eye(dk, device=dev, dtype=torch.float32).expand(H, dk, dk)
+    zero = torch.zeros(H, dk, dv, device=dev, dtype=torch.float32)
+    S0b = torch.stack([eye, zero, eye, zero]).contiguous()
+    _, Sf = backend.scan(qb, kb, vb, gb, bb, S0b)                    # (4, H, dk, dv)
+    mine = torch.stack([Sf[0], Sf[1], Sf[2], Sf[3]]).contiguous()   # P_lo, Q_lo, P_hi, Q_hi
+    gathered = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(gathered, mine, group=group)
+    P_all = torch.stack([gathered[segment_owner(i, world)][0 if i < world else 2] for i in range(2 * world)])
+    Q_all = torch.stack([gathered[segment_owner(i, world)][1 if i < world else 3] for i in range(2 * world)])
+    S_in, S_final = compose_state_prefix(P_all, Q_all, initial_state)
+    my_states = torch.stack([S_in[rank], S_in[2 * world - 1 - rank]]).contiguous()
+    o, _ = backend.scan(torch.cat(q_parts), torch.cat(k_parts), torch.cat(v_parts), torch.cat(g_parts),
+                        torch.cat(beta_parts), my_states)
+    return [o[0:1], o[1:2]], S_final
+
+
+@torch.no_grad()
+def cp_conv_halos(x_parts, kernel_size, *, group=None):
+    """The K-1 input rows that precede each of this rank's two segments (zeros for the first
+    segment of the sequence).  x_parts [lo, hi] each (L, C).  Returns [halo_lo, halo_hi],
+    each (C, K-1) in the conv-state layout (oldest first), ready to be passed as
+    ``initial_states`` of the prefill conv."""
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    Kh = kernel_size - 1
+    tails = [x[-Kh:].contiguous() for x in x_parts]                 # what the NEXT segment needs
+    my_segs = [rank, 2 * world - 1 - rank]
+    halos = [torch.zeros_like(tails[0]), torch.zeros_like(tails[1])]
+    ops = []
+    for part, seg_idx in enumerate(my_segs):
+        nxt_seg = seg_idx + 1
+        if nxt_seg < 2 * world:
+            dst = segment_owner(nxt_seg, world)
+            if dst == rank:                                         # my own two segments are adjacent (seg N-1, N)
+                halos[my_segs.index(nxt_seg)] = tails[part].clone()
+            else:
+                ops.append(dist.P2POp(dist.isend, tails[part], dst, group, tag=nxt_seg))
+        prev_seg = seg_idx - 1
+        if prev_seg >= 0:
+            src = segment_owner(prev_seg, world)
+            if src != rank:
+                ops.append(dist.P2POp(dist.irecv, halos[part], src, group, tag=seg_idx))
+    if ops:
+        for w in dist.batch_isend_irecv(ops):
+            w.wait()
+    return [h.transpose(0, 1).contiguous() for h in halos]
+
+
+@dataclass
+class GlobalLayerShard:
+    """One rank's slice of a sequence for the global-layer mixing step (two zig-zag segments)."""
+    q: list      # [lo, hi] each (1, L, H, dk)
+    k: list      # (1, L, Hkv, dk)
+    v: list
+    g: list      # (1, L, H) log decay
+    beta: list   # (1, L, H)
+    positions: list
+
+
+def shard_sequence(t, rank, world):
+    """Cut full-sequence tensors (1, T, ...) into this rank's two zig-zag segments."""
+    T = t["q"].shape[1]
+    (a0, a1), (b0, b1) = zigzag_segments(T, world)[rank]
+    cut = lambda x: [x[:, a0:a1].contiguous(), x[:, b0:b1].contiguous()]
+    return GlobalLayerShard(q=cut(t["q"]), k=cut(t["k"]), v=cut(t["v"]), g=cut(t["g"]), beta=cut(t["beta"]),
+                            positions=[(a0, a1), (b0, b1)])
+
+
+@torch.no_grad()
+def cp_global_layer_prefill(shard, params, *, backend=None, group=None):
+    """Polar ring pass + gated-delta prefix scan for one rank's shard.  Returns
+    ([(c, mag) lo, hi], [o lo, hi], final memory state)."""
+    tr = lambda x: x.transpose(1, 2)
+    polar = ring_polar_prefill([tr(x) for x in shard.q], [tr(x) for x in shard.k], [tr(x) for x in shard.v],
+                               shard.positions, params, backend=backend, group=group)
+    o, S = cp_gated_delta_scan(shard.q, shard.k, shard.v, shard.g, shard.beta, backend=backend, group=group)
+    return polar, o, S

@@ -159,11 +159,23 @@ def polar_attention_packed_fwd(q, k, v, tile_seq_starts, tile_q_starts, tile_seq
     return c, mag
 
 
-def decode_num_splits(B, Hkv, max_context, sm_count=148):
-    """Key ranges per (sequence, KV head): enough CTAs for ~4 waves over the SMs, at least
-    512 keys per range.  Depends only on launch-time shapes (CUDA-graph safe)."""
-    want = max(1, (4 * sm_count + B * Hkv - 1) // (B * Hkv))
-    return int(max(1, min(want, max(1, max_context // 512), 64)))
+def decode_num_splits(B, Hkv, max_context, sm_count=148, ctas_per_sm=2):
+    """Key ranges per (sequence, KV head).  The split kernel keeps ``ctas_per_sm`` CTAs resident
+    per SM, so the grid B*Hkv*n runs in ceil(B*Hkv*n / (sm_count*ctas_per_sm)) waves; pick the n
+    (at least 1024 keys per range, at most 64 ranges) whose last wave is fullest, preferring
+    more ranges on a tie-ish.  Depends only on launch-time shapes (CUDA-graph safe)."""
+    slots = sm_count * ctas_per_sm
+    n_max = int(max(1, min(64, max_context // 1024)))
+    best_n, best_eff = 1, -1.0
+    for n in range(1, n_max + 1):
+        ctas = B * Hkv * n
+        waves = -(-ctas // slots)
+        eff = ctas / (waves * slots)
+        if ctas < slots:                       # under one wave: more ranges always help
+            eff = ctas / slots
+        if eff > best_eff + 0.02:              # a larger n must buy at least 2% to be preferred
+            best_n, best_eff = n, eff
+    return best_n
 
 
 _scratch_cache = {}

@@ -10,8 +10,9 @@ Polar prefill (H=8, Hkv=2, dk=128, bf16, full causal context) followed by the ga
 chunked scan (H=8, d=128, chunk 64, fp32 state).  Inputs are seeded synthetic tensors with
 the value distributions BASELINE.json names.  `value` times the kernels with the inputs
 resident in HBM; `e2e` times the same public API calls with pinned-host inputs copied in and
-the results copied out inside the timed region.  With N > 1 ranks every rank processes its
-own sequence (weak scaling, no data-path collective).
+the results copied out inside the timed region.  With N > 1 ranks the SAME single sequence is
+sharded over the ranks (context parallel: NCCL ring of K/V blocks, gated-delta state prefix),
+so scaling is strong; the decode leg shards its batch of 64 sequences with no collective.
 
 `--impl reference` times the CPU oracle (a restatement of the reference's pure-PyTorch
 implementation, the only implementation of this path the reference can run without a GPU)
@@ -246,7 +247,7 @@ def run_reference(args, rank):
               f"Polar cost is quadratic, so tok/s at 64K would be ~{T_PREFILL // sample_T}x lower")
     line = {"impl": "reference", "metric": METRIC, "value": val, "unit": "tok/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": "global-layer mixing prefill (Polar + gated-delta scan), CPU sample",
                        "tokens": sample_T, "heads": H, "kv_heads": HKV, "head_dim": DK, "chunk": CHUNK},
             "cpu_baseline": {"value": val, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample},
@@ -301,6 +302,136 @@ def profile_case(which):
     print(json.dumps({"profile": which, **info}))
 
 
+def bench_decode_sharded(ab, device, steps, warmup, peaks, world, dist):
+    """Decode with the batch of 64 sequences split over the ranks (no collective): every rank
+    steps its own 64/N sequences; the aggregate is 64 tokens per slowest-rank step."""
+    global DEC_B
+    full_b = DEC_B
+    DEC_B = full_b // world
+    try:
+        d = bench_decode(ab, device, steps, warmup, peaks)
+    finally:
+        DEC_B = full_b
+    t = torch.tensor([d["ms_per_step"], d["roofline"]["kernel_ms"]], device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, kms = t.tolist()
+    d["ms_per_step"], d["value"] = ms, full_b / (ms * 1e-3)
+    d["config"]["batch"], d["config"]["batch_per_gpu"], d["config"]["sharding"] = full_b, full_b // world, "batch, no collective"
+    return d
+
+
+def run_context_parallel(args, ab, rank, local_rank, world, device, peaks):
+    """N > 1: ONE 65,536-token sequence sharded over the ranks (zig-zag segments); Polar K/V
+    blocks travel an NCCL ring, the gated-delta state is handed over as an affine-map prefix."""
+    import torch.distributed as dist
+    from atma_b200 import context_parallel as cp
+    dist.init_process_group("nccl", device_id=device)
+    full = make_prefill_inputs(seed=4)                       # the same sequence on every rank
+    sh = cp.shard_sequence(full, rank, world)
+    del full
+    fields = ("q", "k", "v", "g", "beta")
+    host = {f: [x.pin_memory() for x in getattr(sh, f)] for f in fields}
+    params = default_polar_params(device)
+
+    def to_dev():
+        return cp.GlobalLayerShard(positions=sh.positions,
+                                   **{f: [x.to(device, non_blocking=True) for x in host[f]] for f in fields})
+
+    def step(shard, ev=None):
+        tr = lambda x: x.transpose(1, 2)
+        if ev:
+            ev[0].record()
+        polar = cp.ring_polar_prefill([tr(x) for x in shard.q], [tr(x) for x in shard.k], [tr(x) for x in shard.v],
+                                      shard.positions, params)
+        if ev:
+            ev[1].record()
+        o, S = cp.cp_gated_delta_scan(shard.q, shard.k, shard.v, shard.g, shard.beta)
+        if ev:
+            ev[2].record()
+        return polar, o, S
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    dev_shard = to_dev()
+    for _ in range(args.warmup):
+        step(dev_shard)
+    sampler = ClockSampler(local_rank)
+    barrier()
+    sampler.start()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step(dev_shard, ev[i])
+    e1.record()
+    barrier()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / args.steps
+    polar_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / args.steps
+    scan_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / args.steps
+
+    out_host = None
+
+    def e2e_step():
+        nonlocal out_host
+        polar, o, S = step(to_dev())
+        outs = [polar[0][0], polar[0][1], polar[1][0], polar[1][1], o[0], o[1], S]
+        if out_host is None:
+            out_host = [torch.empty(x.shape, dtype=x.dtype, pin_memory=True) for x in outs]
+        for dst, src in zip(out_host, outs):
+            dst.copy_(src, non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    s1.record()
+    barrier()
+    e2e_ms = s0.elapsed_time(s1) / args.steps
+    h2d = sum(x.numel() * x.element_size() for f in fields for x in host[f])
+    d2h = sum(x.numel() * x.element_size() for x in out_host)
+    t = torch.tensor([ms, e2e_ms, polar_ms, scan_ms], device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_ms, polar_ms, scan_ms = t.tolist()
+    bytes_t = torch.tensor([h2d, d2h], device=device, dtype=torch.float64)
+    dist.all_reduce(bytes_t)
+    h2d, d2h = bytes_t.tolist()
+    del dev_shard
+    torch.cuda.empty_cache()
+    decode = None if args.skip_decode else bench_decode_sharded(ab, device, max(args.steps, 10), args.warmup, peaks, world, dist)
+    dist.barrier()
+    dist.destroy_process_group()
+    if rank != 0:
+        return
+    achieved_tf = polar_flops(T_PREFILL) / (polar_ms * 1e-3) / 1e12
+    line = {
+        "metric": METRIC, "value": T_PREFILL / (ms * 1e-3), "unit": "tok/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "global-layer mixing prefill: Polar attention + gated-delta scan, ONE 65536-token sequence "
+                               "context-parallel over the GPUs (zig-zag segments, NCCL ring of K/V blocks, state prefix)",
+                   "tokens": T_PREFILL, "heads": H, "kv_heads": HKV, "head_dim": DK, "chunk": CHUNK, "window": None,
+                   "l2": "per-GPU inputs shrink with N; at N=8 they are 34 MB, below L2", "polar_kernel": "tcgen05"},
+        "e2e": {"value": T_PREFILL / (e2e_ms * 1e-3), "unit": "tok/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": args.steps * (2 * world + 1 + 4),
+        "clocks": clocks,
+        "roofline": {"kernel": "polar_prefill (ring pass, all ranks)", "bound": "tensor", "achieved": achieved_tf,
+                     "peak": peaks["tf_burst"] * world, "unit": "TFLOP/s", "frac": achieved_tf / (peaks["tf_burst"] * world),
+                     "traffic": None, "algorithmic_flops": polar_flops(T_PREFILL), "kernel_ms": polar_ms,
+                     "peak_source": peaks["source"] + f" burst x {world} GPUs"},
+        "scan": {"kernel_ms": scan_ms, "algorithmic_flops": scan_flops(T_PREFILL)},
+        "cpu_baseline": None,
+        "decode": decode,
+    }
+    print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -328,11 +459,11 @@ def main():
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=device)
     peaks = measured_peaks()
+    if world > 1:
+        run_context_parallel(args, ab, rank, local_rank, world, device, peaks)
+        return
+    dist = None
 
     host = make_prefill_inputs(seed=4 + rank, pinned=True)
     dev_in = {n: x.to(device) for n, x in host.items()}
@@ -421,8 +552,8 @@ def main():
     line = {
         "metric": METRIC, "value": world * T_PREFILL / (ms * 1e-3), "unit": "tok/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "global-layer mixing prefill: Polar attention + gated-delta scan, one 65536-token sequence per GPU",
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "global-layer mixing prefill: Polar attention + gated-delta scan, one 65536-token sequence",
                    "tokens": T_PREFILL, "heads": H, "kv_heads": HKV, "head_dim": DK, "chunk": CHUNK,
                    "window": None, "l2": "inputs (268 MB) larger than L2 (126 MB)",
                    "polar_kernel": "tcgen05" if tensor_path else "cuda-core fp32"},

@@ -97,6 +97,9 @@ def chunk_gated_delta_rule_oracle(q, k, v, g, beta, initial_state=None, chunk=64
     (F.normalize, eps 1e-12) as the in-kernel normalisation does.  Returns
     o (B,T,H,dv) and the final state (B,H,dk,dv), both in ``compute_dtype``."""
     cd = compute_dtype
+    if k.shape[2] != q.shape[2]:                     # un-expanded KV heads: head h reads KV head h // G
+        G = q.shape[2] // k.shape[2]
+        k, v = k.repeat_interleave(G, dim=2), v.repeat_interleave(G, dim=2)
     qn = F.normalize(q.to(cd), dim=-1).transpose(1, 2)
     kn = F.normalize(k.to(cd), dim=-1).transpose(1, 2)
     vt = v.to(cd).transpose(1, 2)

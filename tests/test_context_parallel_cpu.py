@@ -1,0 +1,124 @@
+"""CPU (gloo, world_size 2 and 3): the context-parallel routing - zig-zag segments, ring plan,
+statistics carry, affine state prefix, conv halos - reproduces the single-process result.
+The compute backend here is the CPU oracle; the GPU path swaps in the CUDA kernels only."""
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import oracle
+from oracle.polar import polar_streaming_stats, polar_finalize
+from atma_b200 import context_parallel as cp
+
+
+class OracleBackend:
+    def prepare_params(self, params, device):
+        return params
+
+    def polar_block(self, q, k, v, n_keys, params, key_offset, stats_in, finalize, eps, window):
+        stats = polar_streaming_stats(q, k, v, n_keys, len_gain_raw=params["len_gain_raw"], window=window,
+                                      key_offset=key_offset, carry=stats_in, tile=8)
+        if not finalize:
+            return stats
+        return polar_finalize(stats, n_keys, eps=eps, window=window, **params)
+
+    def scan(self, q, k, v, g, beta, initial_state):
+        return oracle.chunk_gated_delta_rule_oracle(q, k, v, g, beta, initial_state=initial_state, chunk=8)
+
+
+def _inputs(T, H, Hkv, dk):
+    g = torch.Generator().manual_seed(0)
+    t = dict(q=torch.randn(1, T, H, dk, generator=g), k=torch.randn(1, T, Hkv, dk, generator=g),
+             v=torch.randn(1, T, Hkv, dk, generator=g),
+             g=-torch.nn.functional.softplus(torch.randn(1, T, H, generator=g)),
+             beta=torch.sigmoid(torch.randn(1, T, H, generator=g)))
+    params = dict(v_null=torch.randn(H, dk, generator=g) * 0.3, null_base=torch.full((H,), 2.0),
+                  null_slope_raw=torch.full((H,), 0.5), len_gain_raw=torch.full((H,), -1.0),
+                  mag_beta_raw=torch.full((H,), -1.5))
+    x = torch.randn(T, 6, generator=g)
+    return t, params, x
+
+
+def _worker(rank, world, port, T, ret):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.set_num_threads(1)
+        H, Hkv, dk = 4, 2, 16
+        t, params, x = _inputs(T, H, Hkv, dk)
+        shard = cp.shard_sequence(t, rank, world)
+        polar, o, S = cp.cp_global_layer_prefill(shard, params, backend=OracleBackend())
+        halos = cp.cp_conv_halos([x[a:b] for a, b in shard.positions], 4)
+        ret[rank] = dict(pos=shard.positions, c=[p[0] for p in polar], mag=[p[1] for p in polar], o=o, S=S, halos=halos)
+    finally:
+        dist.destroy_process_group()
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+@pytest.mark.parametrize("world,T", [(2, 64), (3, 96)])
+def test_context_parallel_matches_single_process(world, T):
+    H, Hkv, dk = 4, 2, 16
+    t, params, x = _inputs(T, H, Hkv, dk)
+    n = torch.arange(1, T + 1, dtype=torch.float32)
+    c_ref, m_ref = oracle.polar_prefill_oracle(t["q"].transpose(1, 2), t["k"].transpose(1, 2), t["v"].transpose(1, 2), n, params)
+    ke, ve = t["k"].repeat_interleave(H // Hkv, 2), t["v"].repeat_interleave(H // Hkv, 2)
+    o_ref, S_ref = oracle.chunk_gated_delta_rule_oracle(t["q"], ke, ve, t["g"], t["beta"], chunk=8)
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_worker, args=(world, _free_port(), T, ret), nprocs=world, join=True)
+    assert len(ret) == world
+    for rank in range(world):
+        r = ret[rank]
+        for part, (a, b) in enumerate(r["pos"]):
+            assert (r["c"][part] - c_ref[:, :, a:b]).abs().max() < 1e-5
+            assert (r["mag"][part] - m_ref[:, :, a:b]).abs().max() < 1e-5
+            assert (r["o"][part] - o_ref[:, a:b]).abs().max() < 1e-4
+            expect = torch.zeros(3, 6) if a == 0 else x[a - 3:a]
+            assert torch.equal(r["halos"][part], expect.t())
+        assert (r["S"] - S_ref[0]).abs().max() < 1e-4
+
+
+def test_zigzag_and_plan_cover_the_causal_triangle():
+    for world in (1, 2, 4, 8):
+        segs = cp.zigzag_segments(16 * world, world)
+        flat = sorted(s for pair in segs for s in pair)
+        assert flat == [(i * 8, (i + 1) * 8) for i in range(2 * world)]
+        seen = set()
+        for rank in range(world):
+            plan = cp.ring_plan(rank, world)
+            assert [a for a, _ in plan] == [(rank - s) % world for s in range(world)]
+            loads = [len(p) for _, p in plan]
+            assert loads[0] == (3 if True else 2) and all(x == 2 for x in loads[1:])      # balanced steps
+            for a, prods in plan:
+                for qp, kp, diag in prods:
+                    qs = rank if qp == 0 else 2 * world - 1 - rank
+                    ks = a if kp == 0 else 2 * world - 1 - a
+                    assert ks <= qs and diag == (ks == qs)
+                    seen.add((qs, ks))
+        assert seen == {(i, j) for i in range(2 * world) for j in range(i + 1)}
+    with pytest.raises(ValueError):
+        cp.zigzag_segments(100, 8)
+
+
+def test_state_prefix_composition():
+    g = torch.Generator().manual_seed(1)
+    P = torch.randn(5, 2, 4, 4, generator=g) * 0.5
+    Q = torch.randn(5, 2, 4, 3, generator=g)
+    S0 = torch.randn(2, 4, 3, generator=g)
+    states, final = cp.compose_state_prefix(P, Q, S0)
+    S = S0
+    for i in range(5):
+        assert torch.allclose(states[i], S)
+        S = P[i] @ S + Q[i]
+    assert torch.allclose(final, S)

@@ -1,0 +1,71 @@
+"""GPU (needs >= 2 devices; skipped on a 1-GPU box): the context-parallel prefill over NCCL gives
+the single-GPU result - Polar ring with statistics carry, gated-delta state prefix."""
+
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+T, H, HKV, DK = 2048, 8, 2, 128
+
+
+def _inputs():
+    g = torch.Generator().manual_seed(0)
+    t = dict(q=torch.randn(1, T, H, DK, generator=g).bfloat16(), k=torch.randn(1, T, HKV, DK, generator=g).bfloat16(),
+             v=torch.randn(1, T, HKV, DK, generator=g).bfloat16(),
+             g=-torch.nn.functional.softplus(torch.randn(1, T, H, generator=g)),
+             beta=torch.sigmoid(torch.randn(1, T, H, generator=g)))
+    params = dict(v_null=torch.randn(H, DK, generator=g) * 0.3, null_base=torch.full((H,), 2.0),
+                  null_slope_raw=torch.full((H,), 0.5), len_gain_raw=torch.full((H,), -1.0),
+                  mag_beta_raw=torch.full((H,), -1.5))
+    return t, params
+
+
+def _worker(rank, world, port, ret):
+    import torch.distributed as dist
+    import atma_b200
+    from atma_b200 import context_parallel as cp
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        t, params = _inputs()
+        tg = {n: x.to(dev) for n, x in t.items()}
+        pg = {n: x.to(dev) for n, x in params.items()}
+        shard = cp.shard_sequence(tg, rank, world)
+        polar, o, S = cp.cp_global_layer_prefill(shard, pg)
+        torch.cuda.synchronize()
+        ret[rank] = dict(pos=shard.positions, c=[p[0].float().cpu() for p in polar], mag=[p[1].float().cpu() for p in polar],
+                         o=[x.float().cpu() for x in o], S=S.float().cpu())
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_rank_context_parallel_matches_one_gpu():
+    import torch.multiprocessing as mp
+    import atma_b200
+    world = 2
+    t, params = _inputs()
+    tg = {n: x.cuda() for n, x in t.items()}
+    pg = {n: x.cuda() for n, x in params.items()}
+    n = torch.arange(1, T + 1, dtype=torch.float32).cuda()
+    c_ref, m_ref = atma_b200.polar_attention_fwd(tg["q"].transpose(1, 2), tg["k"].transpose(1, 2), tg["v"].transpose(1, 2), n, **pg)
+    o_ref, S_ref = atma_b200.chunk_gated_delta_rule(q=tg["q"], k=tg["k"], v=tg["v"], g=tg["g"], beta=tg["beta"], scale=1.0,
+                                                    output_final_state=True, use_qk_l2norm_in_kernel=True)
+    c_ref, m_ref, o_ref, S_ref = (x.float().cpu() for x in (c_ref, m_ref, o_ref, S_ref))
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    ret = mp.Manager().dict()
+    mp.spawn(_worker, args=(world, port, ret), nprocs=world, join=True)
+    rel = lambda a, b: float((a - b).abs().max() / b.abs().max().clamp_min(1e-12))
+    for rank in range(world):
+        r = ret[rank]
+        for part, (a, b) in enumerate(r["pos"]):
+            assert rel(r["c"][part], c_ref[:, :, a:b]) < 2e-2
+            assert rel(r["mag"][part], m_ref[:, :, a:b]) < 2e-2
+            assert rel(r["o"][part], o_ref[:, a:b]) < 2e-2
+        assert rel(r["S"], S_ref[0]) < 2e-2
