@@ -15,10 +15,11 @@ previous segment's last K-1 inputs.  This module shards ONE sequence over the ra
   and carries its running statistics (m, L, Q2, S) to the next step; the null sink is folded
   on the last block a query segment sees;
 * **gated-delta memory**: a segment acts on the state as an affine map S_out = P S_in + Qm.
-  Each rank gets (P, Qm) of both of its segments from one batched scan (the P rows use v = 0
-  and the identity as initial state), an all-gather shares the 2N pairs (1 MB each at the
-  model's shape), the prefix is composed locally in fp32, and a second batched scan produces
-  the outputs from the true incoming states;
+  Each rank builds the per-chunk factors of its two segments once, gets (P, Qm) of both from
+  one launch of four recurrences over them (the P recurrences use v = 0 and start from the
+  identity), an all-gather shares the 2N pairs (1 MB each at the model's shape), the prefix is
+  composed locally in fp32, and a second launch produces the outputs from the true incoming
+  states - the factors are not recomputed;
 * **depthwise conv**: a K-1 row halo from the previous segment's owner.
 
 The compute kernels are injected through a small backend object so that the routing can be
@@ -73,6 +74,14 @@ class CudaBackend:
         from .gated_delta import chunk_gated_delta_rule
         return chunk_gated_delta_rule(q=q, k=k, v=v, g=g, beta=beta, scale=1.0, initial_state=initial_state,
                                       output_final_state=True, use_qk_l2norm_in_kernel=True)
+
+    def scan_factors(self, q, k, v, g, beta):
+        from .gated_delta import scan_factors
+        return scan_factors(q, k, v, g, beta, scale=1.0, use_qk_l2norm_in_kernel=True)
+
+    def scan_recur(self, factors, rec_of, initial_state, zero_value, want_output):
+        from .gated_delta import scan_recur
+        return scan_recur(factors, rec_of, initial_state, zero_value, want_output)
 
     def prepare_params(self, params, device):
         from .polar import _params
@@ -161,16 +170,13 @@ def cp_gated_delta_scan(q_parts, k_parts, v_parts, g_parts, beta_parts, *, backe
     dev = q_parts[0].device
     if dk != dv:
         raise ValueError("the affine-map pass stores the dk x dk map in the state, so it needs dk == dv")
-    # batch of four recurrences: (lo, P), (lo, Q), (hi, P), (hi, Q)
-    qb = torch.cat([q_parts[0], q_parts[0], q_parts[1], q_parts[1]])
-    kb = torch.cat([k_parts[0], k_parts[0], k_parts[1], k_parts[1]])
-    vb = torch.cat([torch.zeros_like(v_parts[0]), v_parts[0], torch.zeros_like(v_parts[1]), v_parts[1]])
-    gb = torch.cat([g_parts[0], g_parts[0], g_parts[1], g_parts[1]])
-    bb = torch.cat([beta_parts[0], beta_parts[0], beta_parts[1], beta_parts[1]])
+    # four recurrences over the factors of the two segments: (lo, P), (lo, Q), (hi, P), (hi, Q)
     eye = torch.eye(dk, device=dev, dtype=torch.float32).expand(H, dk, dk)
     zero = torch.zeros(H, dk, dv, device=dev, dtype=torch.float32)
     S0b = torch.stack([eye, zero, eye, zero]).contiguous()
-    _, Sf = backend.scan(qb, kb, vb, gb, bb, S0b)                    # (4, H, dk, dv)
+    factors = backend.scan_factors(torch.cat(q_parts), torch.cat(k_parts), torch.cat(v_parts), torch.cat(g_parts),
+                                   torch.cat(beta_parts))
+    _, Sf = backend.scan_recur(factors, [0, 0, 1, 1], S0b, [True, False, True, False], want_output=False)
     mine = torch.stack([Sf[0], Sf[1], Sf[2], Sf[3]]).contiguous()   # P_lo, Q_lo, P_hi, Q_hi
     gathered = [torch.empty_like(mine) for _ in range(world)]
     dist.all_gather(gathered, mine, group=group)
@@ -178,8 +184,7 @@ def cp_gated_delta_scan(q_parts, k_parts, v_parts, g_parts, beta_parts, *, backe
     Q_all = torch.stack([gathered[segment_owner(i, world)][1 if i < world else 3] for i in range(2 * world)])
     S_in, S_final = compose_state_prefix(P_all, Q_all, initial_state)
     my_states = torch.stack([S_in[rank], S_in[2 * world - 1 - rank]]).contiguous()
-    o, _ = backend.scan(torch.cat(q_parts), torch.cat(k_parts), torch.cat(v_parts), torch.cat(g_parts),
-                        torch.cat(beta_parts), my_states)
+    o, _ = backend.scan_recur(factors, [0, 1], my_states, None, want_output=True)
     return [o[0:1], o[1:2]], S_final
 
 

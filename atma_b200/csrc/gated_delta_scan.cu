@@ -223,9 +223,36 @@ int gated_delta_scan_mma(const void* q, const void* k, const void* v, int dtype,
                          const float* initial_state, void* o, float* final_state, void* scratch, int B, int T, int H,
                          int Hkv, int normalize_qk, float scale, cudaStream_t st);
 
+int gated_delta_scan_mma_factors(const void* q, const void* k, const void* v, int dtype, const float* g,
+                                 const float* beta, void* scratch, int B, int T, int H, int Hkv, int normalize_qk,
+                                 float scale, cudaStream_t st);
+int gated_delta_scan_mma_recur(void* scratch, int dtype, int B, int T, int H, int n_rec, const int* rec_of,
+                               const int* zero_u0, const float* initial_state, void* o, float* final_state,
+                               cudaStream_t st);
+
 }  // namespace atma
 
 using namespace atma;
+
+extern "C" int atma_gated_delta_scan_factors(const void* q, const void* k, const void* v, int dtype, const float* g,
+                                             const float* beta, void* scratch, int B, int T, int H, int Hkv, int dk,
+                                             int dv, int normalize_qk, float scale, void* stream) {
+  ATMA_REQUIRE(gated_delta_scan_mma_supported(dtype, dk, dv),
+               "gated_delta_scan_factors: needs 16-bit inputs with dk = dv = 128 (got dtype %d, dk %d, dv %d)", dtype, dk, dv);
+  ATMA_REQUIRE(B > 0 && T > 0 && H > 0 && Hkv > 0 && H % Hkv == 0, "gated_delta_scan_factors: bad shape");
+  ATMA_REQUIRE(scratch != nullptr && (uintptr_t)scratch % 256 == 0 && (uintptr_t)q % 16 == 0 && (uintptr_t)k % 16 == 0 &&
+                   (uintptr_t)v % 16 == 0, "gated_delta_scan_factors: scratch must be 256-byte and inputs 16-byte aligned");
+  return gated_delta_scan_mma_factors(q, k, v, dtype, g, beta, scratch, B, T, H, Hkv, normalize_qk, scale, (cudaStream_t)stream);
+}
+
+extern "C" int atma_gated_delta_scan_recur(void* scratch, int dtype, int B, int T, int H, int dk, int dv, int n_rec,
+                                           const int* rec_of, const int* zero_u0, const float* initial_state, void* o,
+                                           float* final_state, void* stream) {
+  ATMA_REQUIRE(gated_delta_scan_mma_supported(dtype, dk, dv), "gated_delta_scan_recur: needs 16-bit, dk = dv = 128");
+  ATMA_REQUIRE(scratch != nullptr && B > 0 && T > 0 && H > 0, "gated_delta_scan_recur: bad arguments");
+  return gated_delta_scan_mma_recur(scratch, dtype, B, T, H, n_rec, rec_of, zero_u0, initial_state, o, final_state,
+                                    (cudaStream_t)stream);
+}
 
 extern "C" int64_t atma_gated_delta_scan_scratch_bytes(int B, int T, int H, int dk, int dv) {
   const int NC = (T + kScanC - 1) / kScanC;

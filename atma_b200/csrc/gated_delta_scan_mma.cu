@@ -7,7 +7,7 @@
 // Kernel A (one CTA per chunk) forms K K^T and Q K^T with mma.sync, inverts the unit lower
 // triangular 64x64 system in fp32 (16x16 diagonal blocks by substitution, then two levels of
 // block merges), and forms W and U0 with mma.sync; all factors go to scratch as 16-bit tiles.
-// Kernel B (one CTA per (sequence, head, 64-column half of S)) walks the chunks in order: the
+// Kernel B (one CTA per (recurrence, head, 32- or 64-column slice of S)) walks the chunks in order: the
 // fp32 state lives in the mma accumulators of its 4 warps for the whole sequence, a 16-bit copy
 // in shared memory serves as the B operand of the two state products, and the per-chunk factors
 // stream in through a 2-stage cp.async ring.  The recurrence is latency-bound, which is why it
@@ -262,24 +262,35 @@ scan_local_mma_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict
 // ------------------------------------------------------------------------------------------------
 // Kernel B: the recurrence over chunks
 // ------------------------------------------------------------------------------------------------
-constexpr int kStageBytes = 3 * kC * kD * 2 + kC * 64 * 2 + kC * kC * 2;      // W, Qg, Kt, U0 half, Rq = 65,536 B
-constexpr int kSeqSmem = 2 * kStageBytes + kD * 64 * 2 + kC * 64 * 2;         // + S copy + U copy = 155,648 B
+struct RecMap {            // recurrence i walks the chunk records of batch entry rec[i];
+  int rec[16];             // zero_u0[i] != 0 replaces U0 by zero (the "v = 0" recurrence that
+  int zero_u0[16];         // yields a segment's state-transfer matrix)
+};
 
-template <bool kBf16>
+template <int NCOL> struct SeqCfg {
+  static constexpr int kStage = 3 * kC * kD * 2 + kC * NCOL * 2 + kC * kC * 2;   // W, Qg, Kt, U0 slice, Rq
+  static constexpr int kSmem = 2 * kStage + kD * NCOL * 2 + kC * NCOL * 2;       // + S copy + U copy
+};
+
+template <bool kBf16, int NCOL>
 __global__ void __launch_bounds__(128)
 scan_seq_mma_kernel(const uint8_t* __restrict__ rec_base, const float* __restrict__ gc_base,
                     const float* __restrict__ initial_state, uint16_t* __restrict__ o,
-                    float* __restrict__ final_state, int Tlen, int H, int NC) {
+                    float* __restrict__ final_state, int Tlen, int H, int NC, const RecMap map) {
+  constexpr int NT = NCOL / 8, NP = NCOL / 16, CHN = NCOL / 8;
+  constexpr int kStage = SeqCfg<NCOL>::kStage;
   extern __shared__ __align__(128) uint8_t sm[];
-  uint8_t* Sb = sm + 2 * kStageBytes;                // [128 k][64 v] 16-bit, swizzled (rows of 128 B)
-  uint8_t* Ub = Sb + kD * 64 * 2;                    // [64 s][64 v]
+  uint8_t* Sb = sm + 2 * kStage;                     // [128 k][NCOL v] 16-bit, swizzled
+  uint8_t* Ub = Sb + kD * NCOL * 2;                  // [64 s][NCOL v]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int half = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int slice = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int rb = map.rec[b];
+  const bool zero_u0 = map.zero_u0[b] != 0;
   const int gq = lane >> 2, tq = lane & 3;
-  const uint8_t* recs = rec_base + ((int64_t)b * H + h) * NC * (int64_t)kRecBytes;
-  const float* gcs = gc_base + ((int64_t)b * H + h) * NC;
+  const uint8_t* recs = rec_base + ((int64_t)rb * H + h) * NC * (int64_t)kRecBytes;
+  const float* gcs = gc_base + ((int64_t)rb * H + h) * NC;
 
-  auto stage_ptr = [&](int s) { return sm + s * kStageBytes; };
+  auto stage_ptr = [&](int s) { return sm + s * kStage; };
   auto load_stage = [&](int c, int s) {
     const uint8_t* rec = recs + (int64_t)c * kRecBytes;
     uint8_t* dst = stage_ptr(s);
@@ -287,27 +298,30 @@ scan_seq_mma_kernel(const uint8_t* __restrict__ rec_base, const float* __restric
       const int tile = i / (kC * 16), r = (i >> 4) & 63, ch = i & 15;
       cp_async16(smem_u32(dst) + tile * (kC * kD * 2) + tile_off(r, ch * 8, kD), rec + tile * (kC * kD * 2) + r * 256 + ch * 16, true);
     }
-    for (int i = tid; i < kC * 8; i += 128) {                  // U0 columns [64*half, +64), Rq
+    for (int i = tid; i < kC * CHN; i += 128) {                // U0 columns [NCOL*slice, +NCOL)
+      const int r = i / CHN, ch = i % CHN;
+      cp_async16(smem_u32(dst) + 3 * kC * kD * 2 + tile_off(r, ch * 8, NCOL), rec + kRecU0 + r * 256 + slice * NCOL * 2 + ch * 16, !zero_u0);
+    }
+    for (int i = tid; i < kC * 8; i += 128) {                  // Rq
       const int r = i >> 3, ch = i & 7;
-      cp_async16(smem_u32(dst) + 3 * kC * kD * 2 + tile_off(r, ch * 8, 64), rec + kRecU0 + r * 256 + half * 128 + ch * 16, true);
-      cp_async16(smem_u32(dst) + 3 * kC * kD * 2 + kC * 64 * 2 + tile_off(r, ch * 8, 64), rec + kRecRq + r * 128 + ch * 16, true);
+      cp_async16(smem_u32(dst) + 3 * kC * kD * 2 + kC * NCOL * 2 + tile_off(r, ch * 8, 64), rec + kRecRq + r * 128 + ch * 16, true);
     }
   };
 
-  // fp32 state: warp w owns rows k = 32w .. 32w+31 (two 16-row tiles) x 64 columns
-  float S[2][8][4];
-  const int64_t sbase = ((int64_t)b * H + h) * kD * kD + half * 64;
+  // fp32 state: warp w owns rows k = 32w .. 32w+31 (two 16-row tiles) x NCOL columns
+  float S[2][NT][4];
+  const int64_t sbase = ((int64_t)b * H + h) * kD * kD + slice * NCOL;
 #pragma unroll
   for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt)
+    for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
       for (int hh = 0; hh < 2; ++hh) {
         const int kr = 32 * warp + 16 * mt + gq + 8 * hh, col = 8 * nt + 2 * tq;
         float2 v2 = make_float2(0.f, 0.f);
         if (initial_state) v2 = *reinterpret_cast<const float2*>(initial_state + sbase + (int64_t)kr * kD + col);
         S[mt][nt][2 * hh] = v2.x; S[mt][nt][2 * hh + 1] = v2.y;
-        *reinterpret_cast<uint32_t*>(Sb + tile_off(kr, col, 64)) = pack2<kBf16>(v2.x, v2.y);
+        *reinterpret_cast<uint32_t*>(Sb + tile_off(kr, col, NCOL)) = pack2<kBf16>(v2.x, v2.y);
       }
   load_stage(0, 0);
   cp_async_commit();
@@ -325,16 +339,16 @@ scan_seq_mma_kernel(const uint8_t* __restrict__ rec_base, const float* __restric
     __syncthreads();                                           // stage s landed; Sb from the previous chunk visible
     const uint32_t Wsm = smem_u32(stage_ptr(s)), Qsm = Wsm + kC * kD * 2, Ksm = Qsm + kC * kD * 2;
     const uint8_t* U0s = stage_ptr(s) + 3 * kC * kD * 2;
-    const uint32_t Rsm = Wsm + 3 * kC * kD * 2 + kC * 64 * 2;
+    const uint32_t Rsm = Wsm + 3 * kC * kD * 2 + kC * NCOL * 2;
     const float gC = gcs[c];
 
     // U = U0 - W S ; O = Qg S   (rows 16w..16w+15 of the chunk)
-    float U[8][4], O[8][4];
+    float U[NT][4], O[NT][4];
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) {
+    for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
       for (int hh = 0; hh < 2; ++hh) {
-        const float2 u2 = unpack2<kBf16>(*reinterpret_cast<const uint32_t*>(U0s + tile_off(16 * warp + gq + 8 * hh, 8 * nt + 2 * tq, 64)));
+        const float2 u2 = unpack2<kBf16>(*reinterpret_cast<const uint32_t*>(U0s + tile_off(16 * warp + gq + 8 * hh, 8 * nt + 2 * tq, NCOL)));
         U[nt][2 * hh] = u2.x; U[nt][2 * hh + 1] = u2.y;
         O[nt][2 * hh] = 0.f; O[nt][2 * hh + 1] = 0.f;
       }
@@ -345,9 +359,9 @@ scan_seq_mma_kernel(const uint8_t* __restrict__ rec_base, const float* __restric
       ldsm_x4(Wsm + tile_off(16 * warp + am, 16 * ks + ak, kD), aw);
       ldsm_x4(Qsm + tile_off(16 * warp + am, 16 * ks + ak, kD), aq);
 #pragma unroll
-      for (int pr = 0; pr < 4; ++pr) {
+      for (int pr = 0; pr < NP; ++pr) {
         uint32_t bf[4];
-        ldsm_x4_trans(smem_u32(Sb) + tile_off(16 * ks + bk, 16 * pr + bn, 64), bf);
+        ldsm_x4_trans(smem_u32(Sb) + tile_off(16 * ks + bk, 16 * pr + bn, NCOL), bf);
         mma16816<kBf16>(U[2 * pr], aw, bf[0], bf[1]);
         mma16816<kBf16>(U[2 * pr + 1], aw, bf[2], bf[3]);
         mma16816<kBf16>(O[2 * pr], aq, bf[0], bf[1]);
@@ -355,35 +369,37 @@ scan_seq_mma_kernel(const uint8_t* __restrict__ rec_base, const float* __restric
       }
     }
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) {
-      *reinterpret_cast<uint32_t*>(Ub + tile_off(16 * warp + gq, 8 * nt + 2 * tq, 64)) = pack2<kBf16>(U[nt][0], U[nt][1]);
-      *reinterpret_cast<uint32_t*>(Ub + tile_off(16 * warp + gq + 8, 8 * nt + 2 * tq, 64)) = pack2<kBf16>(U[nt][2], U[nt][3]);
+    for (int nt = 0; nt < NT; ++nt) {
+      *reinterpret_cast<uint32_t*>(Ub + tile_off(16 * warp + gq, 8 * nt + 2 * tq, NCOL)) = pack2<kBf16>(U[nt][0], U[nt][1]);
+      *reinterpret_cast<uint32_t*>(Ub + tile_off(16 * warp + gq + 8, 8 * nt + 2 * tq, NCOL)) = pack2<kBf16>(U[nt][2], U[nt][3]);
     }
     __syncthreads();                                           // U of every warp visible; all reads of Sb done
 
     // O += Rq U  (s <= 16w+15 -> k-steps 0..w) and store
+    if (o != nullptr) {
 #pragma unroll
-    for (int ks = 0; ks < 4; ++ks) {
-      if (ks <= warp) {
-        uint32_t ar[4];
-        ldsm_x4(Rsm + tile_off(16 * warp + am, 16 * ks + ak, 64), ar);
+      for (int ks = 0; ks < 4; ++ks) {
+        if (ks <= warp) {
+          uint32_t ar[4];
+          ldsm_x4(Rsm + tile_off(16 * warp + am, 16 * ks + ak, 64), ar);
 #pragma unroll
-        for (int pr = 0; pr < 4; ++pr) {
-          uint32_t bf[4];
-          ldsm_x4_trans(smem_u32(Ub) + tile_off(16 * ks + bk, 16 * pr + bn, 64), bf);
-          mma16816<kBf16>(O[2 * pr], ar, bf[0], bf[1]);
-          mma16816<kBf16>(O[2 * pr + 1], ar, bf[2], bf[3]);
+          for (int pr = 0; pr < NP; ++pr) {
+            uint32_t bf[4];
+            ldsm_x4_trans(smem_u32(Ub) + tile_off(16 * ks + bk, 16 * pr + bn, NCOL), bf);
+            mma16816<kBf16>(O[2 * pr], ar, bf[0], bf[1]);
+            mma16816<kBf16>(O[2 * pr + 1], ar, bf[2], bf[3]);
+          }
         }
       }
-    }
 #pragma unroll
-    for (int hh = 0; hh < 2; ++hh) {
-      const int t = c * kC + 16 * warp + gq + 8 * hh;
-      if (t < Tlen) {
-        uint16_t* orow = o + (((int64_t)b * Tlen + t) * H + h) * kD + half * 64;
+      for (int hh = 0; hh < 2; ++hh) {
+        const int t = c * kC + 16 * warp + gq + 8 * hh;
+        if (t < Tlen) {
+          uint16_t* orow = o + (((int64_t)b * Tlen + t) * H + h) * kD + slice * NCOL;
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt)
-          *reinterpret_cast<uint32_t*>(orow + 8 * nt + 2 * tq) = pack2<kBf16>(O[nt][2 * hh], O[nt][2 * hh + 1]);
+          for (int nt = 0; nt < NT; ++nt)
+            *reinterpret_cast<uint32_t*>(orow + 8 * nt + 2 * tq) = pack2<kBf16>(O[nt][2 * hh], O[nt][2 * hh + 1]);
+        }
       }
     }
 
@@ -391,20 +407,20 @@ scan_seq_mma_kernel(const uint8_t* __restrict__ rec_base, const float* __restric
 #pragma unroll
     for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt)
+      for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
         for (int e = 0; e < 4; ++e) S[mt][nt][e] *= gC;
 #pragma unroll
     for (int ks = 0; ks < 4; ++ks) {
-      uint32_t bfr[4][4];
+      uint32_t bfr[NP][4];
 #pragma unroll
-      for (int pr = 0; pr < 4; ++pr) ldsm_x4_trans(smem_u32(Ub) + tile_off(16 * ks + bk, 16 * pr + bn, 64), bfr[pr]);
+      for (int pr = 0; pr < NP; ++pr) ldsm_x4_trans(smem_u32(Ub) + tile_off(16 * ks + bk, 16 * pr + bn, NCOL), bfr[pr]);
 #pragma unroll
       for (int mt = 0; mt < 2; ++mt) {
         uint32_t at[4];
         ldsm_x4_trans(Ksm + tile_off(16 * ks + tk, 32 * warp + 16 * mt + tm, kD), at);
 #pragma unroll
-        for (int pr = 0; pr < 4; ++pr) {
+        for (int pr = 0; pr < NP; ++pr) {
           mma16816<kBf16>(S[mt][2 * pr], at, bfr[pr][0], bfr[pr][1]);
           mma16816<kBf16>(S[mt][2 * pr + 1], at, bfr[pr][2], bfr[pr][3]);
         }
@@ -413,10 +429,10 @@ scan_seq_mma_kernel(const uint8_t* __restrict__ rec_base, const float* __restric
 #pragma unroll
     for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt)
+      for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh)
-          *reinterpret_cast<uint32_t*>(Sb + tile_off(32 * warp + 16 * mt + gq + 8 * hh, 8 * nt + 2 * tq, 64)) =
+          *reinterpret_cast<uint32_t*>(Sb + tile_off(32 * warp + 16 * mt + gq + 8 * hh, 8 * nt + 2 * tq, NCOL)) =
               pack2<kBf16>(S[mt][nt][2 * hh], S[mt][nt][2 * hh + 1]);
     __syncthreads();                                           // stage s and Ub free; new Sb complete
   }
@@ -425,7 +441,7 @@ scan_seq_mma_kernel(const uint8_t* __restrict__ rec_base, const float* __restric
 #pragma unroll
     for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt)
+      for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
           const int kr = 32 * warp + 16 * mt + gq + 8 * hh, col = 8 * nt + 2 * tq;
@@ -446,32 +462,80 @@ int64_t gated_delta_scan_mma_scratch_bytes(int B, int T, int H) {
   return (int64_t)B * H * NC * kRecBytes + (int64_t)B * H * NC * sizeof(float) + 256;
 }
 
-int gated_delta_scan_mma(const void* q, const void* k, const void* v, int dtype, const float* g, const float* beta,
-                         const float* initial_state, void* o, float* final_state, void* scratch, int B, int T, int H,
-                         int Hkv, int normalize_qk, float scale, cudaStream_t st) {
+static float* gc_array(void* scratch, int B, int H, int NC) {
+  uint8_t* recs = static_cast<uint8_t*>(scratch);
+  return reinterpret_cast<float*>(recs + (((int64_t)B * H * NC * kRecBytes + 255) / 256) * 256);
+}
+
+// Kernel A only: the chunk-local factors of B sequences into `scratch`.
+int gated_delta_scan_mma_factors(const void* q, const void* k, const void* v, int dtype, const float* g,
+                                 const float* beta, void* scratch, int B, int T, int H, int Hkv, int normalize_qk,
+                                 float scale, cudaStream_t st) {
   const int NC = (T + kC - 1) / kC;
   uint8_t* recs = static_cast<uint8_t*>(scratch);
-  float* gcs = reinterpret_cast<float*>(recs + (((int64_t)B * H * NC * kRecBytes + 255) / 256) * 256);
+  float* gcs = gc_array(scratch, B, H, NC);
   const int smemA = 3 * kC * kD * 2 + (2 * kC * 65 + 32 * 33) * 4 + kC * kC * 2 + 4 * kC * 4;
-  const bool bf = dtype == ATMA_BF16;
-  if (bf) {
+  if (dtype == ATMA_BF16) {
     ATMA_CUDA_OK(cudaFuncSetAttribute(scan_local_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smemA));
-    ATMA_CUDA_OK(cudaFuncSetAttribute(scan_seq_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSeqSmem));
     scan_local_mma_kernel<true><<<dim3(NC, H, B), 128, smemA, st>>>((const uint16_t*)q, (const uint16_t*)k, (const uint16_t*)v, g,
                                                                    beta, recs, gcs, T, H, Hkv, NC, normalize_qk, scale);
   } else {
     ATMA_CUDA_OK(cudaFuncSetAttribute(scan_local_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smemA));
-    ATMA_CUDA_OK(cudaFuncSetAttribute(scan_seq_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSeqSmem));
     scan_local_mma_kernel<false><<<dim3(NC, H, B), 128, smemA, st>>>((const uint16_t*)q, (const uint16_t*)k, (const uint16_t*)v, g,
                                                                     beta, recs, gcs, T, H, Hkv, NC, normalize_qk, scale);
   }
-  int rc = launch_status("gated_delta_scan (chunk-local, mma)");
-  if (rc != ATMA_OK) return rc;
-  if (bf)
-    scan_seq_mma_kernel<true><<<dim3(2, H, B), 128, kSeqSmem, st>>>(recs, gcs, initial_state, (uint16_t*)o, final_state, T, H, NC);
-  else
-    scan_seq_mma_kernel<false><<<dim3(2, H, B), 128, kSeqSmem, st>>>(recs, gcs, initial_state, (uint16_t*)o, final_state, T, H, NC);
+  return launch_status("gated_delta_scan (chunk-local, mma)");
+}
+
+// Kernel B only: n_rec recurrences over the factors of a scratch built for B sequences.
+int gated_delta_scan_mma_recur(void* scratch, int dtype, int B, int T, int H, int n_rec, const int* rec_of,
+                               const int* zero_u0, const float* initial_state, void* o, float* final_state,
+                               cudaStream_t st) {
+  const int NC = (T + kC - 1) / kC;
+  if (n_rec < 1 || n_rec > 16) return fail(ATMA_ERR_INVALID, "gated_delta_scan_recur: n_rec=%d outside 1..16", n_rec);
+  RecMap map{};
+  for (int i = 0; i < n_rec; ++i) {
+    map.rec[i] = rec_of ? rec_of[i] : i;
+    map.zero_u0[i] = zero_u0 ? zero_u0[i] : 0;
+    if (map.rec[i] < 0 || map.rec[i] >= B)
+      return fail(ATMA_ERR_INVALID, "gated_delta_scan_recur: rec_of[%d]=%d outside the %d factor sets", i, map.rec[i], B);
+  }
+  const uint8_t* recs = static_cast<const uint8_t*>(scratch);
+  const float* gcs = gc_array(scratch, B, H, NC);
+  const bool bf = dtype == ATMA_BF16;
+  // few recurrences: 32-column slices (4 CTAs per head) shorten the per-chunk critical path
+  const bool narrow = (int64_t)n_rec * H * 2 < 148;
+#define ATMA_LAUNCH(BF, NCOL)                                                                                     \
+  do {                                                                                                            \
+    auto kern = scan_seq_mma_kernel<BF, NCOL>;                                                                    \
+    ATMA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SeqCfg<NCOL>::kSmem));   \
+    kern<<<dim3(kD / NCOL, H, n_rec), 128, SeqCfg<NCOL>::kSmem, st>>>(recs, gcs, initial_state, (uint16_t*)o,     \
+                                                                       final_state, T, H, NC, map);               \
+  } while (0)
+  if (bf) { if (narrow) ATMA_LAUNCH(true, 32); else ATMA_LAUNCH(true, 64); }
+  else { if (narrow) ATMA_LAUNCH(false, 32); else ATMA_LAUNCH(false, 64); }
+#undef ATMA_LAUNCH
   return launch_status("gated_delta_scan (recurrence, mma)");
+}
+
+int gated_delta_scan_mma(const void* q, const void* k, const void* v, int dtype, const float* g, const float* beta,
+                         const float* initial_state, void* o, float* final_state, void* scratch, int B, int T, int H,
+                         int Hkv, int normalize_qk, float scale, cudaStream_t st) {
+  int rc = gated_delta_scan_mma_factors(q, k, v, dtype, g, beta, scratch, B, T, H, Hkv, normalize_qk, scale, st);
+  if (rc != ATMA_OK) return rc;
+  int done = 0;
+  while (done < B) {                                  // at most 16 recurrences per launch
+    const int n = (B - done) < 16 ? (B - done) : 16;
+    int rec_of[16];
+    for (int i = 0; i < n; ++i) rec_of[i] = done + i;
+    const int64_t so = (int64_t)done * H * kD * kD, oo = (int64_t)done * T * H * kD;
+    rc = gated_delta_scan_mma_recur(scratch, dtype, B, T, H, n, rec_of, nullptr,
+                                    initial_state ? initial_state + so : nullptr,
+                                    o ? (void*)((uint16_t*)o + oo) : nullptr, final_state ? final_state + so : nullptr, st);
+    if (rc != ATMA_OK) return rc;
+    done += n;
+  }
+  return ATMA_OK;
 }
 
 }  // namespace atma

@@ -19,8 +19,10 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
 __device__ __forceinline__ int swz(int row, int chunk) { return chunk ^ (row & 7); }
 
 // byte offset of element (row, col) in a swizzled tile whose rows hold `row_elems` 16-bit values
+// (32, 64 or 128).  Rows of 64 bytes share a 128-byte line in pairs, so they swizzle on row/2.
 __device__ __forceinline__ uint32_t tile_off(int row, int col, int row_elems) {
-  return (uint32_t)(row * row_elems * 2 + (swz(row, col >> 3) << 4) + ((col & 7) << 1));
+  const int sw = (row_elems >= 64) ? (row & 7) : ((row >> 1) & 3);
+  return (uint32_t)(row * row_elems * 2 + (((col >> 3) ^ sw) << 4) + ((col & 7) << 1));
 }
 
 __device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void* gsrc, bool valid) {

@@ -91,3 +91,50 @@ def chunk_gated_delta_rule(q=None, k=None, v=None, g=None, beta=None, scale=None
         _lib.ptr(initial_state), _lib.ptr(o), _lib.ptr(final), _lib.ptr(scratch),
         B, T, H, Hkv, dk, dv, 1 if use_qk_l2norm_in_kernel else 0, float(scale), _lib.stream_ptr()))
     return o, final
+
+
+class ScanFactors:
+    """Handle on the per-chunk factors of B sequences (see ``scan_factors``)."""
+
+    def __init__(self, scratch, B, T, H, dk, dv, dtype, device):
+        self.scratch, self.B, self.T, self.H, self.dk, self.dv, self.dtype, self.device = scratch, B, T, H, dk, dv, dtype, device
+
+
+@torch.no_grad()
+def scan_factors(q, k, v, g, beta, scale=1.0, use_qk_l2norm_in_kernel=True):
+    """First half of ``chunk_gated_delta_rule`` for a sequence that is split across GPUs: the
+    state-independent per-chunk factors (16-bit inputs, dk = dv = 128).  The returned handle owns
+    its scratch memory; pass it to ``scan_recur`` any number of times."""
+    _lib.require_cuda(q, "scan_factors")
+    lib = _lib.load()
+    B, T, H, dk = q.shape
+    dv, Hkv = v.shape[-1], k.shape[2]
+    q, k, v = q.contiguous(), k.to(q.dtype).contiguous(), v.to(q.dtype).contiguous()
+    g, beta = g.float().contiguous(), beta.float().contiguous()
+    scratch = torch.empty(int(lib.atma_gated_delta_scan_scratch_bytes(B, T, H, dk, dv)), device=q.device, dtype=torch.uint8)
+    _lib.check(lib.atma_gated_delta_scan_factors(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.dtype_code(q), _lib.ptr(g),
+                                                 _lib.ptr(beta), _lib.ptr(scratch), B, T, H, Hkv, dk, dv,
+                                                 1 if use_qk_l2norm_in_kernel else 0, float(scale), _lib.stream_ptr()))
+    return ScanFactors(scratch, B, T, H, dk, dv, q.dtype, q.device)
+
+
+@torch.no_grad()
+def scan_recur(factors, rec_of, initial_state=None, zero_value=None, want_output=True):
+    """Second half: run ``len(rec_of)`` (<= 16) recurrences over ``factors``.  Recurrence i walks
+    the factors of sequence ``rec_of[i]`` from ``initial_state[i]`` ((n,H,dk,dv) fp32 or None).
+    ``zero_value[i]`` true runs it with v = 0 (started from the identity it yields the
+    state-transfer matrix of the segment).  Returns (o (n,T,H,dv) or None, final_state (n,H,dk,dv))."""
+    import ctypes
+    lib = _lib.load()
+    f = factors
+    n = len(rec_of)
+    rec_arr = (ctypes.c_int * n)(*[int(x) for x in rec_of])
+    zero_arr = (ctypes.c_int * n)(*[1 if (zero_value is not None and zero_value[i]) else 0 for i in range(n)])
+    if initial_state is not None:
+        initial_state = initial_state.float().contiguous()
+    o = torch.empty((n, f.T, f.H, f.dv), device=f.device, dtype=f.dtype) if want_output else None
+    final = torch.empty((n, f.H, f.dk, f.dv), device=f.device, dtype=torch.float32)
+    _lib.check(lib.atma_gated_delta_scan_recur(_lib.ptr(f.scratch), _lib.DTYPE_CODE[f.dtype], f.B, f.T, f.H, f.dk, f.dv, n,
+                                               rec_arr, zero_arr, _lib.ptr(initial_state), _lib.ptr(o), _lib.ptr(final),
+                                               _lib.stream_ptr()))
+    return o, final

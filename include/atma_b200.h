@@ -176,6 +176,28 @@ int atma_gated_delta_scan(const void* q, const void* k, const void* v, int dtype
                           int normalize_qk, float scale, void* stream);
 
 /* ------------------------------------------------------------------------------------
+ * The two halves of atma_gated_delta_scan, for a sequence that is split across GPUs.
+ * (The reference has no multi-GPU path; its single-device statement of the same hand-over is
+ * the chunked-prefill state carry of inference/models/atma.py:262-301.)
+ * _factors builds the state-independent per-chunk factors of B sequences into `scratch`
+ * (16-bit inputs, dk = dv = 128 only; arguments as atma_gated_delta_scan).
+ * _recur runs n_rec (<= 16) recurrences over those factors: recurrence i uses the factors of
+ * sequence rec_of[i] (host array, NULL = identity), starts from initial_state[i] (fp32
+ * [n_rec][H][dk][dv], NULL = zeros), writes o[i] ([n_rec][T][H][dv], NULL = no outputs) and
+ * final_state[i].  zero_u0[i] != 0 (host array, NULL = all 0) runs the recurrence with v = 0:
+ * started from the identity it returns the matrix P of the segment's affine state map
+ * S_out = P S_in + Q, while the plain recurrence started from zero returns Q.
+ * ---------------------------------------------------------------------------------- */
+int atma_gated_delta_scan_factors(const void* q, const void* k, const void* v, int dtype,
+                                  const float* g, const float* beta, void* scratch,
+                                  int B, int T, int H, int Hkv, int dk, int dv,
+                                  int normalize_qk, float scale, void* stream);
+int atma_gated_delta_scan_recur(void* scratch, int dtype, int B, int T, int H, int dk, int dv,
+                                int n_rec, const int* rec_of, const int* zero_u0,
+                                const float* initial_state, void* o, float* final_state,
+                                void* stream);
+
+/* ------------------------------------------------------------------------------------
  * Depthwise causal conv, one decode step, in place on a slot-indexed state table.
  * Replaces kernel/causal_conv1d_triton.py:17-42 behind causal_conv1d_decode_step (:46-63).
  * x, out [B][D] (row strides x_sb / out_sb), weight [D][K] dense, state [max_seqs][D][K-1]

@@ -26,8 +26,18 @@ class OracleBackend:
             return stats
         return polar_finalize(stats, n_keys, eps=eps, window=window, **params)
 
-    def scan(self, q, k, v, g, beta, initial_state):
-        return oracle.chunk_gated_delta_rule_oracle(q, k, v, g, beta, initial_state=initial_state, chunk=8)
+    def scan_factors(self, q, k, v, g, beta):
+        return (q, k, v, g, beta)
+
+    def scan_recur(self, factors, rec_of, initial_state, zero_value, want_output):
+        q, k, v, g, beta = factors
+        idx = torch.tensor(rec_of)
+        vv = v[idx].clone()
+        for i, z in enumerate(zero_value or []):
+            if z:
+                vv[i] = 0
+        o, S = oracle.chunk_gated_delta_rule_oracle(q[idx], k[idx], vv, g[idx], beta[idx], initial_state=initial_state, chunk=8)
+        return (o if want_output else None), S
 
 
 def _inputs(T, H, Hkv, dk):
