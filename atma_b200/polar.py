@@ -22,8 +22,27 @@ HAS_TRITON = torch.cuda.is_available()     # the flag the reference's callers ga
 HAS_CUDA_EXT = HAS_TRITON
 
 
+_param_cache = {}
+
+
 def _params(v_null, null_base, null_slope_raw, len_gain_raw, mag_beta_raw, device):
-    """softplus on the host, as kernel/polar_triton.py:540-544 does."""
+    """softplus on the host, as kernel/polar_triton.py:540-544 does.  The five small tensors are
+    prepared once per (storage, version) of the raw parameters and reused, so a decode step
+    launches nothing but its own kernels."""
+    raw = (v_null, null_base, null_slope_raw, len_gain_raw, mag_beta_raw)
+    key = tuple((t.data_ptr(), t._version, t.dtype, str(t.device)) for t in raw) + (str(device),)
+    hit = _param_cache.get(key)
+    if hit is not None:
+        return hit
+    if len(_param_cache) > 256:
+        _param_cache.clear()
+    out = _params_uncached(v_null, null_base, null_slope_raw, len_gain_raw, mag_beta_raw, device)
+    out["_raw"] = raw                       # keeps the storages alive, so the key cannot be recycled
+    _param_cache[key] = out
+    return out
+
+
+def _params_uncached(v_null, null_base, null_slope_raw, len_gain_raw, mag_beta_raw, device):
     return dict(
         spg=F.softplus(len_gain_raw.detach().float()).contiguous().to(device),
         sps=F.softplus(null_slope_raw.detach().float()).contiguous().to(device),
