@@ -12,7 +12,7 @@
 //   warps 2-3   idle (they complete the first warpgroup, whose registers are handed over)
 //   warps 4-7   softmax + epilogue of tile 0, one thread per query row (= one TMEM lane)
 //   warps 8-11  softmax + epilogue of tile 1
-// The first warpgroup shrinks to 40 registers per thread (setmaxnreg) so that each softmax
+// The first warpgroup shrinks to 72 registers per thread (setmaxnreg) so that each softmax
 // thread can hold its whole 128-column S row in registers.
 //
 // TMEM (512 columns): S_0 [0,128) S_1 [128,256) O_0 [256,384) O_1 [384,512); P_t (16-bit,
@@ -150,7 +150,7 @@ polar_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
   if (tid == 0) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bar.q_full[i], 1); mbar_init(&bar.s_full[i], 1);
-      mbar_init(&bar.p_full[i], 128); mbar_init(&bar.o_final[i], 1);
+      mbar_init(&bar.p_full[i], 4); mbar_init(&bar.o_final[i], 1);
     }
     for (int i = 0; i < kStages; ++i) {
       mbar_init(&bar.k_full[i], 1); mbar_init(&bar.k_empty[i], 1);
@@ -215,7 +215,7 @@ polar_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
   volatile int* abort_flag = &s_abort;
 
   if (warp < 4) {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
   if (warp == 0) {
     // =============================== TMA producer ================================================
     if (lane == 0) {
@@ -245,27 +245,28 @@ polar_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
       constexpr uint32_t idesc_pv = make_idesc(kBM, kDK, kBf16 ? 1 : 0, 0, 1);
       const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
       bool ok = true;
-      // Descriptors are rebuilt from the loop counter inside rolled loops: one thread issues an
-      // MMA every ~64 tensor cycles, so a few integer instructions per MMA cost nothing, while
-      // unrolled loops would keep dozens of loop-invariant 64-bit descriptors in registers.
+      // One thread issues all MMAs, so the issue sequence has to be short: the loops are unrolled
+      // and each descriptor is its tile's base descriptor plus a compile-time constant (the
+      // 14-bit address field cannot carry out: shared memory addresses stay below 256 KiB).
       const uint64_t desc_hi_k = (uint64_t(1024 >> 4) << 32) | (uint64_t(1) << 46) | (uint64_t(2) << 61) | (uint64_t(16 >> 4) << 16);
       const uint64_t desc_hi_v = (uint64_t(1024 >> 4) << 32) | (uint64_t(1) << 46) | (uint64_t(2) << 61) |
                                  (uint64_t((kTileBytes / 2) >> 4) << 16);
       auto issue_qk = [&](int t, int s) {
-        const uint32_t qa = (q_addr + t * kTileBytes) >> 4, ka = (k_addr + s * kTileBytes) >> 4;
-#pragma unroll 1
+        const uint64_t a0 = desc_hi_k | uint64_t(((q_addr + t * kTileBytes) >> 4) & 0x3FFFu);
+        const uint64_t b0 = desc_hi_k | uint64_t(((k_addr + s * kTileBytes) >> 4) & 0x3FFFu);
+#pragma unroll
         for (int kk = 0; kk < kDK / 16; ++kk) {
-          const uint32_t off = ((kk >> 2) * (kTileBytes / 2) + (kk & 3) * 32) >> 4;
-          mma_ss(tbase + t * 128, desc_hi_k | uint64_t((qa + off) & 0x3FFFu), desc_hi_k | uint64_t((ka + off) & 0x3FFFu),
-                 idesc_qk, kk > 0);
+          constexpr int dummy = 0; (void)dummy;
+          const uint64_t off = uint64_t(((kk >> 2) * (kTileBytes / 2) + (kk & 3) * 32) >> 4);   // compile-time constant
+          mma_ss(tbase + t * 128, a0 + off, b0 + off, idesc_qk, kk > 0);
         }
       };
       auto issue_pv = [&](int t, int s, bool acc) {
-        const uint32_t va = (v_addr + s * kTileBytes) >> 4;
-#pragma unroll 1
+        const uint64_t b0 = desc_hi_v | uint64_t(((v_addr + s * kTileBytes) >> 4) & 0x3FFFu);
+        const uint32_t pa = tbase + t * 128, od = tbase + 256 + t * 128;
+#pragma unroll
         for (int kk = 0; kk < kBN / 16; ++kk)
-          mma_ts(tbase + 256 + t * 128, tbase + t * 128 + kk * 8, desc_hi_v | uint64_t((va + kk * (2048 >> 4)) & 0x3FFFu),
-                 idesc_pv, (kk > 0 || acc) ? 1u : 0u);
+          mma_ts(od, pa + kk * 8, b0 + uint64_t(kk * (2048 >> 4)), idesc_pv, (kk > 0 || acc) ? 1u : 0u);
       };
       if (jmax > jmin) {
 #pragma unroll
@@ -316,7 +317,7 @@ polar_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
     __syncwarp();
   }
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
     // =============================== softmax + epilogue ===========================================
     const int t = sm_tile;
     const int h = t ? head[1] : head[0];
@@ -431,7 +432,8 @@ polar_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
       L += l0 + l1; Q2 += q0 + q1;
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(&bar.p_full[t]);
+      __syncwarp();                                                 // one arrival per warp, not per thread
+      if (lane == 0) mbar_arrive(&bar.p_full[t]);
       o_live = true;
     }
 
