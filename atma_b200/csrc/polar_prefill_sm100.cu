@@ -12,7 +12,7 @@
 //   warps 2-3   idle (they complete the first warpgroup, whose registers are handed over)
 //   warps 4-7   softmax + epilogue of tile 0, one thread per query row (= one TMEM lane)
 //   warps 8-11  softmax + epilogue of tile 1
-// The first warpgroup shrinks to 72 registers per thread (setmaxnreg) so that each softmax
+// The first warpgroup shrinks to 88 registers per thread (setmaxnreg) so that each softmax
 // thread can hold its whole 128-column S row in registers.
 //
 // TMEM (512 columns): S_0 [0,128) S_1 [128,256) O_0 [256,384) O_1 [384,512); P_t (16-bit,
@@ -215,7 +215,7 @@ polar_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
   volatile int* abort_flag = &s_abort;
 
   if (warp < 4) {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
   if (warp == 0) {
     // =============================== TMA producer ================================================
     if (lane == 0) {
@@ -317,7 +317,7 @@ polar_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
     __syncwarp();
   }
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
     // =============================== softmax + epilogue ===========================================
     const int t = sm_tile;
     const int h = t ? head[1] : head[0];
