@@ -38,6 +38,10 @@ H, HKV, DK, CHUNK = 8, 2, 128, 64
 T_PREFILL = 65536
 DEC_B, DEC_CTX, DEC_BLOCK = 64, 32768, 256
 METRIC = "global_layer_prefill_tok_s_at_64k"
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) from the committed ncu captures of the
+# small --profile cases (profiles/polar_prefill_sm100_T16384.md, profiles/polar_decode_b16_ctx16384.md).
+PREFILL_TRAFFIC_T16K = 53.1e6
+DECODE_TRAFFIC_RATIO = 273.3 / 268.4
 
 
 def measured_peaks():
@@ -189,7 +193,10 @@ def bench_decode(ab, device, steps, warmup, peaks):
         "ms_per_step": ms, "config": {"batch": DEC_B, "context": DEC_CTX, "block_size": DEC_BLOCK, "layers": 1},
         "roofline": {"kernel": "polar_decode (split + merge)", "bound": "hbm",
                      "achieved": kv_bytes / (polar_ms * 1e-3) / 1e9, "peak": peaks["hbm"], "unit": "GB/s",
-                     "frac": kv_bytes / (polar_ms * 1e-3) / 1e9 / peaks["hbm"], "traffic": None,
+                     "frac": kv_bytes / (polar_ms * 1e-3) / 1e9 / peaks["hbm"],
+                     # ncu capture at B=16 x 16K context: 273.3 MB moved for 268.4 MB algorithmic (x1.018);
+                     # traffic is proportional to the cache bytes, so it is scaled to this launch.
+                     "traffic": kv_bytes * DECODE_TRAFFIC_RATIO,
                      "algorithmic_bytes": kv_bytes, "kernel_ms": polar_ms, "peak_source": peaks["source"]},
         "step_bytes": kv_bytes + state_bytes,
         "step_hbm_frac": (kv_bytes + state_bytes) / (ms * 1e-3) / 1e9 / peaks["hbm"],
@@ -353,8 +360,10 @@ def run_context_parallel(args, ab, rank, local_rank, world, device, peaks):
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
+    h0 = time.perf_counter()
     for i in range(args.steps):
         step(dev_shard, ev[i])
+    host_enqueue_ms = (time.perf_counter() - h0) * 1e3 / args.steps
     e1.record()
     barrier()
     clocks = sampler.stop()
@@ -416,6 +425,7 @@ def run_context_parallel(args, ab, rank, local_rank, world, device, peaks):
                      "traffic": None, "algorithmic_flops": polar_flops(T_PREFILL), "kernel_ms": polar_ms,
                      "peak_source": peaks["source"] + f" burst x {world} GPUs"},
         "scan": {"kernel_ms": scan_ms, "algorithmic_flops": scan_flops(T_PREFILL)},
+        "host_enqueue_ms": host_enqueue_ms,
         "cpu_baseline": None,
         "decode": decode,
     }
@@ -425,8 +435,8 @@ def run_context_parallel(args, ab, rank, local_rank, world, device, peaks):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=5)
-    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline leg (profiling runs)")
     ap.add_argument("--skip-decode", action="store_true", help="omit the decode leg (profiling runs)")
@@ -484,35 +494,35 @@ def main():
     scan_ms = sum(e[2].elapsed_time(e[3]) for e in ev) / args.steps
     # the same kernels one after the other on one stream, for the isolated kernel durations
     from atma_b200.mixing import global_layer_mixing
-    iso = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(3)]
+    iso = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(7)]
     for e in iso:
         global_layer_mixing(dev_in["q"], dev_in["k"], dev_in["v"], dev_in["g"], dev_in["beta"], n_keys, params,
                             overlap=False, events=e)
     torch.cuda.synchronize()
-    polar_iso_ms = sum(e[0].elapsed_time(e[1]) for e in iso) / len(iso)
-    scan_iso_ms = sum(e[2].elapsed_time(e[3]) for e in iso) / len(iso)
+    polar_iso_all = sorted(e[0].elapsed_time(e[1]) for e in iso)
+    polar_iso_ms = polar_iso_all[len(iso) // 2]                     # median
+    scan_iso_ms = sorted(e[2].elapsed_time(e[3]) for e in iso)[len(iso) // 2]
 
     # ---- end to end: pinned host inputs in, results out, inside the timed region ------------------
-    out_host = None
-
-    def e2e_step():
-        nonlocal out_host
-        t = {n: x.to(device, non_blocking=True) for n, x in host.items()}
-        c, mag, o, S = prefill_step(ab, t, n_keys, params)
-        if out_host is None:
-            out_host = [torch.empty(x.shape, dtype=x.dtype, pin_memory=True) for x in (c, mag, o, S)]
-        for dst, src in zip(out_host, (c, mag, o, S)):
-            dst.copy_(src, non_blocking=True)
-
-    for _ in range(2):
-        e2e_step()
+    # Public API for host-resident activations: a three-stream pipeline (copy in | kernels | copy out);
+    # every step copies its own inputs from pinned memory and returns all four results to pinned memory.
+    from atma_b200.mixing import HostFedMixing
+    hosts = [host, make_prefill_inputs(seed=104 + rank, pinned=True)]
+    pipe = HostFedMixing(device)
+    for i in range(4):
+        pipe.submit(hosts[i % 2], n_keys, params)
+    pipe.drain()
     barrier()
     s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     s0.record()
-    for _ in range(args.steps):
-        e2e_step()
+    for s_ in (pipe.copy_in, pipe.compute, pipe.copy_out):
+        s_.wait_event(s0)
+    for i in range(args.steps):
+        ticket = pipe.submit(hosts[i % 2], n_keys, params)
+    pipe.drain()
     s1.record()
     barrier()
+    out_host = pipe.results(ticket)
     e2e_ms = s0.elapsed_time(s1) / args.steps
     h2d = sum(x.numel() * x.element_size() for x in host.values())
     d2h = sum(x.numel() * x.element_size() for x in out_host)
@@ -557,13 +567,17 @@ def main():
                    "window": None, "l2": "inputs (268 MB) larger than L2 (126 MB)",
                    "polar_kernel": "tcgen05" if tensor_path else "cuda-core fp32"},
         "e2e": {"value": world * T_PREFILL / (e2e_ms * 1e-3), "unit": "tok/s", "ms_per_step": e2e_ms,
+                "api": "atma_b200.mixing.HostFedMixing.submit (copy-in | kernels | copy-out streams, double buffered)",
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": 3 * args.steps,
         "clocks": clocks,
         "roofline": {"kernel": "polar_prefill", "bound": "tensor", "achieved": achieved_tf, "peak": peak_tf,
-                     "unit": "TFLOP/s", "frac": achieved_tf / peak_tf, "traffic": None,
+                     "unit": "TFLOP/s", "frac": achieved_tf / peak_tf,
+                     # ncu capture at T=16384: 53.1 MB of DRAM traffic (inputs read once, most of the output
+                     # still in L2 when the kernel ends); scaled by the token count to this launch.
+                     "traffic": PREFILL_TRAFFIC_T16K * (T_PREFILL / 16384),
                      "algorithmic_flops": polar_flops(T_PREFILL), "kernel_ms": polar_ms,
-                     "kernel_ms_alone": polar_iso_ms,
+                     "kernel_ms_alone": polar_iso_ms, "kernel_ms_alone_all": polar_iso_all,
                      "frac_alone": polar_flops(T_PREFILL) / (polar_iso_ms * 1e-3) / 1e12 / peak_tf,
                      "note": "kernel_ms is measured inside the timed region, where the gated-delta recurrence runs "
                              "beside this kernel on a second stream and takes some SMs; kernel_ms_alone is the same "
