@@ -240,12 +240,105 @@ def shard_sequence(t, rank, world):
                             positions=[(a0, a1), (b0, b1)])
 
 
+_side = {}
+
+
+def _side_resources(device, group):
+    """A high-priority stream for the memory branch and a second communicator for its all-gather,
+    so that the gather does not queue behind the ring's send/recv on the first communicator's
+    stream.  Created once per (device, group); every rank must reach the first call together."""
+    key = (device.index, id(group))
+    if key not in _side:
+        ranks = dist.get_process_group_ranks(group) if group is not None else None
+        _side[key] = (torch.cuda.Stream(device=device, priority=-1), dist.new_group(ranks=ranks, backend="nccl"))
+    return _side[key]
+
+
 @torch.no_grad()
-def cp_global_layer_prefill(shard, params, *, backend=None, group=None):
+def cp_global_layer_prefill(shard, params, *, backend=None, group=None, overlap=None):
     """Polar ring pass + gated-delta prefix scan for one rank's shard.  Returns
-    ([(c, mag) lo, hi], [o lo, hi], final memory state)."""
+    ([(c, mag) lo, hi], [o lo, hi], final memory state).  On CUDA tensors the memory branch runs
+    beside the ring on a side stream (``overlap``, default on for CUDA)."""
     tr = lambda x: x.transpose(1, 2)
+    dev = shard.q[0].device
+    if overlap is None:
+        overlap = dev.type == "cuda"
+    if overlap:
+        cur = torch.cuda.current_stream(dev)
+        side, scan_group = _side_resources(dev, group)
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            o, S = cp_gated_delta_scan(shard.q, shard.k, shard.v, shard.g, shard.beta, backend=backend,
+                                       group=scan_group)
     polar = ring_polar_prefill([tr(x) for x in shard.q], [tr(x) for x in shard.k], [tr(x) for x in shard.v],
                                shard.positions, params, backend=backend, group=group)
-    o, S = cp_gated_delta_scan(shard.q, shard.k, shard.v, shard.g, shard.beta, backend=backend, group=group)
+    if overlap:
+        cur.wait_stream(side)
+        for t in (*o, S):
+            t.record_stream(cur)
+    else:
+        o, S = cp_gated_delta_scan(shard.q, shard.k, shard.v, shard.g, shard.beta, backend=backend, group=group)
     return polar, o, S
+
+
+class CapturedPrefill:
+    """``cp_global_layer_prefill`` for one fixed shard shape, captured into a CUDA graph.
+
+    At 8 ranks a 64K-token step is about forty short launches and a dozen NCCL calls per rank;
+    issued one by one from Python the host is slower than the GPU.  Capturing the step (kernels,
+    ring send/recv, the state all-gather, both streams) and replaying it removes the host from
+    the step.  Every rank must construct the object and call ``replay`` the same number of times.
+
+    ``static`` is the shard the graph reads: fill its tensors (``load``, or copy into them from
+    pinned host memory) and call ``replay``; the returned tensors are owned by the graph and are
+    overwritten by the next replay.
+    """
+
+    def __init__(self, shard, params, *, group=None, warmup=3):
+        dev = shard.q[0].device
+        self.group = group
+        self.static = GlobalLayerShard(positions=list(shard.positions),
+                                       **{f: [x.clone() for x in getattr(shard, f)]
+                                          for f in ("q", "k", "v", "g", "beta")})
+        self.params = params
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):                      # warm up off the default stream: lazy
+            for _ in range(warmup):                        # initialisation must not land in the capture
+                cp_global_layer_prefill(self.static, params, group=group)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        dist.barrier(group=group)
+        self.graph = torch.cuda.CUDAGraph()
+        ok = 1
+        try:
+            with torch.cuda.graph(self.graph, capture_error_mode="thread_local"):
+                self.outputs = cp_global_layer_prefill(self.static, params, group=group)
+        except Exception as exc:                           # noqa: BLE001 - reported, then agreed on below
+            ok, self.error = 0, exc
+        flag = torch.tensor([ok], device=dev, dtype=torch.int32)
+        torch.cuda.synchronize(dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+        self.captured = bool(flag.item())                  # all ranks replay, or all run eagerly
+        if not self.captured:
+            self.graph = None
+
+    def close(self):
+        """Release the graph (and the NCCL work captured in it).  Call it on every rank before the
+        process group is destroyed."""
+        self.outputs = None
+        if self.graph is not None:
+            self.graph.reset()
+            self.graph = None
+        self.captured = False
+
+    def load(self, shard):
+        for f in ("q", "k", "v", "g", "beta"):
+            for dst, src in zip(getattr(self.static, f), getattr(shard, f)):
+                dst.copy_(src, non_blocking=True)
+
+    def replay(self):
+        if self.captured:
+            self.graph.replay()
+            return self.outputs
+        return cp_global_layer_prefill(self.static, self.params, group=self.group)

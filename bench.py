@@ -250,7 +250,7 @@ def run_reference(args, rank):
             "cpu_baseline": {"value": val, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample},
             "e2e": {"value": val, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
-    print(json.dumps(line))
+    emit(line)
 
 
 def profile_case(which):
@@ -296,7 +296,7 @@ def profile_case(which):
         info = {"kernel": "scan_local_mma_kernel + scan_seq_mma_kernel", "B": B, "T": T,
                 "flops_per_launch": scan_flops(T) * B}
     torch.cuda.synchronize()
-    print(json.dumps({"profile": which, **info}))
+    emit({"profile": which, **info})
 
 
 def bench_decode_sharded(ab, device, steps, warmup, peaks, world, dist):
@@ -352,30 +352,54 @@ def run_context_parallel(args, ab, rank, local_rank, world, device, peaks):
         torch.cuda.synchronize()
 
     dev_shard = to_dev()
+    # (1) un-overlapped eager pass: the ring and the memory branch one after the other, for the
+    #     per-branch durations the roofline entry quotes
     for _ in range(args.warmup):
         step(dev_shard)
+    barrier()
+    n_eager = max(3, min(args.steps, 10))
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(n_eager)]
+    h0 = time.perf_counter()
+    for i in range(n_eager):
+        step(dev_shard, ev[i])
+    host_enqueue_ms = (time.perf_counter() - h0) * 1e3 / n_eager
+    barrier()
+    polar_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / n_eager
+    scan_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / n_eager
+
+    # (2) the timed step: the public entry (memory branch beside the ring), replayed from a CUDA
+    #     graph unless --no-graph
+    if args.no_graph:
+        run_step = lambda: cp.cp_global_layer_prefill(dev_shard, params)
+        static, graph_used = dev_shard, False
+    else:
+        cap = cp.CapturedPrefill(dev_shard, params)
+        run_step, static, graph_used = cap.replay, cap.static, cap.captured
+        if not cap.captured and rank == 0:
+            print(f"[bench] graph capture failed, running eagerly: {getattr(cap, 'error', None)!r}", file=sys.stderr)
+    for _ in range(args.warmup):
+        run_step()
     sampler = ClockSampler(local_rank)
     barrier()
     sampler.start()
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    h0 = time.perf_counter()
     for i in range(args.steps):
-        step(dev_shard, ev[i])
-    host_enqueue_ms = (time.perf_counter() - h0) * 1e3 / args.steps
+        run_step()
     e1.record()
     barrier()
     clocks = sampler.stop()
     ms = e0.elapsed_time(e1) / args.steps
-    polar_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / args.steps
-    scan_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / args.steps
 
+    # (3) end to end: pinned host shard -> the step's input buffers, step, all results -> pinned host
     out_host = None
 
     def e2e_step():
         nonlocal out_host
-        polar, o, S = step(to_dev())
+        for f in fields:
+            for dst, src in zip(getattr(static, f), host[f]):
+                dst.copy_(src, non_blocking=True)
+        polar, o, S = run_step()
         outs = [polar[0][0], polar[0][1], polar[1][0], polar[1][1], o[0], o[1], S]
         if out_host is None:
             out_host = [torch.empty(x.shape, dtype=x.dtype, pin_memory=True) for x in outs]
@@ -400,7 +424,10 @@ def run_context_parallel(args, ab, rank, local_rank, world, device, peaks):
     bytes_t = torch.tensor([h2d, d2h], device=device, dtype=torch.float64)
     dist.all_reduce(bytes_t)
     h2d, d2h = bytes_t.tolist()
-    del dev_shard
+    del dev_shard, static, run_step
+    if not args.no_graph:
+        cap.close()
+        del cap
     torch.cuda.empty_cache()
     decode = None if args.skip_decode else bench_decode_sharded(ab, device, max(args.steps, 10), args.warmup, peaks, world, dist)
     dist.barrier()
@@ -423,21 +450,43 @@ def run_context_parallel(args, ab, rank, local_rank, world, device, peaks):
         "roofline": {"kernel": "polar_prefill (ring pass, all ranks)", "bound": "tensor", "achieved": achieved_tf,
                      "peak": peaks["tf_burst"] * world, "unit": "TFLOP/s", "frac": achieved_tf / (peaks["tf_burst"] * world),
                      "traffic": None, "algorithmic_flops": polar_flops(T_PREFILL), "kernel_ms": polar_ms,
+                     "note": "kernel_ms = the whole ring pass (all block launches and the hops between them) of an "
+                             "un-overlapped eager run, max over ranks",
                      "peak_source": peaks["source"] + f" burst x {world} GPUs"},
         "scan": {"kernel_ms": scan_ms, "algorithmic_flops": scan_flops(T_PREFILL)},
-        "host_enqueue_ms": host_enqueue_ms,
+        "host_enqueue_ms_eager": host_enqueue_ms, "cuda_graph": graph_used,
         "cpu_baseline": None,
         "decode": decode,
     }
-    print(json.dumps(line))
+    emit(line)
+
+
+_REAL_STDOUT = None
+
+
+def emit(obj):
+    """The one JSON line goes to the process's original stdout; everything else that libraries
+    write to file descriptor 1 while the bench runs (NCCL's version banner, ...) goes to stderr."""
+    data = (json.dumps(obj) + "\n").encode()
+    if _REAL_STDOUT is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_REAL_STDOUT, data)
 
 
 def main():
+    global _REAL_STDOUT
+    sys.stdout.flush()
+    _REAL_STDOUT = os.dup(1)
+    os.dup2(2, 1)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-graph", action="store_true",
+                    help="N > 1: issue the context-parallel step launch by launch instead of replaying a CUDA graph")
     ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline leg (profiling runs)")
     ap.add_argument("--skip-decode", action="store_true", help="omit the decode leg (profiling runs)")
     ap.add_argument("--profile", default=None, choices=["prefill", "decode", "scan"],
@@ -589,7 +638,7 @@ def main():
         "cpu_baseline": cpu,
         "decode": decode,
     }
-    print(json.dumps(line))
+    emit(line)
 
 
 if __name__ == "__main__":

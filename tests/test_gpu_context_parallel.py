@@ -3,6 +3,7 @@ the single-GPU result - Polar ring with statistics carry, gated-delta state pref
 
 import os
 import socket
+import time
 
 import pytest
 import torch
@@ -37,10 +38,31 @@ def _worker(rank, world, port, ret):
         tg = {n: x.to(dev) for n, x in t.items()}
         pg = {n: x.to(dev) for n, x in params.items()}
         shard = cp.shard_sequence(tg, rank, world)
-        polar, o, S = cp.cp_global_layer_prefill(shard, pg)
+        polar, o, S = cp.cp_global_layer_prefill(shard, pg)          # memory branch beside the ring
         torch.cuda.synchronize()
         ret[rank] = dict(pos=shard.positions, c=[p[0].float().cpu() for p in polar], mag=[p[1].float().cpu() for p in polar],
                          o=[x.float().cpu() for x in o], S=S.float().cpu())
+        # the same step replayed from a CUDA graph, twice, with the inputs reloaded in between,
+        # must give exactly what the launch-by-launch step gave
+        ret[f"stage{rank}"] = "launch-by-launch step done"
+        cap = cp.CapturedPrefill(shard, pg)
+        ret[f"stage{rank}"] = f"capture returned (captured={cap.captured}, error={getattr(cap, 'error', None)!r})"
+        same = cap.captured
+        for _ in range(2):
+            for f in ("q", "k", "v", "g", "beta"):
+                for x in getattr(cap.static, f):
+                    x.zero_()
+            cap.load(shard)
+            polar2, o2, S2 = cap.replay()
+            torch.cuda.synchronize()
+            same = same and all(torch.equal(a[0], b[0]) and torch.equal(a[1], b[1]) for a, b in zip(polar, polar2))
+            same = same and all(torch.equal(a, b) for a, b in zip(o, o2)) and torch.equal(S, S2)
+        ret[f"graph{rank}"] = bool(same)
+        ret[f"stage{rank}"] = "replays done"
+        del polar2, o2, S2
+        cap.close()
+        torch.cuda.synchronize()
+        ret[f"stage{rank}"] = "graph released"
     finally:
         dist.destroy_process_group()
 
@@ -60,7 +82,13 @@ def test_two_rank_context_parallel_matches_one_gpu():
     c_ref, m_ref, o_ref, S_ref = (x.float().cpu() for x in (c_ref, m_ref, o_ref, S_ref))
     s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
     ret = mp.Manager().dict()
-    mp.spawn(_worker, args=(world, port, ret), nprocs=world, join=True)
+    ctx = mp.spawn(_worker, args=(world, port, ret), nprocs=world, join=False)
+    deadline = time.time() + 150
+    while not ctx.join(timeout=5):
+        if time.time() > deadline:                  # never leave ranks waiting on one another
+            for p in ctx.processes:
+                p.kill()
+            pytest.fail(f"context-parallel ranks did not finish in time; stages: {[ret.get(f'stage{r}') for r in range(world)]}")
     rel = lambda a, b: float((a - b).abs().max() / b.abs().max().clamp_min(1e-12))
     for rank in range(world):
         r = ret[rank]
@@ -69,3 +97,4 @@ def test_two_rank_context_parallel_matches_one_gpu():
             assert rel(r["mag"][part], m_ref[:, :, a:b]) < 2e-2
             assert rel(r["o"][part], o_ref[:, a:b]) < 2e-2
         assert rel(r["S"], S_ref[0]) < 2e-2
+        assert ret[f"graph{rank}"], "graph replay differs from the launch-by-launch step (or capture failed)"
