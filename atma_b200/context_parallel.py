@@ -143,6 +143,72 @@ def ring_polar_prefill(q_parts, k_parts, v_parts, positions, params, *, backend=
     return out
 
 
+@torch.no_grad()
+def gathered_polar_prefill(q_parts, k_parts, v_parts, positions, params, *, backend=None, group=None,
+                           eps=1e-6, window=None):
+    """Same contract as ``ring_polar_prefill``, for sequences whose K/V fit every GPU: one
+    all-gather brings the un-expanded K/V of the whole sequence into local HBM (token order),
+    then each query segment is ONE kernel launch over the keys it can see (absolute key counts
+    do the masking).  Two launches per rank instead of 2N+1 and no statistics carried through
+    memory; the launch of the later (longer) segment is issued first and the other one runs
+    beside it on a second stream."""
+    backend = backend or CudaBackend()
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    dev = q_parts[0].device
+    Hkv, L, dk = k_parts[0].shape[1], k_parts[0].shape[2], k_parts[0].shape[3]
+    prepared = backend.prepare_params(params, dev)
+    # token-major send buffer (part, k|v, L, Hkv, dk); the gathered slots (rank, part) are put in
+    # sequence order with one index_select per tensor
+    mine = torch.stack([torch.stack([k_parts[p][0].transpose(0, 1), v_parts[p][0].transpose(0, 1)]) for p in (0, 1)])
+    flat = torch.empty((2 * world, 2, L, Hkv, dk), dtype=mine.dtype, device=dev)    # slot 2*rank + part
+    dist.all_gather_into_tensor(flat, mine.contiguous(), group=group)
+    slot_of_seg = _slot_index(world, dev)
+    k_all = flat[:, 0].index_select(0, slot_of_seg).view(2 * world * L, Hkv, dk)
+    v_all = flat[:, 1].index_select(0, slot_of_seg).view(2 * world * L, Hkv, dk)
+
+    def run(part):
+        p0, p1 = positions[part]
+        n_keys = torch.arange(p0 + 1, p1 + 1, device=dev, dtype=torch.float32)
+        kv = lambda x: x[:p1].unsqueeze(0).transpose(1, 2)           # (1, Hkv, visible keys, dk) view
+        return backend.polar_block(q_parts[part], kv(k_all), kv(v_all), n_keys, prepared, 0, None, True, eps, window)
+
+    if dev.type != "cuda":
+        return [run(0), run(1)]
+    cur = torch.cuda.current_stream(dev)
+    second = _second_stream(dev)
+    out_hi = run(1)                                                  # long rows first
+    second.wait_stream(cur)                                          # k_all, v_all are ready
+    with torch.cuda.stream(second):
+        out_lo = run(0)
+    cur.wait_stream(second)
+    for t in out_lo:
+        t.record_stream(cur)
+    k_all.record_stream(second)
+    v_all.record_stream(second)
+    return [out_lo, out_hi]
+
+
+_second = {}
+_slots = {}
+
+
+def _slot_index(world, device):
+    """Gathered slot (2*rank + part) of every segment in sequence order; cached per device so that
+    no host-to-device copy happens inside a captured step."""
+    key = (world, device)
+    if key not in _slots:
+        _slots[key] = torch.tensor([2 * segment_owner(i, world) + (0 if i < world else 1) for i in range(2 * world)],
+                                   device=device)
+    return _slots[key]
+
+
+def _second_stream(device):
+    if device.index not in _second:
+        _second[device.index] = torch.cuda.Stream(device=device)
+    return _second[device.index]
+
+
 def compose_state_prefix(P_all, Q_all, S0=None):
     """S_in of every segment from the per-segment affine maps, in time order.
     P_all (n_seg, H, dk, dk) and Q_all (n_seg, H, dk, dv) in the [K,V] state layout:
@@ -254,11 +320,17 @@ def _side_resources(device, group):
     return _side[key]
 
 
+GATHER_LIMIT_BYTES = 8 << 30
+
+
 @torch.no_grad()
-def cp_global_layer_prefill(shard, params, *, backend=None, group=None, overlap=None):
-    """Polar ring pass + gated-delta prefix scan for one rank's shard.  Returns
+def cp_global_layer_prefill(shard, params, *, backend=None, group=None, overlap=None, polar_mode=None):
+    """Polar pass + gated-delta prefix scan for one rank's shard.  Returns
     ([(c, mag) lo, hi], [o lo, hi], final memory state).  On CUDA tensors the memory branch runs
-    beside the ring on a side stream (``overlap``, default on for CUDA)."""
+    beside the attention on a side stream (``overlap``, default on for CUDA).  ``polar_mode``:
+    "gather" (all-gather K/V, one launch per query segment), "ring" (K/V blocks travel a ring,
+    2N+1 launches with carried statistics; memory per GPU stays O(T/N)), default: gather while
+    the whole sequence's K/V is below ``GATHER_LIMIT_BYTES``."""
     tr = lambda x: x.transpose(1, 2)
     dev = shard.q[0].device
     if overlap is None:
@@ -270,8 +342,15 @@ def cp_global_layer_prefill(shard, params, *, backend=None, group=None, overlap=
         with torch.cuda.stream(side):
             o, S = cp_gated_delta_scan(shard.q, shard.k, shard.v, shard.g, shard.beta, backend=backend,
                                        group=scan_group)
-    polar = ring_polar_prefill([tr(x) for x in shard.q], [tr(x) for x in shard.k], [tr(x) for x in shard.v],
-                               shard.positions, params, backend=backend, group=group)
+    if polar_mode is None:
+        world = dist.get_world_size(group)
+        kv_bytes = 2 * world * sum(x.numel() * x.element_size() for x in (*shard.k, *shard.v))
+        polar_mode = "gather" if kv_bytes <= GATHER_LIMIT_BYTES else "ring"
+    if polar_mode not in ("gather", "ring"):
+        raise ValueError(f"polar_mode must be 'gather' or 'ring', not {polar_mode!r}")
+    polar_fn = gathered_polar_prefill if polar_mode == "gather" else ring_polar_prefill
+    polar = polar_fn([tr(x) for x in shard.q], [tr(x) for x in shard.k], [tr(x) for x in shard.v],
+                     shard.positions, params, backend=backend, group=group)
     if overlap:
         cur.wait_stream(side)
         for t in (*o, S):
@@ -294,9 +373,10 @@ class CapturedPrefill:
     overwritten by the next replay.
     """
 
-    def __init__(self, shard, params, *, group=None, warmup=3):
+    def __init__(self, shard, params, *, group=None, warmup=3, polar_mode=None):
         dev = shard.q[0].device
         self.group = group
+        self.polar_mode = polar_mode
         self.static = GlobalLayerShard(positions=list(shard.positions),
                                        **{f: [x.clone() for x in getattr(shard, f)]
                                           for f in ("q", "k", "v", "g", "beta")})
@@ -305,17 +385,23 @@ class CapturedPrefill:
         side.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(side):                      # warm up off the default stream: lazy
             for _ in range(warmup):                        # initialisation must not land in the capture
-                cp_global_layer_prefill(self.static, params, group=group)
+                cp_global_layer_prefill(self.static, params, group=group, polar_mode=polar_mode)
         torch.cuda.current_stream(dev).wait_stream(side)
         torch.cuda.synchronize(dev)
         dist.barrier(group=group)
         self.graph = torch.cuda.CUDAGraph()
         ok = 1
+        self.error = None
         try:
             with torch.cuda.graph(self.graph, capture_error_mode="thread_local"):
-                self.outputs = cp_global_layer_prefill(self.static, params, group=group)
+                try:
+                    self.outputs = cp_global_layer_prefill(self.static, params, group=group, polar_mode=polar_mode)
+                except Exception as inner:                 # noqa: BLE001 - keep the first error: ending the
+                    self.error = inner                     # capture after it reports "unjoined work" instead
+                    raise
         except Exception as exc:                           # noqa: BLE001 - reported, then agreed on below
-            ok, self.error = 0, exc
+            ok = 0
+            self.error = self.error or exc
         flag = torch.tensor([ok], device=dev, dtype=torch.int32)
         torch.cuda.synchronize(dev)
         dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
@@ -341,4 +427,4 @@ class CapturedPrefill:
         if self.captured:
             self.graph.replay()
             return self.outputs
-        return cp_global_layer_prefill(self.static, self.params, group=self.group)
+        return cp_global_layer_prefill(self.static, self.params, group=self.group, polar_mode=self.polar_mode)

@@ -440,12 +440,15 @@ def run_context_parallel(args, ab, rank, local_rank, world, device, peaks):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": "global-layer mixing prefill: Polar attention + gated-delta scan, ONE 65536-token sequence "
-                               "context-parallel over the GPUs (zig-zag segments, NCCL ring of K/V blocks, state prefix)",
+                               "context-parallel over the GPUs (zig-zag segments, K/V all-gathered over NVLink, one Polar launch per "
+                               "query segment, gated-delta state handed over as an affine-map prefix)",
                    "tokens": T_PREFILL, "heads": H, "kv_heads": HKV, "head_dim": DK, "chunk": CHUNK, "window": None,
                    "l2": "per-GPU inputs shrink with N; at N=8 they are 34 MB, below L2", "polar_kernel": "tcgen05"},
         "e2e": {"value": T_PREFILL / (e2e_ms * 1e-3), "unit": "tok/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-        "gpu_launches": args.steps * (2 * world + 1 + 4),
+        # per rank and step: 2 Polar launches (one per query segment), the chunk-factor kernel and
+        # 2 recurrence launches of this library; NCCL and torch's small copy kernels are not counted
+        "gpu_launches": args.steps * 5 * world,
         "clocks": clocks,
         "roofline": {"kernel": "polar_prefill (ring pass, all ranks)", "bound": "tensor", "achieved": achieved_tf,
                      "peak": peaks["tf_burst"] * world, "unit": "TFLOP/s", "frac": achieved_tf / (peaks["tf_burst"] * world),

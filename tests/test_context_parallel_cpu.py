@@ -53,7 +53,7 @@ def _inputs(T, H, Hkv, dk):
     return t, params, x
 
 
-def _worker(rank, world, port, T, ret):
+def _worker(rank, world, port, T, mode, ret):
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
@@ -61,7 +61,7 @@ def _worker(rank, world, port, T, ret):
         H, Hkv, dk = 4, 2, 16
         t, params, x = _inputs(T, H, Hkv, dk)
         shard = cp.shard_sequence(t, rank, world)
-        polar, o, S = cp.cp_global_layer_prefill(shard, params, backend=OracleBackend())
+        polar, o, S = cp.cp_global_layer_prefill(shard, params, backend=OracleBackend(), polar_mode=mode)
         halos = cp.cp_conv_halos([x[a:b] for a, b in shard.positions], 4)
         ret[rank] = dict(pos=shard.positions, c=[p[0] for p in polar], mag=[p[1] for p in polar], o=o, S=S, halos=halos)
     finally:
@@ -76,8 +76,8 @@ def _free_port():
     return port
 
 
-@pytest.mark.parametrize("world,T", [(2, 64), (3, 96)])
-def test_context_parallel_matches_single_process(world, T):
+@pytest.mark.parametrize("world,T,mode", [(2, 64, "ring"), (3, 96, "ring"), (2, 64, "gather"), (3, 96, "gather")])
+def test_context_parallel_matches_single_process(world, T, mode):
     H, Hkv, dk = 4, 2, 16
     t, params, x = _inputs(T, H, Hkv, dk)
     n = torch.arange(1, T + 1, dtype=torch.float32)
@@ -86,7 +86,7 @@ def test_context_parallel_matches_single_process(world, T):
     o_ref, S_ref = oracle.chunk_gated_delta_rule_oracle(t["q"], ke, ve, t["g"], t["beta"], chunk=8)
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_worker, args=(world, _free_port(), T, ret), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), T, mode, ret), nprocs=world, join=True)
     assert len(ret) == world
     for rank in range(world):
         r = ret[rank]

@@ -38,14 +38,18 @@ def _worker(rank, world, port, ret):
         tg = {n: x.to(dev) for n, x in t.items()}
         pg = {n: x.to(dev) for n, x in params.items()}
         shard = cp.shard_sequence(tg, rank, world)
-        polar, o, S = cp.cp_global_layer_prefill(shard, pg)          # memory branch beside the ring
+        polar, o, S = cp.cp_global_layer_prefill(shard, pg, polar_mode="ring")   # memory branch beside the ring
         torch.cuda.synchronize()
+        pol_g, o_g, S_g = cp.cp_global_layer_prefill(shard, pg, polar_mode="gather")
+        torch.cuda.synchronize()
+        ret[f"gather{rank}"] = dict(c=[p[0].float().cpu() for p in pol_g], mag=[p[1].float().cpu() for p in pol_g])
         ret[rank] = dict(pos=shard.positions, c=[p[0].float().cpu() for p in polar], mag=[p[1].float().cpu() for p in polar],
                          o=[x.float().cpu() for x in o], S=S.float().cpu())
         # the same step replayed from a CUDA graph, twice, with the inputs reloaded in between,
         # must give exactly what the launch-by-launch step gave
         ret[f"stage{rank}"] = "launch-by-launch step done"
-        cap = cp.CapturedPrefill(shard, pg)
+        polar, o, S = pol_g, o_g, S_g
+        cap = cp.CapturedPrefill(shard, pg, polar_mode="gather")
         ret[f"stage{rank}"] = f"capture returned (captured={cap.captured}, error={getattr(cap, 'error', None)!r})"
         same = cap.captured
         for _ in range(2):
@@ -96,5 +100,7 @@ def test_two_rank_context_parallel_matches_one_gpu():
             assert rel(r["c"][part], c_ref[:, :, a:b]) < 2e-2
             assert rel(r["mag"][part], m_ref[:, :, a:b]) < 2e-2
             assert rel(r["o"][part], o_ref[:, a:b]) < 2e-2
+            assert rel(ret[f"gather{rank}"]["c"][part], c_ref[:, :, a:b]) < 2e-2
+            assert rel(ret[f"gather{rank}"]["mag"][part], m_ref[:, :, a:b]) < 2e-2
         assert rel(r["S"], S_ref[0]) < 2e-2
         assert ret[f"graph{rank}"], "graph replay differs from the launch-by-launch step (or capture failed)"
