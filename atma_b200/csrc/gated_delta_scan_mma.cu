@@ -4,9 +4,10 @@
 //   per chunk, independent of the state:  -W = -T diag(beta g) K,  U0 = T diag(beta) V,
 //       Qg = diag(g) Q,  Kt = diag(g_C/g) K,  Rq = tril((g_p/g_s) q_p.k_s),  T = (I + A)^-1
 //   per chunk, on the state S [dk][dv]:    U = U0 - W S;  O = Qg S + Rq U;  S <- g_C S + Kt^T U
-// Kernel A (one CTA per chunk) forms K K^T and Q K^T with mma.sync, inverts the unit lower
-// triangular 64x64 system in fp32 (16x16 diagonal blocks by substitution, then two levels of
-// block merges), and forms W and U0 with mma.sync; all factors go to scratch as 16-bit tiles.
+// Kernel A (one CTA per chunk) forms K K^T and Q K^T with mma.sync, inverts the four 16x16
+// diagonal blocks of the unit lower triangular system in fp32 by substitution, and solves
+// (I + A) [-W | U0] = [-beta g K | beta V] block row by block row with mma.sync, feeding each
+// solved 16-row block back as an operand from registers; all factors go to scratch as 16-bit tiles.
 // Kernel B (one CTA per (recurrence, head, 32- or 64-column slice of S)) walks the chunks in order: the
 // fp32 state lives in the mma accumulators of its 4 warps for the whole sequence, a 16-bit copy
 // in shared memory serves as the B operand of the two state products, and the per-chunk factors
@@ -29,6 +30,15 @@ constexpr int kRecW = 0, kRecQg = kC * kD * 2, kRecKt = 2 * kC * kD * 2, kRecU0 
 // ------------------------------------------------------------------------------------------------
 // Kernel A: chunk-local factors
 // ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+  uint32_t d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+  return d;
+}
+
+constexpr int kAfLd = 66;      // fp32 A rows: even stride so that column pairs are 8-byte aligned
+constexpr int kTfLd = 17;
+
 template <bool kBf16>
 __global__ void __launch_bounds__(128)
 scan_local_mma_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ k, const uint16_t* __restrict__ v,
@@ -38,14 +48,14 @@ scan_local_mma_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict
   uint8_t* Ks = sm;                         // [64][128] 16-bit, swizzled
   uint8_t* Qs = Ks + kC * kD * 2;
   uint8_t* Vs = Qs + kC * kD * 2;
-  float* Af = reinterpret_cast<float*>(Vs + kC * kD * 2);      // [64][65]
-  float* Tf = Af + kC * 65;                                     // [64][65]
-  float* Mf = Tf + kC * 65;                                     // [32][33]
-  uint8_t* Tb = reinterpret_cast<uint8_t*>(Mf + 32 * 33);       // [64][64] 16-bit, swizzled
-  float* lg = reinterpret_cast<float*>(Tb + kC * kC * 2);       // [64] inclusive log decay
+  float* Af = reinterpret_cast<float*>(Vs + kC * kD * 2);      // [64][66] strictly lower triangular A
+  float* Tf = Af + kC * kAfLd;                                  // [4][16][17] inverses of the diagonal blocks
+  uint8_t* Gb = reinterpret_cast<uint8_t*>(Tf + 4 * 16 * kTfLd);  // [64][64] 16-bit, swizzled: the solve operator
+  float* lg = reinterpret_cast<float*>(Gb + kC * kC * 2);       // [64] inclusive log decay
   float* bt = lg + kC;                                          // [64] beta
   float* kinv = bt + kC;                                        // [64]
   float* qinv = kinv + kC;                                      // [64]
+  float* wsum = qinv + kC;                                      // [2]
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
@@ -64,18 +74,26 @@ scan_local_mma_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict
     cp_async16(smem_u32(Vs) + tile_off(r, ch * 8, kD), v + (tok * Hkv + hk) * kD + ch * 8, ok);
   }
   cp_async_commit();
-  if (tid == 0) {
-    float run = 0.f;
-    for (int r = 0; r < kC; ++r) {
-      const int64_t gi = ((int64_t)b * Tlen + t0 + r) * H + h;
-      run += (r < rows) ? g[gi] : 0.f;
-      lg[r] = run;
-      bt[r] = (r < rows) ? beta[gi] : 0.f;
+  // inclusive prefix sum of the log decay over the chunk: one row per thread, two warps
+  float run = 0.f;
+  if (tid < kC) {
+    const int64_t gi = ((int64_t)b * Tlen + t0 + tid) * H + h;
+    run = (tid < rows) ? g[gi] : 0.f;
+    bt[tid] = (tid < rows) ? beta[gi] : 0.f;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float up = __shfl_up_sync(0xffffffffu, run, o);
+      if (lane >= o) run += up;
     }
-    gc_base[((int64_t)b * H + h) * NC + c] = __expf(run);
+    if (lane == 31) wsum[warp] = run;
   }
   cp_async_wait<0>();
   __syncthreads();
+  if (tid < kC) {
+    if (warp == 1) run += wsum[0];
+    lg[tid] = run;
+    if (tid == kC - 1) gc_base[((int64_t)b * H + h) * NC + c] = __expf(run);
+  }
 
   // ---- row norms: thread i handles row i%64 of K (i < 64) or Q ----------------------------------------
   {
@@ -94,8 +112,10 @@ scan_local_mma_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict
   }
   __syncthreads();
 
-  // ---- K K^T and Q K^T for rows 16w..16w+15 (only key tiles at or below the diagonal) ---------------
+  // ---- K K^T for row block `warp` and Q K^T for row block 3 - warp (key blocks at or below the
+  //      diagonal only): every warp does five 16x16 block products per k-step ------------------------
   {
+    const int rk = warp, rq = 3 - warp;
     float kk[8][4], qk[8][4];
 #pragma unroll
     for (int nt = 0; nt < 8; ++nt)
@@ -104,19 +124,20 @@ scan_local_mma_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict
     int am, ak, bn, bk;
     a_rowmajor_lane(lane, am, ak);
     b_nk_lane(lane, bn, bk);
-    const int npairs = warp + 1;                                 // key-tile pairs 0..warp cover s <= 16w+15
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks) {
       uint32_t ak_[4], aq_[4];
-      ldsm_x4(smem_u32(Ks) + tile_off(16 * warp + am, 16 * ks + ak, kD), ak_);
-      ldsm_x4(smem_u32(Qs) + tile_off(16 * warp + am, 16 * ks + ak, kD), aq_);
+      ldsm_x4(smem_u32(Ks) + tile_off(16 * rk + am, 16 * ks + ak, kD), ak_);
+      ldsm_x4(smem_u32(Qs) + tile_off(16 * rq + am, 16 * ks + ak, kD), aq_);
 #pragma unroll
       for (int pr = 0; pr < 4; ++pr) {
-        if (pr < npairs) {
-          uint32_t bf[4];
-          ldsm_x4(smem_u32(Ks) + tile_off(16 * pr + bn, 16 * ks + bk, kD), bf);
+        uint32_t bf[4];
+        ldsm_x4(smem_u32(Ks) + tile_off(16 * pr + bn, 16 * ks + bk, kD), bf);
+        if (pr <= rk) {
           mma16816<kBf16>(kk[2 * pr], ak_, bf[0], bf[1]);
           mma16816<kBf16>(kk[2 * pr + 1], ak_, bf[2], bf[3]);
+        }
+        if (pr <= rq) {
           mma16816<kBf16>(qk[2 * pr], aq_, bf[0], bf[1]);
           mma16816<kBf16>(qk[2 * pr + 1], aq_, bf[2], bf[3]);
         }
@@ -129,69 +150,77 @@ scan_local_mma_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict
     for (int nt = 0; nt < 8; ++nt) {
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        const int p = 16 * warp + gq + 8 * half;
-        float a2[2], r2[2];
+        {                                                        // A rows of block rk
+          const int p = 16 * rk + gq + 8 * half;
+          float a2[2];
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int s = 8 * nt + 2 * tq + e;
-          float av = 0.f, rv = 0.f;
-          if (s <= p) {
-            const float ratio = __expf(lg[p] - lg[s]);
-            rv = ratio * qk[nt][2 * half + e] * qinv[p] * kinv[s];
-            if (s < p) av = bt[p] * ratio * kk[nt][2 * half + e] * kinv[p] * kinv[s];
+          for (int e = 0; e < 2; ++e) {
+            const int s = 8 * nt + 2 * tq + e;
+            a2[e] = (s < p) ? bt[p] * __expf(lg[p] - lg[s]) * kk[nt][2 * half + e] * kinv[p] * kinv[s] : 0.f;
           }
-          a2[e] = av; r2[e] = rv;
-          Af[p * 65 + s] = av;
+          *reinterpret_cast<float2*>(Af + p * kAfLd + 8 * nt + 2 * tq) = make_float2(a2[0], a2[1]);
         }
-        *reinterpret_cast<uint32_t*>(rq_out + p * kC + 8 * nt + 2 * tq) = pack2<kBf16>(r2[0], r2[1]);
+        {                                                        // Rq rows of block rq
+          const int p = 16 * rq + gq + 8 * half;
+          float r2[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int s = 8 * nt + 2 * tq + e;
+            r2[e] = (s <= p) ? __expf(lg[p] - lg[s]) * qk[nt][2 * half + e] * qinv[p] * kinv[s] : 0.f;
+          }
+          *reinterpret_cast<uint32_t*>(rq_out + p * kC + 8 * nt + 2 * tq) = pack2<kBf16>(r2[0], r2[1]);
+        }
       }
     }
   }
   __syncthreads();
 
-  // ---- T = (I + A)^-1, fp32 -------------------------------------------------------------------------
-  for (int i = tid; i < kC * kC; i += 128) Tf[(i >> 6) * 65 + (i & 63)] = 0.f;
-  __syncthreads();
-  if (tid < 64) {                                               // 16x16 diagonal blocks by substitution
+  // ---- inverses of the four 16x16 diagonal blocks of I + A by substitution (fp32) ----------------------
+  if (tid < 64) {
     const int blk = tid >> 4, j = tid & 15;
     float x[16];
 #pragma unroll
     for (int p = 0; p < 16; ++p) {
       float acc = (p == j) ? 1.f : 0.f;
 #pragma unroll
-      for (int s = 0; s < p; ++s) acc = fmaf(-Af[(16 * blk + p) * 65 + 16 * blk + s], x[s], acc);
+      for (int s = 0; s < p; ++s) acc = fmaf(-Af[(16 * blk + p) * kAfLd + 16 * blk + s], x[s], acc);
       x[p] = acc;
-      Tf[(16 * blk + p) * 65 + 16 * blk + j] = acc;
+      Tf[(blk * 16 + p) * kTfLd + j] = acc;
     }
   }
   __syncthreads();
-  // merge: for a block matrix [[A11,0],[A21,A22]], T21 = -T22 (A21 T11)
-  for (int level = 0; level < 2; ++level) {
-    const int n = 16 << level;                                  // size of the diagonal blocks being merged
-    const int groups = kC / (2 * n);
-    for (int i = tid; i < groups * n * n; i += 128) {           // M = A21 T11
-      const int gidx = i / (n * n), rr = (i / n) % n, cc = i % n;
-      const int base = gidx * 2 * n;
-      float acc = 0.f;
-      for (int s = cc; s < n; ++s) acc = fmaf(Af[(base + n + rr) * 65 + base + s], Tf[(base + s) * 65 + base + cc], acc);
-      Mf[(gidx * n + rr) * 33 + cc] = acc;
+
+  // ---- the solve operator G (16-bit A operand): G_ii = T_ii, G_ij = -T_ii A_ij for j < i ---------------
+  //      (I + A) X = R  <=>  X_i = G_ii R_i + sum_{j<i} G_ij X_j, blocks of 16 rows
+  {
+    // off-diagonal blocks: 6 blocks x 16 rows x 8 column pairs = 768 pairs, 6 per thread
+#pragma unroll
+    for (int it = 0; it < 6; ++it) {
+      const int o = tid + 128 * it;
+      const int blk = o >> 7;                                   // 0..5 -> (1,0) (2,0) (2,1) (3,0) (3,1) (3,2)
+      const int bi = (blk == 0) ? 1 : (blk < 3 ? 2 : 3);
+      const int bj = (blk == 0) ? 0 : (blk < 3 ? blk - 1 : blk - 3);
+      const int rr = (o >> 3) & 15, cc = (o & 7) * 2;
+      float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+      for (int s = 0; s < 16; ++s) {
+        const float t = Tf[(bi * 16 + rr) * kTfLd + s];
+        const float2 a = *reinterpret_cast<const float2*>(Af + (16 * bi + s) * kAfLd + 16 * bj + cc);
+        a0 = fmaf(t, a.x, a0); a1 = fmaf(t, a.y, a1);
+      }
+      *reinterpret_cast<uint32_t*>(Gb + tile_off(16 * bi + rr, 16 * bj + cc, kC)) = pack2<kBf16>(-a0, -a1);
     }
-    __syncthreads();
-    for (int i = tid; i < groups * n * n; i += 128) {           // T21 = -T22 M
-      const int gidx = i / (n * n), rr = (i / n) % n, cc = i % n;
-      const int base = gidx * 2 * n;
-      float acc = 0.f;
-      for (int s = 0; s <= rr; ++s) acc = fmaf(Tf[(base + n + rr) * 65 + base + n + s], Mf[(gidx * n + s) * 33 + cc], acc);
-      Tf[(base + n + rr) * 65 + base + cc] = -acc;
+    // diagonal blocks: 4 x 16 x 8 pairs = 512 pairs, 4 per thread
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int o = tid + 128 * it;
+      const int bi = o >> 7, rr = (o >> 3) & 15, cc = (o & 7) * 2;
+      *reinterpret_cast<uint32_t*>(Gb + tile_off(16 * bi + rr, 16 * bi + cc, kC)) =
+          pack2<kBf16>(Tf[(bi * 16 + rr) * kTfLd + cc], Tf[(bi * 16 + rr) * kTfLd + cc + 1]);
     }
-    __syncthreads();
-  }
-  for (int i = tid; i < kC * kC / 2; i += 128) {                // 16-bit copy of T (A operand)
-    const int p = i >> 5, s = (i & 31) * 2;
-    *reinterpret_cast<uint32_t*>(Tb + tile_off(p, s, kC)) = pack2<kBf16>(Tf[p * 65 + s], Tf[p * 65 + s + 1]);
   }
 
-  // ---- emit Qg and Kt; turn K into -beta g K and V into beta V in place (B operands) -----------------
+  // ---- emit Qg and Kt; turn K into -beta g K and V into beta V in place (right-hand sides) -------------
   {
     const float lgC = lg[kC - 1];
     uint4* qg_out = reinterpret_cast<uint4*>(rec + kRecQg);
@@ -221,39 +250,48 @@ scan_local_mma_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict
   }
   __syncthreads();
 
-  // ---- -W = T (-beta g K) and U0 = T (beta V): rows 16w.., k-steps 0..w (T is lower triangular) -------
+  // ---- blocked forward solve: -W (warps 0,1) and U0 (warps 2,3), 64 columns per warp.  A solved
+  //      block goes back in as a B operand straight from the accumulators (8x8 register transposes),
+  //      so the four steps need no barrier ------------------------------------------------------------
   {
     int am, ak, bk, bn;
     a_rowmajor_lane(lane, am, ak);
     b_kn_lane(lane, bk, bn);
     const int gq = lane >> 2, tq = lane & 3;
-#pragma unroll 1
-    for (int which = 0; which < 2; ++which) {
-      const uint8_t* Bs = which ? Vs : Ks;
-      float acc[16][4];
+    const int which = warp >> 1, cb = (warp & 1) * 64;
+    const uint8_t* Bs = which ? Vs : Ks;
+    uint16_t* out = reinterpret_cast<uint16_t*>(rec + (which ? kRecU0 : kRecW));
+    uint32_t xb[3][8][2];
 #pragma unroll
-      for (int nt = 0; nt < 16; ++nt)
+    for (int i = 0; i < 4; ++i) {
+      float acc[8][4];
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
         for (int e = 0; e < 4; ++e) acc[nt][e] = 0.f;
+      uint32_t af[4];
+      ldsm_x4(smem_u32(Gb) + tile_off(16 * i + am, 16 * i + ak, kC), af);
 #pragma unroll
-      for (int ks = 0; ks < 4; ++ks) {
-        if (ks <= warp) {
-          uint32_t af[4];
-          ldsm_x4(smem_u32(Tb) + tile_off(16 * warp + am, 16 * ks + ak, kC), af);
+      for (int pr = 0; pr < 4; ++pr) {
+        uint32_t bf[4];
+        ldsm_x4_trans(smem_u32(Bs) + tile_off(16 * i + bk, cb + 16 * pr + bn, kD), bf);
+        mma16816<kBf16>(acc[2 * pr], af, bf[0], bf[1]);
+        mma16816<kBf16>(acc[2 * pr + 1], af, bf[2], bf[3]);
+      }
 #pragma unroll
-          for (int pr = 0; pr < 8; ++pr) {
-            uint32_t bf[4];
-            ldsm_x4_trans(smem_u32(Bs) + tile_off(16 * ks + bk, 16 * pr + bn, kD), bf);
-            mma16816<kBf16>(acc[2 * pr], af, bf[0], bf[1]);
-            mma16816<kBf16>(acc[2 * pr + 1], af, bf[2], bf[3]);
-          }
+      for (int j = 0; j < 3; ++j) {
+        if (j < i) {
+          ldsm_x4(smem_u32(Gb) + tile_off(16 * i + am, 16 * j + ak, kC), af);
+#pragma unroll
+          for (int nt = 0; nt < 8; ++nt) mma16816<kBf16>(acc[nt], af, xb[j][nt][0], xb[j][nt][1]);
         }
       }
-      uint16_t* out = reinterpret_cast<uint16_t*>(rec + (which ? kRecU0 : kRecW));
 #pragma unroll
-      for (int nt = 0; nt < 16; ++nt) {
-        *reinterpret_cast<uint32_t*>(out + (16 * warp + gq) * kD + 8 * nt + 2 * tq) = pack2<kBf16>(acc[nt][0], acc[nt][1]);
-        *reinterpret_cast<uint32_t*>(out + (16 * warp + gq + 8) * kD + 8 * nt + 2 * tq) = pack2<kBf16>(acc[nt][2], acc[nt][3]);
+      for (int nt = 0; nt < 8; ++nt) {
+        const uint32_t lo = pack2<kBf16>(acc[nt][0], acc[nt][1]), hi = pack2<kBf16>(acc[nt][2], acc[nt][3]);
+        *reinterpret_cast<uint32_t*>(out + (16 * i + gq) * kD + cb + 8 * nt + 2 * tq) = lo;
+        *reinterpret_cast<uint32_t*>(out + (16 * i + gq + 8) * kD + cb + 8 * nt + 2 * tq) = hi;
+        if (i < 3) { xb[i][nt][0] = movmatrix_trans(lo); xb[i][nt][1] = movmatrix_trans(hi); }
       }
     }
   }
@@ -474,7 +512,7 @@ int gated_delta_scan_mma_factors(const void* q, const void* k, const void* v, in
   const int NC = (T + kC - 1) / kC;
   uint8_t* recs = static_cast<uint8_t*>(scratch);
   float* gcs = gc_array(scratch, B, H, NC);
-  const int smemA = 3 * kC * kD * 2 + (2 * kC * 65 + 32 * 33) * 4 + kC * kC * 2 + 4 * kC * 4;
+  const int smemA = 3 * kC * kD * 2 + (kC * kAfLd + 4 * 16 * kTfLd) * 4 + kC * kC * 2 + (4 * kC + 4) * 4;
   if (dtype == ATMA_BF16) {
     ATMA_CUDA_OK(cudaFuncSetAttribute(scan_local_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smemA));
     scan_local_mma_kernel<true><<<dim3(NC, H, B), 128, smemA, st>>>((const uint16_t*)q, (const uint16_t*)k, (const uint16_t*)v, g,
