@@ -41,7 +41,7 @@ METRIC = "global_layer_prefill_tok_s_at_64k"
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) from the committed ncu captures of the
 # small --profile cases (profiles/polar_prefill_sm100_T16384.md, profiles/polar_decode_b16_ctx16384.md).
 PREFILL_TRAFFIC_T16K = 53.1e6
-DECODE_TRAFFIC_RATIO = 273.3 / 268.4
+DECODE_TRAFFIC_RATIO = 273.2 / 268.4
 
 
 def measured_peaks():
@@ -194,7 +194,7 @@ def bench_decode(ab, device, steps, warmup, peaks):
         "roofline": {"kernel": "polar_decode (split + merge)", "bound": "hbm",
                      "achieved": kv_bytes / (polar_ms * 1e-3) / 1e9, "peak": peaks["hbm"], "unit": "GB/s",
                      "frac": kv_bytes / (polar_ms * 1e-3) / 1e9 / peaks["hbm"],
-                     # ncu capture at B=16 x 16K context: 273.3 MB moved for 268.4 MB algorithmic (x1.018);
+                     # ncu capture at B=16 x 16K context: 273.2 MB moved for 268.4 MB algorithmic (x1.018);
                      # traffic is proportional to the cache bytes, so it is scaled to this launch.
                      "traffic": kv_bytes * DECODE_TRAFFIC_RATIO,
                      "algorithmic_bytes": kv_bytes, "kernel_ms": polar_ms, "peak_source": peaks["source"]},
