@@ -75,6 +75,10 @@ _SIGNATURES = {
                                               c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]),
     "atma_gated_delta_scan_recur": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                             POINTER(c_int), POINTER(c_int), c_void_p, c_void_p, c_void_p, c_void_p]),
+    "atma_gated_delta_scan_varlen": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                             c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
+                                             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]),
+    "atma_gated_delta_scan_varlen_scratch_bytes": (c_int64, [c_int64, c_int, c_int, c_int, c_int]),
     "atma_causal_conv1d_decode_step": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64,
                                                c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p]),
     "atma_packed_causal_conv1d": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p,

@@ -229,6 +229,12 @@ int gated_delta_scan_mma_factors(const void* q, const void* k, const void* v, in
 int gated_delta_scan_mma_recur(void* scratch, int dtype, int B, int T, int H, int n_rec, const int* rec_of,
                                const int* zero_u0, const float* initial_state, void* o, float* final_state,
                                cudaStream_t st);
+int64_t gated_delta_scan_mma_varlen_scratch_bytes(int64_t total_tokens, int n_seqs, int H);
+int gated_delta_scan_mma_varlen(const void* q, const void* k, const void* v, int dtype, const float* g, const float* beta,
+                                const int32_t* cu_seqlens, int n_seqs, int64_t total_tokens, const float* initial_state,
+                                float* final_state, float* state_table, int64_t slot_stride, const int64_t* slots,
+                                const int32_t* has_initial, void* o, void* scratch, int H, int Hkv, int normalize_qk,
+                                float scale, cudaStream_t st);
 
 }  // namespace atma
 
@@ -252,6 +258,33 @@ extern "C" int atma_gated_delta_scan_recur(void* scratch, int dtype, int B, int 
   ATMA_REQUIRE(scratch != nullptr && B > 0 && T > 0 && H > 0, "gated_delta_scan_recur: bad arguments");
   return gated_delta_scan_mma_recur(scratch, dtype, B, T, H, n_rec, rec_of, zero_u0, initial_state, o, final_state,
                                     (cudaStream_t)stream);
+}
+
+extern "C" int64_t atma_gated_delta_scan_varlen_scratch_bytes(int64_t total_tokens, int n_seqs, int H, int dk, int dv) {
+  if (!gated_delta_scan_mma_supported(ATMA_BF16, dk, dv) || total_tokens < 0 || n_seqs < 0) return 0;
+  return gated_delta_scan_mma_varlen_scratch_bytes(total_tokens, n_seqs, H);
+}
+
+extern "C" int atma_gated_delta_scan_varlen(const void* q, const void* k, const void* v, int dtype, const float* g,
+                                            const float* beta, const int32_t* cu_seqlens, int n_seqs,
+                                            int64_t total_tokens, const float* initial_state, float* final_state,
+                                            float* state_table, int64_t slot_stride, const int64_t* slots,
+                                            const int32_t* has_initial, void* o, void* scratch, int H, int Hkv, int dk,
+                                            int dv, int normalize_qk, float scale, void* stream) {
+  ATMA_REQUIRE(gated_delta_scan_mma_supported(dtype, dk, dv),
+               "gated_delta_scan_varlen: needs 16-bit inputs with dk = dv = 128 (got dtype %d, dk %d, dv %d)", dtype, dk, dv);
+  ATMA_REQUIRE(n_seqs >= 0 && total_tokens >= 0 && H > 0 && Hkv > 0 && H % Hkv == 0, "gated_delta_scan_varlen: bad shape");
+  ATMA_REQUIRE(total_tokens / kScanC + n_seqs < (1 << 30), "gated_delta_scan_varlen: too many chunks");
+  if (n_seqs == 0) return ATMA_OK;
+  ATMA_REQUIRE(cu_seqlens != nullptr, "gated_delta_scan_varlen: cu_seqlens is required");
+  ATMA_REQUIRE(state_table == nullptr || slots != nullptr, "gated_delta_scan_varlen: a state table needs slots");
+  ATMA_REQUIRE(state_table == nullptr || (initial_state == nullptr && final_state == nullptr),
+               "gated_delta_scan_varlen: pass either a slot-indexed state table or dense state arrays, not both");
+  ATMA_REQUIRE(scratch != nullptr && (uintptr_t)scratch % 256 == 0 && (uintptr_t)q % 16 == 0 && (uintptr_t)k % 16 == 0 &&
+                   (uintptr_t)v % 16 == 0, "gated_delta_scan_varlen: scratch must be 256-byte and inputs 16-byte aligned");
+  return gated_delta_scan_mma_varlen(q, k, v, dtype, g, beta, cu_seqlens, n_seqs, total_tokens, initial_state, final_state,
+                                     state_table, slot_stride, slots, has_initial, o, scratch, H, Hkv, normalize_qk, scale,
+                                     (cudaStream_t)stream);
 }
 
 extern "C" int64_t atma_gated_delta_scan_scratch_bytes(int B, int T, int H, int dk, int dv) {

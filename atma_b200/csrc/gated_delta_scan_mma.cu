@@ -36,6 +36,30 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
   return d;
 }
 
+// Packed ("varlen") batches: sequences of different lengths back to back in one token axis.  Chunks
+// never straddle sequences: sequence i owns chunk records cu_chunks[i] .. cu_chunks[i+1]-1.
+struct VarLen {
+  const int32_t* cu_seqlens;   // device [n_seqs + 1] token offsets; nullptr = dense (B, T) batch
+  const int32_t* cu_chunks;    // device [n_seqs + 1] chunk offsets (built by varlen_chunk_offsets_kernel)
+  int n_seqs;
+  const int64_t* slots;        // device [n_seqs] rows of state_table, or nullptr (dense state arrays)
+  const int32_t* has_initial;  // device [n_seqs] or nullptr (= every sequence starts from its table row)
+  float* state_table;          // [rows][H][dk][dv] fp32, or nullptr
+  int64_t slot_stride;         // elements between table rows
+};
+
+__global__ void varlen_chunk_offsets_kernel(const int32_t* __restrict__ cu_seqlens, int32_t* __restrict__ cu_chunks, int n_seqs) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    int acc = 0;
+    cu_chunks[0] = 0;
+    for (int i = 0; i < n_seqs; ++i) {
+      const int len = max(cu_seqlens[i + 1] - cu_seqlens[i], 0);
+      acc += (len + kC - 1) / kC;
+      cu_chunks[i + 1] = acc;
+    }
+  }
+}
+
 constexpr int kAfLd = 66;      // fp32 A rows: even stride so that column pairs are 8-byte aligned
 constexpr int kTfLd = 17;
 
@@ -43,7 +67,8 @@ template <bool kBf16>
 __global__ void __launch_bounds__(128)
 scan_local_mma_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ k, const uint16_t* __restrict__ v,
                       const float* __restrict__ g, const float* __restrict__ beta, uint8_t* __restrict__ rec_base,
-                      float* __restrict__ gc_base, int Tlen, int H, int Hkv, int NC, int normalize_qk, float scale) {
+                      float* __restrict__ gc_base, int Tlen, int H, int Hkv, int NC, int normalize_qk, float scale,
+                      const VarLen var) {
   extern __shared__ __align__(128) uint8_t sm[];
   uint8_t* Ks = sm;                         // [64][128] 16-bit, swizzled
   uint8_t* Qs = Ks + kC * kD * 2;
@@ -59,8 +84,18 @@ scan_local_mma_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-  const int t0 = c * kC;
-  const int rows = min(kC, Tlen - t0);
+  int t0 = c * kC;                          // first token of the chunk on the (b, token) axis
+  int rows = min(kC, Tlen - t0);
+  if (var.cu_seqlens != nullptr) {          // packed batch: find the sequence that owns chunk c
+    if (c >= var.cu_chunks[var.n_seqs]) return;
+    int lo_s = 0, hi_s = var.n_seqs;        // largest s with cu_chunks[s] <= c
+    while (hi_s - lo_s > 1) {
+      const int mid = (lo_s + hi_s) >> 1;
+      if (var.cu_chunks[mid] <= c) lo_s = mid; else hi_s = mid;
+    }
+    t0 = var.cu_seqlens[lo_s] + (c - var.cu_chunks[lo_s]) * kC;
+    rows = min(kC, var.cu_seqlens[lo_s + 1] - t0);
+  }
   const int hk = h / (H / Hkv);
   uint8_t* rec = rec_base + (((int64_t)b * H + h) * NC + c) * (int64_t)kRecBytes;
 
@@ -314,7 +349,7 @@ template <bool kBf16, int NCOL>
 __global__ void __launch_bounds__(128)
 scan_seq_mma_kernel(const uint8_t* __restrict__ rec_base, const float* __restrict__ gc_base,
                     const float* __restrict__ initial_state, uint16_t* __restrict__ o,
-                    float* __restrict__ final_state, int Tlen, int H, int NC, const RecMap map) {
+                    float* __restrict__ final_state, int Tlen, int H, int NC, const RecMap map, const VarLen var) {
   constexpr int NT = NCOL / 8, NP = NCOL / 16, CHN = NCOL / 8;
   constexpr int kStage = SeqCfg<NCOL>::kStage;
   extern __shared__ __align__(128) uint8_t sm[];
@@ -322,9 +357,15 @@ scan_seq_mma_kernel(const uint8_t* __restrict__ rec_base, const float* __restric
   uint8_t* Ub = Sb + kD * NCOL * 2;                  // [64 s][NCOL v]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int slice = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-  const int rb = map.rec[b];
-  const bool zero_u0 = map.zero_u0[b] != 0;
+  const bool packed = var.cu_seqlens != nullptr;
+  const int rb = packed ? 0 : map.rec[b];
+  const bool zero_u0 = packed ? false : map.zero_u0[b] != 0;
   const int gq = lane >> 2, tq = lane & 3;
+  // chunk records [c_begin, c_end) and the tokens [tok_base, tok_end) they cover
+  const int c_begin = packed ? var.cu_chunks[b] : 0;
+  const int c_end = packed ? var.cu_chunks[b + 1] : NC;
+  const int64_t tok_base = packed ? (int64_t)var.cu_seqlens[b] : (int64_t)b * Tlen;
+  const int64_t tok_end = packed ? (int64_t)var.cu_seqlens[b + 1] : tok_base + Tlen;
   const uint8_t* recs = rec_base + ((int64_t)rb * H + h) * NC * (int64_t)kRecBytes;
   const float* gcs = gc_base + ((int64_t)rb * H + h) * NC;
 
@@ -349,6 +390,14 @@ scan_seq_mma_kernel(const uint8_t* __restrict__ rec_base, const float* __restric
   // fp32 state: warp w owns rows k = 32w .. 32w+31 (two 16-row tiles) x NCOL columns
   float S[2][NT][4];
   const int64_t sbase = ((int64_t)b * H + h) * kD * kD + slice * NCOL;
+  // where the state comes from and goes to: dense (n, H, dk, dv) arrays, or rows of a slot-indexed table
+  const float* s_in = initial_state ? initial_state + sbase : nullptr;
+  float* s_out = final_state ? final_state + sbase : nullptr;
+  if (packed && var.state_table != nullptr) {
+    float* row = var.state_table + var.slots[b] * var.slot_stride + (int64_t)h * kD * kD + slice * NCOL;
+    s_in = (var.has_initial == nullptr || var.has_initial[b] != 0) ? row : nullptr;
+    s_out = row;
+  }
 #pragma unroll
   for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
@@ -357,11 +406,11 @@ scan_seq_mma_kernel(const uint8_t* __restrict__ rec_base, const float* __restric
       for (int hh = 0; hh < 2; ++hh) {
         const int kr = 32 * warp + 16 * mt + gq + 8 * hh, col = 8 * nt + 2 * tq;
         float2 v2 = make_float2(0.f, 0.f);
-        if (initial_state) v2 = *reinterpret_cast<const float2*>(initial_state + sbase + (int64_t)kr * kD + col);
+        if (s_in) v2 = *reinterpret_cast<const float2*>(s_in + (int64_t)kr * kD + col);
         S[mt][nt][2 * hh] = v2.x; S[mt][nt][2 * hh + 1] = v2.y;
         *reinterpret_cast<uint32_t*>(Sb + tile_off(kr, col, NCOL)) = pack2<kBf16>(v2.x, v2.y);
       }
-  load_stage(0, 0);
+  if (c_begin < c_end) load_stage(c_begin, 0);
   cp_async_commit();
 
   int am, ak, bk, bn, tk, tm;
@@ -369,9 +418,9 @@ scan_seq_mma_kernel(const uint8_t* __restrict__ rec_base, const float* __restric
   b_kn_lane(lane, bk, bn);
   a_km_lane(lane, tk, tm);
 
-  for (int c = 0; c < NC; ++c) {
-    const int s = c & 1;
-    if (c + 1 < NC) load_stage(c + 1, s ^ 1);
+  for (int c = c_begin; c < c_end; ++c) {
+    const int s = (c - c_begin) & 1;
+    if (c + 1 < c_end) load_stage(c + 1, s ^ 1);
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();                                           // stage s landed; Sb from the previous chunk visible
@@ -431,9 +480,9 @@ scan_seq_mma_kernel(const uint8_t* __restrict__ rec_base, const float* __restric
       }
 #pragma unroll
       for (int hh = 0; hh < 2; ++hh) {
-        const int t = c * kC + 16 * warp + gq + 8 * hh;
-        if (t < Tlen) {
-          uint16_t* orow = o + (((int64_t)b * Tlen + t) * H + h) * kD + slice * NCOL;
+        const int64_t t = tok_base + (int64_t)(c - c_begin) * kC + 16 * warp + gq + 8 * hh;
+        if (t < tok_end) {
+          uint16_t* orow = o + (t * H + h) * kD + slice * NCOL;
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt)
             *reinterpret_cast<uint32_t*>(orow + 8 * nt + 2 * tq) = pack2<kBf16>(O[nt][2 * hh], O[nt][2 * hh + 1]);
@@ -475,7 +524,7 @@ scan_seq_mma_kernel(const uint8_t* __restrict__ rec_base, const float* __restric
     __syncthreads();                                           // stage s and Ub free; new Sb complete
   }
   cp_async_wait<0>();
-  if (final_state) {
+  if (s_out) {
 #pragma unroll
     for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
@@ -483,7 +532,7 @@ scan_seq_mma_kernel(const uint8_t* __restrict__ rec_base, const float* __restric
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
           const int kr = 32 * warp + 16 * mt + gq + 8 * hh, col = 8 * nt + 2 * tq;
-          *reinterpret_cast<float2*>(final_state + sbase + (int64_t)kr * kD + col) =
+          *reinterpret_cast<float2*>(s_out + (int64_t)kr * kD + col) =
               make_float2(S[mt][nt][2 * hh], S[mt][nt][2 * hh + 1]);
         }
   }
@@ -516,11 +565,11 @@ int gated_delta_scan_mma_factors(const void* q, const void* k, const void* v, in
   if (dtype == ATMA_BF16) {
     ATMA_CUDA_OK(cudaFuncSetAttribute(scan_local_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smemA));
     scan_local_mma_kernel<true><<<dim3(NC, H, B), 128, smemA, st>>>((const uint16_t*)q, (const uint16_t*)k, (const uint16_t*)v, g,
-                                                                   beta, recs, gcs, T, H, Hkv, NC, normalize_qk, scale);
+                                                                   beta, recs, gcs, T, H, Hkv, NC, normalize_qk, scale, VarLen{});
   } else {
     ATMA_CUDA_OK(cudaFuncSetAttribute(scan_local_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smemA));
     scan_local_mma_kernel<false><<<dim3(NC, H, B), 128, smemA, st>>>((const uint16_t*)q, (const uint16_t*)k, (const uint16_t*)v, g,
-                                                                    beta, recs, gcs, T, H, Hkv, NC, normalize_qk, scale);
+                                                                    beta, recs, gcs, T, H, Hkv, NC, normalize_qk, scale, VarLen{});
   }
   return launch_status("gated_delta_scan (chunk-local, mma)");
 }
@@ -541,19 +590,66 @@ int gated_delta_scan_mma_recur(void* scratch, int dtype, int B, int T, int H, in
   const uint8_t* recs = static_cast<const uint8_t*>(scratch);
   const float* gcs = gc_array(scratch, B, H, NC);
   const bool bf = dtype == ATMA_BF16;
-  // few recurrences: 32-column slices (4 CTAs per head) shorten the per-chunk critical path
-  const bool narrow = (int64_t)n_rec * H * 2 < 148;
+  // one CTA per SM: 32-column slices (4 CTAs per head) shorten the per-chunk critical path as long
+  // as the whole grid still fits one wave
+  const bool narrow = (int64_t)n_rec * H * 4 <= 148;
 #define ATMA_LAUNCH(BF, NCOL)                                                                                     \
   do {                                                                                                            \
     auto kern = scan_seq_mma_kernel<BF, NCOL>;                                                                    \
     ATMA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SeqCfg<NCOL>::kSmem));   \
     kern<<<dim3(kD / NCOL, H, n_rec), 128, SeqCfg<NCOL>::kSmem, st>>>(recs, gcs, initial_state, (uint16_t*)o,     \
-                                                                       final_state, T, H, NC, map);               \
+                                                                       final_state, T, H, NC, map, VarLen{});     \
   } while (0)
   if (bf) { if (narrow) ATMA_LAUNCH(true, 32); else ATMA_LAUNCH(true, 64); }
   else { if (narrow) ATMA_LAUNCH(false, 32); else ATMA_LAUNCH(false, 64); }
 #undef ATMA_LAUNCH
   return launch_status("gated_delta_scan (recurrence, mma)");
+}
+
+// Packed batch: chunk offsets, factors of every chunk, one recurrence per sequence, all in one go.
+// Scratch layout: records of NCu = total/64 + n_seqs chunks per head | g_C | cu_chunks.
+int64_t gated_delta_scan_mma_varlen_scratch_bytes(int64_t total_tokens, int n_seqs, int H) {
+  const int64_t NCu = total_tokens / kC + n_seqs;
+  return gated_delta_scan_mma_scratch_bytes(1, (int)(NCu * kC), H) + (((int64_t)n_seqs + 1) * 4 + 255) / 256 * 256;
+}
+
+int gated_delta_scan_mma_varlen(const void* q, const void* k, const void* v, int dtype, const float* g, const float* beta,
+                                const int32_t* cu_seqlens, int n_seqs, int64_t total_tokens, const float* initial_state,
+                                float* final_state, float* state_table, int64_t slot_stride, const int64_t* slots,
+                                const int32_t* has_initial, void* o, void* scratch, int H, int Hkv, int normalize_qk,
+                                float scale, cudaStream_t st) {
+  const int NCu = (int)(total_tokens / kC) + n_seqs;          // upper bound on the chunk count
+  uint8_t* recs = static_cast<uint8_t*>(scratch);
+  float* gcs = gc_array(scratch, 1, H, NCu);
+  int32_t* cu_chunks = reinterpret_cast<int32_t*>(recs + gated_delta_scan_mma_scratch_bytes(1, NCu * kC, H));
+  varlen_chunk_offsets_kernel<<<1, 32, 0, st>>>(cu_seqlens, cu_chunks, n_seqs);
+  VarLen var{cu_seqlens, cu_chunks, n_seqs, slots, has_initial, state_table, slot_stride};
+  const int smemA = 3 * kC * kD * 2 + (kC * kAfLd + 4 * 16 * kTfLd) * 4 + kC * kC * 2 + (4 * kC + 4) * 4;
+  const bool bf = dtype == ATMA_BF16;
+  if (bf) {
+    ATMA_CUDA_OK(cudaFuncSetAttribute(scan_local_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smemA));
+    scan_local_mma_kernel<true><<<dim3(NCu, H, 1), 128, smemA, st>>>((const uint16_t*)q, (const uint16_t*)k, (const uint16_t*)v, g,
+                                                                    beta, recs, gcs, 0, H, Hkv, NCu, normalize_qk, scale, var);
+  } else {
+    ATMA_CUDA_OK(cudaFuncSetAttribute(scan_local_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smemA));
+    scan_local_mma_kernel<false><<<dim3(NCu, H, 1), 128, smemA, st>>>((const uint16_t*)q, (const uint16_t*)k, (const uint16_t*)v, g,
+                                                                     beta, recs, gcs, 0, H, Hkv, NCu, normalize_qk, scale, var);
+  }
+  int rc = launch_status("gated_delta_scan (packed, chunk-local, mma)");
+  if (rc != ATMA_OK) return rc;
+  const bool narrow = (int64_t)n_seqs * H * 4 <= 148;
+  RecMap map{};
+#define ATMA_LAUNCH(BF, NCOL)                                                                                     \
+  do {                                                                                                            \
+    auto kern = scan_seq_mma_kernel<BF, NCOL>;                                                                    \
+    ATMA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SeqCfg<NCOL>::kSmem));   \
+    kern<<<dim3(kD / NCOL, H, n_seqs), 128, SeqCfg<NCOL>::kSmem, st>>>(recs, gcs, initial_state, (uint16_t*)o,    \
+                                                                        final_state, 0, H, NCu, map, var);        \
+  } while (0)
+  if (bf) { if (narrow) ATMA_LAUNCH(true, 32); else ATMA_LAUNCH(true, 64); }
+  else { if (narrow) ATMA_LAUNCH(false, 32); else ATMA_LAUNCH(false, 64); }
+#undef ATMA_LAUNCH
+  return launch_status("gated_delta_scan (packed, recurrence, mma)");
 }
 
 int gated_delta_scan_mma(const void* q, const void* k, const void* v, int dtype, const float* g, const float* beta,

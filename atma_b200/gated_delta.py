@@ -60,15 +60,97 @@ def _scan_scratch(device, nbytes):
     return buf
 
 
+def _varlen_supported(q, dk, dv):
+    return q.dtype in (torch.bfloat16, torch.float16) and dk == 128 and dv == 128
+
+
+@torch.no_grad()
+def _scan_varlen(q, k, v, g, beta, cu_seqlens, scale, use_qk_l2norm_in_kernel, *, initial_state=None,
+                 want_final=False, state_table=None, slots=None, has_initial=None):
+    """Packed batch through one factor launch and one recurrence launch (16-bit, dk = dv = 128)."""
+    lib = _lib.load()
+    total, H, dk = q.shape
+    Hkv, dv = k.shape[1], v.shape[-1]
+    n_seqs = cu_seqlens.numel() - 1
+    q, k, v = q.contiguous(), k.to(q.dtype).contiguous(), v.to(q.dtype).contiguous()
+    g, beta = g.float().contiguous(), beta.float().contiguous()
+    cu = cu_seqlens.to(device=q.device, dtype=torch.int32).contiguous()
+    o = torch.empty((total, H, dv), device=q.device, dtype=q.dtype)
+    final = None
+    if state_table is None:
+        if initial_state is not None:
+            initial_state = initial_state.float().contiguous()
+        if want_final:
+            final = torch.empty((n_seqs, H, dk, dv), device=q.device, dtype=torch.float32)
+        slot_stride = 0
+    else:
+        if state_table.dtype != torch.float32 or state_table.stride(3) != 1 or state_table.stride(2) != dv \
+                or state_table.stride(1) != dk * dv:
+            raise ValueError("state_table must be float32 with dense [H, dk, dv] rows")
+        slots = slots.to(device=q.device, dtype=torch.int64).contiguous()
+        if has_initial is not None:
+            has_initial = has_initial.to(device=q.device, dtype=torch.int32).contiguous()
+        slot_stride = state_table.stride(0)
+    scratch = _scan_scratch(q.device, max(256, lib.atma_gated_delta_scan_varlen_scratch_bytes(total, n_seqs, H, dk, dv)))
+    _lib.check(lib.atma_gated_delta_scan_varlen(
+        _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.dtype_code(q), _lib.ptr(g), _lib.ptr(beta), _lib.ptr(cu), n_seqs,
+        total, _lib.ptr(initial_state), _lib.ptr(final), _lib.ptr(state_table), slot_stride, _lib.ptr(slots),
+        _lib.ptr(has_initial), _lib.ptr(o), _lib.ptr(scratch), H, Hkv, dk, dv, 1 if use_qk_l2norm_in_kernel else 0,
+        float(scale), _lib.stream_ptr()))
+    return o, final
+
+
+@torch.no_grad()
+def packed_gated_delta_prefill(q, k, v, g, beta, cu_seqlens, state_table, slots, has_initial=None, scale=1.0,
+                               use_qk_l2norm_in_kernel=True):
+    """The memory branch of a packed (several sequences, one token axis) prefill in one call.
+
+    The reference loops over the sequences, calls the scan once per sequence with that
+    sequence's table row as ``initial_state`` when it continues a cached prefix, and copies
+    the final state back (inference/models/atma.py:494-503).  Here the rows are read and
+    written by the recurrence kernel itself.
+
+    q (total,H,dk); k, v (total,H or Hkv,d); g, beta (total,H); cu_seqlens (n+1,) int, on the
+    host or the device; state_table (rows,H,dk,dv) fp32, updated IN PLACE at rows ``slots``
+    (n,); has_initial (n,) bool/int or None (= every sequence continues from its row).
+    Returns o (total,H,dv) in q's dtype."""
+    _lib.require_cuda(q, "packed_gated_delta_prefill")
+    dk, dv = q.shape[-1], v.shape[-1]
+    if _varlen_supported(q, dk, dv):
+        o, _ = _scan_varlen(q, k, v, g, beta, cu_seqlens, scale, use_qk_l2norm_in_kernel, state_table=state_table,
+                            slots=slots, has_initial=has_initial)
+        return o
+    # fp32 inputs or other head sizes: the dense entry once per sequence (lengths read on the host)
+    cu = cu_seqlens.tolist()
+    slot_l = slots.tolist()
+    init_l = None if has_initial is None else has_initial.tolist()
+    o = torch.empty((q.shape[0], q.shape[1], dv), device=q.device, dtype=q.dtype)
+    for i in range(len(cu) - 1):
+        a, b = cu[i], cu[i + 1]
+        if b <= a:
+            continue
+        s0 = state_table[slot_l[i]].unsqueeze(0) if (init_l is None or init_l[i]) else None
+        oi, Si = chunk_gated_delta_rule(q=q[a:b].unsqueeze(0), k=k[a:b].unsqueeze(0), v=v[a:b].unsqueeze(0),
+                                        g=g[a:b].unsqueeze(0), beta=beta[a:b].unsqueeze(0), scale=scale,
+                                        initial_state=s0, output_final_state=True,
+                                        use_qk_l2norm_in_kernel=use_qk_l2norm_in_kernel)
+        o[a:b] = oi[0]
+        state_table[slot_l[i]] = Si[0]
+    return o
+
+
 @torch.no_grad()
 def chunk_gated_delta_rule(q=None, k=None, v=None, g=None, beta=None, scale=None,
                            initial_state=None, output_final_state=False,
-                           use_qk_l2norm_in_kernel=False, **unused):
+                           use_qk_l2norm_in_kernel=False, cu_seqlens=None, **unused):
     """Chunked gated-delta scan.  q (B,T,H,dk); k (B,T,H or Hkv,dk), v (B,T,H or Hkv,dv) - the
     un-expanded KV heads are accepted, head h then reads KV head h // (H // Hkv); g (B,T,H) log-decay (<= 0);
     beta (B,T,H); initial_state (B,H,dk,dv) fp32 or None.  Returns (o (B,T,H,dv) in q's dtype,
     final_state (B,H,dk,dv) fp32 or None).  ``scale`` defaults to dk**-0.5 as in
-    flash-linear-attention; the reference always passes 1.0."""
+    flash-linear-attention; the reference always passes 1.0.
+
+    ``cu_seqlens`` (n+1,) as in flash-linear-attention: the batch axis must be 1 and the token
+    axis holds n sequences back to back; initial_state / final_state are then (n,H,dk,dv)."""
     _lib.require_cuda(q, "chunk_gated_delta_rule")
     lib = _lib.load()
     B, T, H, dk = q.shape
@@ -78,6 +160,26 @@ def chunk_gated_delta_rule(q=None, k=None, v=None, g=None, beta=None, scale=None
         raise ValueError("k and v must share a head count that divides q's")
     if scale is None:
         scale = dk ** -0.5
+    if cu_seqlens is not None:
+        if B != 1:
+            raise ValueError("with cu_seqlens the batch axis must be 1 (sequences are packed on the token axis)")
+        n = cu_seqlens.numel() - 1
+        if _varlen_supported(q, dk, dv):
+            o, final = _scan_varlen(q[0], k[0], v[0], g[0], beta[0], cu_seqlens, scale, use_qk_l2norm_in_kernel,
+                                    initial_state=initial_state, want_final=output_final_state)
+            return o.unsqueeze(0), final
+        cu = cu_seqlens.tolist()
+        o = torch.empty((1, T, H, dv), device=q.device, dtype=q.dtype)
+        finals = []
+        for i in range(n):
+            a, b = cu[i], cu[i + 1]
+            s0 = None if initial_state is None else initial_state[i:i + 1]
+            oi, Si = chunk_gated_delta_rule(q=q[:, a:b], k=k[:, a:b], v=v[:, a:b], g=g[:, a:b], beta=beta[:, a:b],
+                                            scale=scale, initial_state=s0, output_final_state=True,
+                                            use_qk_l2norm_in_kernel=use_qk_l2norm_in_kernel)
+            o[:, a:b] = oi
+            finals.append(Si)
+        return o, (torch.cat(finals) if output_final_state else None)
     q, k, v = q.contiguous(), k.to(q.dtype).contiguous(), v.to(q.dtype).contiguous()
     g = g.float().contiguous()
     beta = beta.float().contiguous()

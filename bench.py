@@ -439,7 +439,7 @@ def run_context_parallel(args, ab, rank, local_rank, world, device, peaks):
         "metric": METRIC, "value": T_PREFILL / (ms * 1e-3), "unit": "tok/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "global-layer mixing prefill: Polar attention + gated-delta scan, ONE 65536-token sequence "
+        "config": {"workload": f"global-layer mixing prefill: Polar attention + gated-delta scan, ONE {T_PREFILL}-token sequence "
                                "context-parallel over the GPUs (zig-zag segments, K/V all-gathered over NVLink, one Polar launch per "
                                "query segment, gated-delta state handed over as an affine-map prefix)",
                    "tokens": T_PREFILL, "heads": H, "kv_heads": HKV, "head_dim": DK, "chunk": CHUNK, "window": None,
@@ -488,6 +488,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--tokens", type=int, default=T_PREFILL,
+                    help="prefill length (default: the metric's 65,536; 262,144 is the long context-parallel case)")
     ap.add_argument("--no-graph", action="store_true",
                     help="N > 1: issue the context-parallel step launch by launch instead of replaying a CUDA graph")
     ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline leg (profiling runs)")
@@ -496,6 +498,10 @@ def main():
                     help="run a few launches of ONE kernel on a small case (a few hundred MB, larger than L2) "
                          "and exit; meant to be wrapped in ncu")
     args = ap.parse_args()
+    global T_PREFILL, METRIC
+    if args.tokens != T_PREFILL:
+        T_PREFILL = args.tokens
+        METRIC = f"global_layer_prefill_tok_s_at_{T_PREFILL}"
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -614,9 +620,9 @@ def main():
         "metric": METRIC, "value": world * T_PREFILL / (ms * 1e-3), "unit": "tok/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "global-layer mixing prefill: Polar attention + gated-delta scan, one 65536-token sequence",
+        "config": {"workload": f"global-layer mixing prefill: Polar attention + gated-delta scan, one {T_PREFILL}-token sequence",
                    "tokens": T_PREFILL, "heads": H, "kv_heads": HKV, "head_dim": DK, "chunk": CHUNK,
-                   "window": None, "l2": "inputs (268 MB) larger than L2 (126 MB)",
+                   "window": None, "l2": f"inputs ({(2 * H + 2 * HKV) * DK * 2 * T_PREFILL / 1e6:.0f} MB) larger than L2 (126 MB)",
                    "polar_kernel": "tcgen05" if tensor_path else "cuda-core fp32"},
         "e2e": {"value": world * T_PREFILL / (e2e_ms * 1e-3), "unit": "tok/s", "ms_per_step": e2e_ms,
                 "api": "atma_b200.mixing.HostFedMixing.submit (copy-in | kernels | copy-out streams, double buffered)",

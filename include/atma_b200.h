@@ -197,6 +197,34 @@ int atma_gated_delta_scan_recur(void* scratch, int dtype, int B, int T, int H, i
                                 const float* initial_state, void* o, float* final_state,
                                 void* stream);
 
+/* ----------------------------------------------------------------------------------
+ * Packed ("varlen") gated-delta prefill: n_seqs sequences of different lengths back to back
+ * on one token axis, one call.  Replaces the per-sequence loop around chunk_gated_delta_rule
+ * in the reference's packed prefill (inference/models/atma.py:494-503; the loop is named as
+ * the remaining prefill gap in docs/kernel.md:328-329) and follows the cu_seqlens convention
+ * of flash-linear-attention's chunk_gated_delta_rule.
+ *   q [total][H][dk]; k, v [total][Hkv][d]; g, beta fp32 [total][H]; o [total][H][dv]
+ *   cu_seqlens   DEVICE int32 [n_seqs + 1], token offsets (cu_seqlens[n_seqs] <= total)
+ *   state: EITHER dense arrays initial_state / final_state fp32 [n_seqs][H][dk][dv] (each
+ *   may be NULL: start from zero / do not return), OR a slot-indexed table state_table
+ *   ([rows][H][dk][dv] fp32, slot_stride elements between rows) with DEVICE int64 slots
+ *   [n_seqs]: sequence i starts from row slots[i] when has_initial is NULL or
+ *   has_initial[i] != 0 (DEVICE int32), else from zero, and its final state is written to
+ *   that row in place.  A sequence of length 0 leaves its state unchanged.
+ *   16-bit inputs with dk = dv = 128 only (ATMA_ERR_INVALID otherwise: loop over
+ *   atma_gated_delta_scan).  scratch: atma_gated_delta_scan_varlen_scratch_bytes bytes,
+ *   256-byte aligned.  No host synchronisation; safe to capture in a CUDA graph.
+ * ---------------------------------------------------------------------------------- */
+int atma_gated_delta_scan_varlen(const void* q, const void* k, const void* v, int dtype,
+                                 const float* g, const float* beta, const int32_t* cu_seqlens,
+                                 int n_seqs, int64_t total_tokens, const float* initial_state,
+                                 float* final_state, float* state_table, int64_t slot_stride,
+                                 const int64_t* slots, const int32_t* has_initial, void* o,
+                                 void* scratch, int H, int Hkv, int dk, int dv, int normalize_qk,
+                                 float scale, void* stream);
+int64_t atma_gated_delta_scan_varlen_scratch_bytes(int64_t total_tokens, int n_seqs, int H,
+                                                   int dk, int dv);
+
 /* ------------------------------------------------------------------------------------
  * Depthwise causal conv, one decode step, in place on a slot-indexed state table.
  * Replaces kernel/causal_conv1d_triton.py:17-42 behind causal_conv1d_decode_step (:46-63).

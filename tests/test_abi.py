@@ -68,6 +68,13 @@ def test_argument_validation_needs_no_gpu(lib):
     with pytest.raises(ValueError):
         _lib.check(_lib.ATMA_ERR_INVALID)
     assert lib.atma_polar_decode_scratch_floats(64, 8, 128, 8) == 64 * 8 * 8 * 132
+    # the packed scan: fp32 inputs are refused before anything is launched; scratch sizing is pure arithmetic
+    rc = lib.atma_gated_delta_scan_varlen(None, None, None, 0, None, None, None, 2, 100, None, None, None, 0, None, None,
+                                          None, None, 8, 2, 128, 128, 1, 1.0, None)
+    assert rc == _lib.ATMA_ERR_INVALID and b"16-bit" in lib.atma_last_error()
+    chunks = 1000 // 64 + 3
+    assert lib.atma_gated_delta_scan_varlen_scratch_bytes(1000, 3, 8, 128, 128) >= 8 * chunks * 73728
+    assert lib.atma_gated_delta_scan_varlen_scratch_bytes(1000, 3, 8, 64, 64) == 0
 
 
 def test_ops_refuse_cpu_tensors():

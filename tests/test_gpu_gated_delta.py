@@ -127,3 +127,73 @@ def test_scan_state_carry_layout_and_decode_continuity():
                                                       torch.exp(glog[:, t]).cuda(), beta[:, t].cuda(), table, slots))
     assert max_rel(torch.stack(outs, 1), o_full[:, T:].float()) < 2e-2
     assert max_rel(table[slots], S_full) < 2e-2
+
+
+# ---- packed ("varlen") scan: several sequences on one token axis, one call ------------------------------
+def _packed_inputs(lens, H, Hkv, d, dtype, seed):
+    total = sum(lens)
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(total, H, d, generator=g).to(dtype)
+    k = torch.randn(total, Hkv, d, generator=g).to(dtype)
+    v = torch.randn(total, Hkv, d, generator=g).to(dtype)
+    glog = F.logsigmoid(torch.randn(total, H, generator=g) + 3.0)
+    beta = torch.sigmoid(torch.randn(total, H, generator=g))
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+    return q, k, v, glog, beta, cu
+
+
+@pytest.mark.parametrize("dtype,d,tol", [(torch.bfloat16, 128, 2e-2), (torch.float16, 128, 2e-2), (torch.float32, 64, 1e-4)])
+def test_packed_scan_matches_oracle_per_sequence(dtype, d, tol):
+    """Ragged lengths (below one chunk, exact chunk multiples, odd tails, an empty sequence) in one
+    call == the oracle run sequence by sequence, outputs and final states, with initial states."""
+    lens, H, Hkv = [130, 64, 7, 0, 300, 1], 4, 2
+    q, k, v, glog, beta, cu = _packed_inputs(lens, H, Hkv, d, dtype, seed=21)
+    S0 = torch.randn(len(lens), H, d, d, generator=torch.Generator().manual_seed(3)) * 0.3
+    o, S = atma_b200.chunk_gated_delta_rule(q=q.cuda()[None], k=k.cuda()[None], v=v.cuda()[None], g=glog.cuda()[None],
+                                            beta=beta.cuda()[None], scale=1.0, initial_state=S0.cuda(),
+                                            output_final_state=True, use_qk_l2norm_in_kernel=True, cu_seqlens=cu.cuda())
+    assert o.shape == (1, sum(lens), H, d) and S.shape == (len(lens), H, d, d)
+    err = max_rel if dtype != torch.float32 else max_abs
+    for i, n in enumerate(lens):
+        a, b = int(cu[i]), int(cu[i + 1])
+        if n == 0:
+            assert torch.equal(S[i].cpu(), S0[i])                  # an empty sequence passes its state through
+            continue
+        o_ref, S_ref = oracle.chunk_gated_delta_rule_oracle(q[None, a:b], k[None, a:b], v[None, a:b], glog[None, a:b],
+                                                            beta[None, a:b], initial_state=S0[i:i + 1])
+        assert err(o[0, a:b], o_ref[0]) < tol, (i, n)
+        assert err(S[i], S_ref[0]) < tol, (i, n)
+
+
+def test_packed_prefill_updates_the_slot_table_in_place():
+    """packed_gated_delta_prefill == the reference's per-sequence loop (scan from the slot's row when the
+    sequence continues a cached prefix, else from zero; copy the final state back): bit-identical to
+    the dense kernel called sequence by sequence, rows of other slots untouched."""
+    lens, H, Hkv, d = [200, 65, 511, 33], 8, 2, 128
+    q, k, v, glog, beta, cu = _packed_inputs(lens, H, Hkv, d, torch.bfloat16, seed=5)
+    gen = torch.Generator().manual_seed(9)
+    table = (torch.randn(7, H, d, d, generator=gen) * 0.2).cuda()
+    slots = torch.tensor([5, 0, 3, 6])
+    has_initial = torch.tensor([1, 0, 1, 0])
+    expect = table.clone()
+    qc, kc, vc, gc, bc = q.cuda(), k.cuda(), v.cuda(), glog.cuda(), beta.cuda()
+    o_expect = torch.empty(sum(lens), H, d, dtype=torch.bfloat16, device="cuda")
+    for i in range(len(lens)):
+        a, b = int(cu[i]), int(cu[i + 1])
+        s0 = expect[slots[i]][None].clone() if has_initial[i] else None
+        oi, Si = atma_b200.chunk_gated_delta_rule(q=qc[None, a:b], k=kc[None, a:b], v=vc[None, a:b], g=gc[None, a:b],
+                                                  beta=bc[None, a:b], scale=1.0, initial_state=s0,
+                                                  output_final_state=True, use_qk_l2norm_in_kernel=True)
+        o_expect[a:b] = oi[0]
+        expect[slots[i]] = Si[0]
+    o = atma_b200.packed_gated_delta_prefill(qc, kc, vc, gc, bc, cu, table, slots, has_initial)
+    assert torch.equal(o, o_expect)
+    assert torch.equal(table, expect)
+    # every sequence continuing from its row (has_initial=None), device-resident cu_seqlens
+    table2 = expect.clone()
+    o2 = atma_b200.packed_gated_delta_prefill(qc, kc, vc, gc, bc, cu.cuda(), table2, slots.cuda())
+    a, b = int(cu[1]), int(cu[2])
+    o_ref, S_ref = atma_b200.chunk_gated_delta_rule(q=qc[None, a:b], k=kc[None, a:b], v=vc[None, a:b], g=gc[None, a:b],
+                                                    beta=bc[None, a:b], scale=1.0, initial_state=expect[0][None],
+                                                    output_final_state=True, use_qk_l2norm_in_kernel=True)
+    assert torch.equal(o2[a:b], o_ref[0]) and torch.equal(table2[0], S_ref[0])
