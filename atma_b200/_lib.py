@@ -84,6 +84,12 @@ _SIGNATURES = {
     "atma_packed_causal_conv1d": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p,
                                           c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
                                           c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "atma_qkv_prep_prefill": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64,
+                                      c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                      c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
+                                      c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                      c_void_p, c_void_p, c_void_p,
+                                      c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p]),
     "atma_store_kvcache": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
                                    c_int, c_int, c_int, c_void_p]),
     "atma_squared_relu_gate": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_int,

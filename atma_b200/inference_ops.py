@@ -89,3 +89,57 @@ def linear_head_rms(x, weight, bias, *, num_heads, head_dim=128, gated=False, ep
                                         x.shape[0], x.shape[1], num_heads, head_dim, 1 if gated else 0,
                                         float(eps), _lib.dtype_code(x), _lib.stream_ptr()))
     return out
+
+
+@torch.no_grad()
+def qkv_prep_prefill(q_gate, k, v, w_q, w_k, w_v, state_q, state_k, state_v, token_seq_starts, token_seq_ends,
+                     token_seq_slots, k_cache=None, v_cache=None, slot_mapping=None, initial_states=None, eps=None):
+    """One launch for what the reference's packed global-layer prefill does in nine
+    (inference/models/atma.py:391-399,431-441,468-471): per-head RMSNorm of q and k, the three
+    Canon convolutions in residual form with their conv-state rows, and the K/V cache scatter.
+
+    q_gate (tokens, H, 2*dk) as the q projection produces it (the gate half is left alone);
+    k, v (tokens, Hkv, dk); w_* (C, K); state_* (rows, C, K-1) updated IN PLACE (None = not
+    kept); token_seq_* per-token int32 maps as for ``packed_causal_conv1d``; k_cache, v_cache
+    with ``slot_mapping`` (tokens,) int64 updated IN PLACE; ``initial_states`` = (iq, ik, iv)
+    tables read as every sequence's left context (must not be the tables being written), None =
+    fresh prompts.  Returns q (tokens, H, dk), k, v (tokens, Hkv, dk), ready for
+    ``polar_attention_packed_fwd`` / the scan with un-expanded KV heads."""
+    _lib.require_cuda(q_gate, "qkv_prep_prefill")
+    lib = _lib.load()
+    total, H, two_dk = q_gate.shape
+    dk = two_dk // 2
+    Hkv = k.shape[1]
+    K = w_q.shape[1]
+    dt = q_gate.dtype
+    if q_gate.stride(2) != 1:
+        q_gate = q_gate.contiguous()
+    k, v = k.to(dt).contiguous(), v.to(dt).contiguous()
+    w_q, w_k, w_v = (w.to(dt).contiguous() for w in (w_q, w_k, w_v))
+    if eps is None:
+        eps = torch.finfo(torch.float32).eps            # what F.rms_norm uses when eps is None (also for 16-bit inputs)
+    for st in (state_q, state_k, state_v):
+        if st is not None and (st.dtype != dt or st.stride(2) != 1 or st.stride(1) != K - 1):
+            raise ValueError("conv-state tables must be in the activation dtype with dense [C, K-1] rows")
+    iq, ik, iv = initial_states if initial_states is not None else (None, None, None)
+    for a, b in ((iq, state_q), (ik, state_k), (iv, state_v)):
+        if a is not None and (b is None or a.shape[1:] != b.shape[1:] or a.stride() != b.stride() or a.dtype != dt):
+            raise ValueError("an initial-state table must have the layout of the table that is written")
+    i32 = lambda t: t.to(device=q_gate.device, dtype=torch.int32).contiguous()
+    s0, e0, sl = i32(token_seq_starts), i32(token_seq_ends), i32(token_seq_slots)
+    if k_cache is not None:
+        if k_cache.dtype != dt or not k_cache.is_contiguous() or not v_cache.is_contiguous():
+            raise ValueError("the caches must be contiguous and in the activation dtype")
+        slot_mapping = slot_mapping.to(device=q_gate.device, dtype=torch.int64).contiguous()
+    q_out = torch.empty((total, H, dk), device=q_gate.device, dtype=dt)
+    k_out = torch.empty((total, Hkv, dk), device=q_gate.device, dtype=dt)
+    v_out = torch.empty((total, Hkv, dk), device=q_gate.device, dtype=dt)
+    ss = lambda t: 0 if t is None else t.stride(0)
+    _lib.check(lib.atma_qkv_prep_prefill(
+        _lib.ptr(q_gate), q_gate.stride(0), q_gate.stride(1), _lib.ptr(k), k.stride(0), _lib.ptr(v), v.stride(0),
+        _lib.ptr(w_q), _lib.ptr(w_k), _lib.ptr(w_v), _lib.ptr(state_q), _lib.ptr(state_k), _lib.ptr(state_v),
+        _lib.ptr(iq), _lib.ptr(ik), _lib.ptr(iv), ss(state_q), ss(state_k), ss(state_v),
+        _lib.ptr(s0), _lib.ptr(e0), _lib.ptr(sl), _lib.ptr(q_out), _lib.ptr(k_out), _lib.ptr(v_out),
+        _lib.ptr(k_cache), _lib.ptr(v_cache), _lib.ptr(slot_mapping) if k_cache is not None else None,
+        total, H, Hkv, dk, K, float(eps), _lib.dtype_code(q_gate), _lib.stream_ptr()))
+    return q_out, k_out, v_out

@@ -254,6 +254,36 @@ int atma_packed_causal_conv1d(const void* x, int64_t x_st, const void* weight,
                               const int32_t* token_seq_slot,
                               int total, int C, int K, int dtype, int residual, void* stream);
 
+/* ----------------------------------------------------------------------------------
+ * Fused q/k/v preparation of a global layer's packed prefill (next-step fusion; the reference
+ * runs it as separate ops: F.rms_norm of q and k per head, x + packed_causal_conv1d(x) for
+ * q, k and v, then store_kvcache - inference/models/atma.py:391-399,431-441,468-471).
+ *   q_gate  [total][H][..]: q is the first dk elements of each head's chunk (element strides
+ *           qg_row_stride / qg_head_stride; the gate half is not touched)
+ *   k, v    [total][Hkv][dk] with row strides in elements
+ *   w_*     conv weights [C][K] in the activation dtype, K in 2..4
+ *   state_* conv-state tables [rows][C][K-1], row stride state_*_stride elements: the row
+ *           token_seq_slot of a sequence receives its last K-1 conv inputs (NULL = not kept)
+ *   init_*  tables of the same layout read as the left context of every sequence with a
+ *           slot >= 0 (a continued prefix); NULL = fresh prompts.  Must not alias state_*.
+ *   token_seq_start / _end / _slot: DEVICE int32 per token, as for atma_packed_causal_conv1d
+ *   q_out [total][H][dk], k_out, v_out [total][Hkv][dk] dense
+ *   k_cache, v_cache [slots][Hkv][dk] + DEVICE int64 slot_mapping per token (-1 = skip);
+ *           NULL caches = no scatter.   eps: the RMSNorm epsilon (F.rms_norm with eps=None uses
+ *           the fp32 machine epsilon, also for 16-bit inputs).  Each fused op rounds to the activation dtype where the
+ *           separate ops would.
+ * ---------------------------------------------------------------------------------- */
+int atma_qkv_prep_prefill(const void* q_gate, int64_t qg_row_stride, int64_t qg_head_stride,
+                          const void* k, int64_t k_row_stride, const void* v, int64_t v_row_stride,
+                          const void* w_q, const void* w_k, const void* w_v,
+                          void* state_q, void* state_k, void* state_v,
+                          const void* init_q, const void* init_k, const void* init_v,
+                          int64_t state_q_stride, int64_t state_k_stride, int64_t state_v_stride,
+                          const int32_t* token_seq_start, const int32_t* token_seq_end,
+                          const int32_t* token_seq_slot, void* q_out, void* k_out, void* v_out,
+                          void* k_cache, void* v_cache, const int64_t* slot_mapping,
+                          int total, int H, int Hkv, int dk, int K, float eps, int dtype, void* stream);
+
 /* ------------------------------------------------------------------------------------
  * Scatter new K/V rows into the paged cache.  Replaces inference/layers/attention.py:7-27
  * behind store_kvcache (:30-56).  key, value [N][D] with row strides (D = Hkv*dk

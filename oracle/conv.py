@@ -66,3 +66,44 @@ def store_kvcache_oracle(key, value, k_cache, v_cache, slot_mapping):
         if s >= 0:
             kf[s] = key[i]
             vf[s] = value[i]
+
+
+def qkv_prep_prefill_oracle(q_gate, k, v, w_q, w_k, w_v, state_q, state_k, state_v, token_seq_starts, token_seq_ends,
+                            token_seq_slots, k_cache, v_cache, slot_mapping, initial_states=None, eps=None):
+    """The q/k/v preparation of a global layer's packed prefill, op by op as the reference runs it
+    (inference/models/atma.py:391-399 rms_norm of q and k per head; :431-441 x + packed conv for
+    q, k, v; :468-471 store_kvcache).  q_gate (tokens, H, 2*dk); k, v (tokens, Hkv, dk); conv
+    weights (C, K); state tables (rows, C, K-1) MUTATED; caches MUTATED.  ``initial_states`` =
+    (iq, ik, iv) tables read as left context of every sequence (a continued prefix), None = fresh
+    prompts as in the reference's packed path.  Every op rounds to the input dtype as eager does.
+    Returns q (tokens, H, dk), k, v (tokens, Hkv, dk) in the input dtype."""
+    import torch.nn.functional as F
+    total, H, two_dk = q_gate.shape
+    dk = two_dk // 2
+    dt = q_gate.dtype
+    qn = F.rms_norm(q_gate[..., :dk], (dk,), eps=eps).reshape(total, -1)
+    kn = F.rms_norm(k, (dk,), eps=eps).reshape(total, -1)
+    vn = v.reshape(total, -1)
+    outs = []
+    for x, w, st, idx in ((qn, w_q, state_q, 0), (kn, w_k, state_k, 1), (vn, w_v, state_v, 2)):
+        conv = torch.zeros(total, x.shape[1], dtype=torch.float32)
+        done = set()
+        for t in range(total):
+            s, e, slot = int(token_seq_starts[t]), int(token_seq_ends[t]), int(token_seq_slots[t])
+            if (s, e) in done:
+                continue
+            done.add((s, e))
+            init = None
+            if initial_states is not None and slot >= 0:
+                init = initial_states[idx][slot]
+            o, fin = causal_conv1d_prefill(x[s:e], w, init)
+            conv[s:e] = o
+            if slot >= 0:
+                st[slot] = fin.to(st.dtype)
+        outs.append((x.float() + conv.to(dt).float()).to(dt))
+    q_out = outs[0].view(total, H, dk)
+    k_out = outs[1].view(total, -1, dk)
+    v_out = outs[2].view(total, -1, dk)
+    if k_cache is not None:
+        store_kvcache_oracle(k_out, v_out, k_cache, v_cache, slot_mapping)
+    return q_out, k_out, v_out

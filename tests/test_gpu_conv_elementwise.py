@@ -5,7 +5,7 @@ import torch
 
 import atma_b200
 import oracle
-from conftest import max_abs
+from conftest import max_abs, max_rel
 from gpu_util import rand
 
 pytestmark = pytest.mark.gpu
@@ -119,3 +119,83 @@ def test_linear_head_rms(gated, heads):
     expected = oracle.linear_head_rms_oracle(x, weight, bias, num_heads=heads, head_dim=head_dim, gated=gated)
     actual = atma_b200.linear_head_rms(x.cuda(), weight.cuda(), bias.cuda(), num_heads=heads, head_dim=head_dim, gated=gated)
     torch.testing.assert_close(actual.float().cpu(), expected, atol=0.02, rtol=0.02)
+
+
+# ---- fused q/k/v preparation of the packed prefill (RMSNorm + 3 residual convs + state rows + cache scatter) ----
+def _prep_case(dtype, lens, H=4, Hkv=2, dk=128, K=4, seed=0, rows=6):
+    g = torch.Generator().manual_seed(seed)
+    total = sum(lens)
+    q_gate = torch.randn(total, H, 2 * dk, generator=g).to(dtype)
+    k = torch.randn(total, Hkv, dk, generator=g).to(dtype)
+    v = torch.randn(total, Hkv, dk, generator=g).to(dtype)
+    w = [(torch.randn(C, K, generator=g) * 0.3).to(dtype) for C in (H * dk, Hkv * dk, Hkv * dk)]
+    states = [torch.randn(rows, C, K - 1, generator=g).to(dtype) for C in (H * dk, Hkv * dk, Hkv * dk)]
+    slots = torch.randperm(rows, generator=g)[:len(lens)].tolist()
+    slots[-1] = -1                                            # a sequence whose state is not kept
+    starts, ends, sl = [], [], []
+    pos = 0
+    for n, s in zip(lens, slots):
+        starts += [pos] * n; ends += [pos + n] * n; sl += [s] * n
+        pos += n
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32)
+    n_cache = total + 5
+    k_cache = torch.randn(n_cache, Hkv, dk, generator=g).to(dtype)
+    v_cache = torch.randn(n_cache, Hkv, dk, generator=g).to(dtype)
+    slot_mapping = torch.randperm(n_cache, generator=g)[:total].to(torch.int64)
+    slot_mapping[3] = -1
+    return q_gate, k, v, w, states, i32(starts), i32(ends), i32(sl), k_cache, v_cache, slot_mapping
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.bfloat16, 2e-2), (torch.float32, 1e-4)])
+@pytest.mark.parametrize("continued", [False, True])
+def test_qkv_prep_prefill_matches_the_op_by_op_oracle(dtype, tol, continued):
+    """Ragged packed sequences (shorter than the kernel, crossing the 32-token tile, one without a
+    state slot): the fused launch == rms_norm + x + conv(x) + state write + store_kvcache run op by
+    op on the CPU; state rows and cache rows that nothing addresses stay as they were."""
+    lens = [2, 37, 1, 64, 29]
+    q_gate, k, v, w, states, s0, e0, sl, k_cache, v_cache, sm = _prep_case(dtype, lens, seed=3)
+    init = [s.clone() for s in states] if continued else None
+    ref_states = [s.clone() for s in states]
+    ref_kc, ref_vc = k_cache.clone(), v_cache.clone()
+    q_ref, k_ref, v_ref = oracle.qkv_prep_prefill_oracle(q_gate, k, v, *w, *ref_states, s0, e0, sl, ref_kc, ref_vc, sm,
+                                                         initial_states=init)
+    dev_states = [s.cuda() for s in states]
+    kc, vc = k_cache.cuda(), v_cache.cuda()
+    q_o, k_o, v_o = atma_b200.qkv_prep_prefill(q_gate.cuda(), k.cuda(), v.cuda(), *(x.cuda() for x in w), *dev_states,
+                                               s0.cuda(), e0.cuda(), sl.cuda(), kc, vc, sm.cuda(),
+                                               initial_states=None if init is None else [x.cuda() for x in init])
+    err = max_rel if dtype != torch.float32 else max_abs
+    for got, want in ((q_o, q_ref), (k_o, k_ref), (v_o, v_ref)):
+        assert got.dtype == dtype and err(got, want) < tol
+    for got, want, before in zip(dev_states, ref_states, states):
+        assert err(got, want) < tol
+        untouched = [r for r in range(before.shape[0]) if r not in sl.tolist()]
+        assert torch.equal(got.cpu()[untouched], before[untouched])
+    assert err(kc, ref_kc) < tol and err(vc, ref_vc) < tol
+    unused = [r for r in range(k_cache.shape[0]) if r not in sm.tolist()]
+    assert torch.equal(kc.cpu()[unused], k_cache[unused]) and torch.equal(vc.cpu()[unused], v_cache[unused])
+    assert torch.equal(kc[sm[5]], k_o[5]) and torch.equal(vc[sm[5]], v_o[5])      # the cache holds the post-conv rows
+
+
+def test_qkv_prep_prefill_equals_the_separate_kernels():
+    """Against this library's own unfused calls (F.rms_norm, packed_causal_conv1d, store_kvcache) in bf16:
+    same rounding points, so q, k, v and the cache rows agree to the last bit or one bf16 ulp."""
+    import torch.nn.functional as F
+    lens = [100, 31, 70]
+    q_gate, k, v, w, states, s0, e0, sl, k_cache, v_cache, sm = _prep_case(torch.bfloat16, lens, seed=11)
+    sl = torch.where(sl < 0, torch.zeros_like(sl) + 5, sl)
+    dk = k.shape[-1]
+    qg, kg, vg = q_gate.cuda(), k.cuda(), v.cuda()
+    wg = [x.cuda() for x in w]
+    st_f = [s.cuda() for s in states]
+    kc, vc = k_cache.cuda(), v_cache.cuda()
+    q_o, k_o, v_o = atma_b200.qkv_prep_prefill(qg, kg, vg, *wg, *st_f, s0.cuda(), e0.cuda(), sl.cuda(), kc, vc, sm.cuda())
+    st_u = [s.cuda() for s in states]
+    xs = [F.rms_norm(qg[..., :dk], (dk,)).reshape(len(qg), -1), F.rms_norm(kg, (dk,)).reshape(len(kg), -1),
+          vg.reshape(len(vg), -1)]
+    outs = [x + atma_b200.packed_causal_conv1d(x, wi, si, s0.cuda(), e0.cuda(), sl.cuda()) for x, wi, si in zip(xs, wg, st_u)]
+    for got, want in zip((q_o, k_o, v_o), outs):
+        assert max_rel(got.reshape(want.shape), want) < 8e-3
+        assert (got.reshape(want.shape) != want).float().mean() < 0.02
+    for a, b in zip(st_f, st_u):
+        assert max_rel(a, b) < 8e-3
