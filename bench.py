@@ -479,7 +479,7 @@ def emit(obj):
 
 
 def main():
-    global _REAL_STDOUT
+    global _REAL_STDOUT, T_PREFILL, METRIC
     sys.stdout.flush()
     _REAL_STDOUT = os.dup(1)
     os.dup2(2, 1)
@@ -498,7 +498,6 @@ def main():
                     help="run a few launches of ONE kernel on a small case (a few hundred MB, larger than L2) "
                          "and exit; meant to be wrapped in ncu")
     args = ap.parse_args()
-    global T_PREFILL, METRIC
     if args.tokens != T_PREFILL:
         T_PREFILL = args.tokens
         METRIC = f"global_layer_prefill_tok_s_at_{T_PREFILL}"
