@@ -1,0 +1,97 @@
+"""Packed prefill of one global attention layer, composed from this package's kernels.
+
+Host-side mirror of the packed ("grouped") prefill branch of the reference's
+``AtmaGlobalAttention.forward`` (inference/models/atma.py:389-399,429-441,466-510) together with
+the per-token maps its model runner builds (inference/engine/model_runner.py:395-404):
+
+    q|gate, k, v projections      cuBLAS (F.linear)
+    RMSNorm + Canon convs + cache  qkv_prep_prefill            one launch, conv-state rows and K/V pages written
+    Polar attention                polar_attention_packed_fwd  un-expanded KV heads, one launch for all sequences
+    memory branch                  packed_gated_delta_prefill  one call for all sequences, state rows in place,
+                                                               on a side stream beside the attention
+    combine                        W_o(c * sigmoid(gate)) + W_mu(mag) + mem.proj(RMSNorm(r) * sigmoid(mem.gate x))
+
+The reference expands K/V to H heads, loops over the sequences for the memory branch and runs
+the q/k/v preparation as nine separate ops; the results are the same.
+"""
+
+import torch
+import torch.nn.functional as F
+
+from .gated_delta import packed_gated_delta_prefill
+from .inference_ops import qkv_prep_prefill
+from .mixing import _side_stream
+from .polar import polar_attention_packed_fwd
+
+
+class PackedMaps:
+    """Device-side index tensors of a packed batch (sequences back to back on the token axis)."""
+
+    def __init__(self, seqlens, seq_slots, device, tile=128):
+        starts, ends, slots, t_seq, t_q, t_len, cu = [], [], [], [], [], [], [0]
+        pos = 0
+        for n, slot in zip(seqlens, seq_slots):
+            for q0 in range(0, n, tile):
+                t_seq.append(pos); t_q.append(q0); t_len.append(n)
+            starts += [pos] * n; ends += [pos + n] * n; slots += [int(slot)] * n
+            pos += n
+            cu.append(pos)
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=device)
+        self.total = pos
+        self.token_seq_starts, self.token_seq_ends, self.token_seq_slots = i32(starts), i32(ends), i32(slots)
+        self.tile_seq_starts, self.tile_q_starts, self.tile_seq_lens = i32(t_seq), i32(t_q), i32(t_len)
+        self.cu_seqlens = i32(cu)
+        self.seq_slots = torch.tensor([int(s) for s in seq_slots], dtype=torch.int64, device=device)
+
+
+def _linear(x, sd, name):
+    b = sd.get(name + ".bias")
+    return F.linear(x, sd[name + ".weight"].to(x.dtype), None if b is None else b.to(x.dtype))
+
+
+@torch.no_grad()
+def global_attention_prefill_packed(x, sd, maps, *, num_heads, num_kv_heads, head_dim, conv_states, mem_state_table,
+                                    k_cache=None, v_cache=None, slot_mapping=None, window=None, mem_gamma_bias=3.9,
+                                    mem_beta_bias=0.0, prefix="attn.", overlap=True):
+    """x (tokens, D) packed fresh prompts; ``sd`` the attention module's tensors (reference names
+    under ``prefix``: q, k, v, proj, mu_proj, canon_q/k/v, the five Polar parameters, and mem.*
+    when the layer has a memory); ``maps`` a ``PackedMaps``; ``conv_states`` = (q, k, v) conv-state
+    tables and ``mem_state_table`` (rows, H, dk, dk) fp32, all updated IN PLACE at the sequences'
+    slots; ``k_cache``/``v_cache`` with ``slot_mapping`` receive the post-conv K/V rows.
+    Returns the layer's mixing output (tokens, D)."""
+    P = prefix
+    H, Hkv, dk = num_heads, num_kv_heads, head_dim
+    total = x.shape[0]
+    q_gate = _linear(x, sd, P + "q").view(total, H, 2 * dk)
+    k = _linear(x, sd, P + "k").view(total, Hkv, dk)
+    v = _linear(x, sd, P + "v").view(total, Hkv, dk)
+    w = [sd[P + f"canon_{n}.weight"].squeeze(1) for n in ("q", "k", "v")]
+    q, k, v = qkv_prep_prefill(q_gate, k, v, *w, *conv_states, maps.token_seq_starts, maps.token_seq_ends,
+                               maps.token_seq_slots, k_cache, v_cache, slot_mapping)
+
+    has_mem = (P + "mem.proj.weight") in sd
+    cur = torch.cuda.current_stream(x.device)
+    side = _side_stream(x.device) if (overlap and has_mem) else cur
+    r = None
+    if has_mem:
+        if side is not cur:
+            side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            g = F.logsigmoid(_linear(x, sd, P + "mem.w_gamma").float() + mem_gamma_bias)
+            beta = torch.sigmoid(_linear(x, sd, P + "mem.w_beta").float() + mem_beta_bias)
+            r = packed_gated_delta_prefill(q, k, v, g, beta, maps.cu_seqlens, mem_state_table, maps.seq_slots)
+            r = F.rms_norm(r, (dk,)).reshape(total, H * dk)
+            mem_out = _linear(r * torch.sigmoid(_linear(x, sd, P + "mem.gate")), sd, P + "mem.proj")
+
+    c, mag = polar_attention_packed_fwd(q, k, v, maps.tile_seq_starts, maps.tile_q_starts, maps.tile_seq_lens,
+                                        window=window, v_null=sd[P + "v_null"], null_base=sd[P + "null_base"],
+                                        null_slope_raw=sd[P + "null_slope_raw"], len_gain_raw=sd[P + "len_gain_raw"],
+                                        mag_beta_raw=sd[P + "mag_beta_raw"])
+    gate = q_gate[..., dk:].reshape(total, H * dk)
+    out = _linear(c.reshape(total, H * dk) * torch.sigmoid(gate), sd, P + "proj") + _linear(mag, sd, P + "mu_proj")
+    if has_mem:
+        if side is not cur:
+            cur.wait_stream(side)
+            mem_out.record_stream(cur)
+        out = out + mem_out
+    return out
