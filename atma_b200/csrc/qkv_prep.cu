@@ -6,18 +6,21 @@
 // (inference/models/atma.py:396-399,431-441,468-471; kernel/inference_ops_triton.py:139-160;
 // inference/layers/attention.py:30-56).
 //
-// One CTA = one head (of q, k or v) x a tile of 32 tokens.  Thread c owns channel c of the head:
-// it holds the tile's inputs (plus the K-1 rows before the tile) in registers, the row sums of
-// squares are reduced across the CTA through shared memory, and every output is written once.
-// The kernel is bandwidth-bound: it reads each projection element once (a (K-1)/32 halo aside)
-// and writes q, k, v once plus the K/V cache rows.
+// One CTA = one head (of q, k or v) x 256 tokens.  Sixteen threads cover a head row with eight
+// channels each (16-byte accesses); such a group streams 32 tokens (plus the K-1 rows before
+// them): eight packed rows per thread are always in flight, the last K normalised rows sit in
+// registers, the row sums of squares are reduced with shuffles, and every output is written once.
+// The kernel is bandwidth-bound: each projection element comes from DRAM once (a (K-1)/32 halo
+// aside) and q, k, v plus the K/V cache rows go out once.
 #include "common.cuh"
 
 namespace atma {
 
 namespace {
 
-constexpr int kPrepTok = 32;       // tokens per CTA
+constexpr int kPrepTok = 32;       // tokens per 16-thread group
+constexpr int kPrepGroups = 8;     // groups per CTA: a CTA covers 256 tokens of one head
+constexpr int kPrepAhead = 8;      // rows each thread keeps in flight
 constexpr int kPrepMaxK = 4;
 
 struct PrepArgs {
@@ -34,16 +37,83 @@ struct PrepArgs {
   float eps;
 };
 
+// eight consecutive channels per thread: one 16-byte access for 16-bit types, two for fp32
+template <typename T> __device__ __forceinline__ void load8(const T* p, float (&o)[8]);
+template <> __device__ __forceinline__ void load8<float>(const float* p, float (&o)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+}
+template <> __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&o)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); o[2 * i] = f.x; o[2 * i + 1] = f.y; }
+}
+template <> __device__ __forceinline__ void load8<__half>(const __half* p, float (&o)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const float2 f = __half22float2(h[i]); o[2 * i] = f.x; o[2 * i + 1] = f.y; }
+}
+template <typename T> __device__ __forceinline__ void store8(T* p, const float (&v)[8]);
+template <> __device__ __forceinline__ void store8<float>(float* p, const float (&v)[8]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+template <> __device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[8]) {
+  uint4 u;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+  *reinterpret_cast<uint4*>(p) = u;
+}
+template <> __device__ __forceinline__ void store8<__half>(__half* p, const float (&v)[8]) {
+  uint4 u;
+  __half2* h = reinterpret_cast<__half2*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+  *reinterpret_cast<uint4*>(p) = u;
+}
+
+// a row fragment as it comes from memory (kept packed while it waits in the prefetch ring)
+template <typename T> struct RawRow { uint4 u; };
+template <> struct RawRow<float> { float4 lo, hi; };
+template <typename T> __device__ __forceinline__ void raw_load(RawRow<T>& r, const T* p) { r.u = *reinterpret_cast<const uint4*>(p); }
+template <> __device__ __forceinline__ void raw_load<float>(RawRow<float>& r, const float* p) {
+  r.lo = *reinterpret_cast<const float4*>(p); r.hi = *reinterpret_cast<const float4*>(p + 4);
+}
+template <typename T> __device__ __forceinline__ void raw_zero(RawRow<T>& r) { r.u = make_uint4(0u, 0u, 0u, 0u); }
+template <> __device__ __forceinline__ void raw_zero<float>(RawRow<float>& r) {
+  r.lo = make_float4(0.f, 0.f, 0.f, 0.f); r.hi = r.lo;
+}
+template <typename T> __device__ __forceinline__ void raw_unpack(const RawRow<T>& r, float (&o)[8]) {
+  load8<T>(reinterpret_cast<const T*>(&r.u), o);
+}
+template <> __device__ __forceinline__ void raw_unpack<float>(const RawRow<float>& r, float (&o)[8]) {
+  o[0] = r.lo.x; o[1] = r.lo.y; o[2] = r.lo.z; o[3] = r.lo.w; o[4] = r.hi.x; o[5] = r.hi.y; o[6] = r.hi.z; o[7] = r.hi.w;
+}
+
 template <typename T, int K>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 3)
 qkv_prep_kernel(const PrepArgs a) {
-  __shared__ float s_part[kPrepTok + kPrepMaxK - 1][4];
-  const int c = threadIdx.x, lane = c & 31, warp = c >> 5;
-  const int t0 = blockIdx.x * kPrepTok;
-  const int unit = blockIdx.y;                       // [0,H): q heads, [H,H+Hkv): k heads, then v heads
+  constexpr int kCtaTok = kPrepTok * kPrepGroups;
+  __shared__ int s_s0[kCtaTok], s_e0[kCtaTok], s_slot[kCtaTok];
+  __shared__ long long s_cs[kCtaTok];
+  const int grp = threadIdx.x >> 4, li = threadIdx.x & 15;      // 16 threads x 8 channels cover one head row
+  const int t0 = (blockIdx.x * kPrepGroups + grp) * kPrepTok;   // this group's first token
+  for (int i = threadIdx.x; i < kCtaTok; i += 128) {             // the per-token maps of the CTA's tokens
+    const int t = blockIdx.x * kCtaTok + i;
+    const bool ok = t < a.total;
+    s_s0[i] = ok ? a.seq_start[t] : 0;
+    s_e0[i] = ok ? a.seq_end[t] : 0;
+    s_slot[i] = ok ? a.seq_slot[t] : -1;
+    s_cs[i] = (ok && a.slot_mapping != nullptr) ? a.slot_mapping[t] : -1;
+  }
+  const int unit = blockIdx.y;                                   // [0,H): q heads, [H,H+Hkv): k heads, then v heads
   const int which = unit < a.H ? 0 : (unit < a.H + a.Hkv ? 1 : 2);
   const int head = which == 0 ? unit : (which == 1 ? unit - a.H : unit - a.H - a.Hkv);
   const int heads = which == 0 ? a.H : a.Hkv;
+  const int c = li * 8;
   const bool active = c < a.dk;
   const bool normalize = which != 2;
 
@@ -51,75 +121,105 @@ qkv_prep_kernel(const PrepArgs a) {
   if (which == 0) { src = (const T*)a.qg + (int64_t)head * a.qg_head; row_st = a.qg_row; }
   else if (which == 1) { src = (const T*)a.k + (int64_t)head * a.dk; row_st = a.k_row; }
   else { src = (const T*)a.v + (int64_t)head * a.dk; row_st = a.v_row; }
-  T* dst = (T*)(which == 0 ? a.q_out : (which == 1 ? a.k_out : a.v_out)) + (int64_t)head * a.dk;
+  src += c;
+  T* dst = (T*)(which == 0 ? a.q_out : (which == 1 ? a.k_out : a.v_out)) + (int64_t)head * a.dk + c;
   const int64_t dst_row = (int64_t)heads * a.dk;
-  const int ch = head * a.dk + c;                    // channel of the conv / state table
-
-  // ---- inputs of rows t0-(K-1) .. t0+31 and their sums of squares ---------------------------------
-  float x[kPrepTok + K - 1];
-#pragma unroll
-  for (int i = 0; i < kPrepTok + K - 1; ++i) {
-    const int t = t0 - (K - 1) + i;
-    x[i] = (active && t >= 0 && t < a.total) ? to_f32(src[(int64_t)t * row_st + c]) : 0.f;
-  }
-  if (normalize) {
-#pragma unroll
-    for (int i = 0; i < kPrepTok + K - 1; ++i) {
-      const float s = warp_sum(x[i] * x[i]);
-      if (lane == 0) s_part[i][warp] = s;
-    }
-    __syncthreads();
-    const float inv_dk = 1.0f / (float)a.dk;
-#pragma unroll
-    for (int i = 0; i < kPrepTok + K - 1; ++i) {
-      const float ss = s_part[i][0] + s_part[i][1] + s_part[i][2] + s_part[i][3];
-      x[i] = round_through<T>(x[i] * rsqrtf(ss * inv_dk + a.eps));      // the eager op rounds to T here
-    }
-  }
-  if (!active) return;
-
-  float wt[K];
-#pragma unroll
-  for (int j = 0; j < K; ++j) wt[j] = to_f32(((const T*)a.w[which])[(int64_t)ch * K + j]);
+  const int ch = head * a.dk + c;                                // first of this thread's conv channels
+  T* cache = (T*)(which == 1 ? a.k_cache : a.v_cache);
   T* state = (T*)a.state[which];
   const T* init = (const T*)a.init[which];
   const int64_t state_ss = a.state_ss[which];
+  const float inv_dk = 1.0f / (float)a.dk;
 
+  float wt[8][K];
 #pragma unroll
-  for (int i = 0; i < kPrepTok; ++i) {
-    const int t = t0 + i;
-    if (t >= a.total) break;
-    const int s0 = a.seq_start[t], e0 = a.seq_end[t], slot = a.seq_slot[t];
+  for (int j = 0; j < 8; ++j)
+#pragma unroll
+    for (int kk = 0; kk < K; ++kk)
+      wt[j][kk] = active ? to_f32(((const T*)a.w[which])[(int64_t)(ch + j) * K + kk]) : 0.f;
+
+  // ---- stream the rows t0-(K-1) .. t0+kPrepTok-1: a ring of kPrepAhead packed rows in flight, a
+  //      window of the last K normalised rows in registers ----------------------------------------------
+  RawRow<T> ring[kPrepAhead];
+  auto fetch = [&](RawRow<T>& r, int row) {                      // row index relative to t0-(K-1)
+    const int t = t0 - (K - 1) + row;
+    if (active && t >= 0 && t < a.total && row < kPrepTok + K - 1) raw_load<T>(r, src + (int64_t)t * row_st);
+    else raw_zero<T>(r);
+  };
+#pragma unroll
+  for (int i = 0; i < kPrepAhead; ++i) fetch(ring[i], i);
+  __syncthreads();                                               // the token maps are in shared memory
+
+  float win[K][8];
+#pragma unroll
+  for (int i = 0; i < kPrepTok + K - 1; ++i) {
+    float (&x)[8] = win[i % K];
+    raw_unpack<T>(ring[i % kPrepAhead], x);
+    fetch(ring[i % kPrepAhead], i + kPrepAhead);
+    if (normalize) {
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss = fmaf(x[j], x[j], ss);
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);     // the 16 threads of the row
+      const float r = rsqrtf(ss * inv_dk + a.eps);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] = round_through<T>(x[j] * r);                 // the eager op rounds to T here
+    }
+    if (i < K - 1) continue;                                     // still filling the window
+    const int ti = grp * kPrepTok + (i - (K - 1));
+    const int t = t0 + (i - (K - 1));
+    if (!active || t >= a.total) continue;
+    const int s0 = s_s0[ti], e0 = s_e0[ti], slot = s_slot[ti];
     const bool from_state = init != nullptr && slot >= 0;
-    // input `back` rows before token t as this sequence sees it: its own rows, else its saved state, else 0
-    auto tap = [&](int back) -> float {
-      if (t - back >= s0) return x[i + (K - 1) - back];
-      if (from_state) return to_f32(init[slot * state_ss + (int64_t)ch * (K - 1) + (K - 1) - (s0 - (t - back))]);
+    // channel j's input `back` rows before token t as this sequence sees it: its own rows, else
+    // its saved state, else 0
+    auto tap = [&](int back, int j) -> float {
+      if (t - back >= s0) return win[(i - back) % K][j];
+      if (from_state) return to_f32(init[slot * state_ss + (int64_t)(ch + j) * (K - 1) + (K - 1) - (s0 - (t - back))]);
       return 0.f;
     };
-    float acc = 0.f;
+    float y[8];
+    if (t - (K - 1) >= s0) {                                     // the common case: all taps inside the sequence
 #pragma unroll
-    for (int j = 0; j < K; ++j) acc = fmaf(tap(K - 1 - j), wt[j], acc);
-    const T y = from_f32<T>(x[i + K - 1] + round_through<T>(acc));      // x + conv(x), each rounded as eager does
-    dst[(int64_t)t * dst_row + c] = y;
-    if (which != 0 && a.slot_mapping != nullptr) {
-      const int64_t cs = a.slot_mapping[t];
-      if (cs >= 0) ((T*)(which == 1 ? a.k_cache : a.v_cache))[(cs * a.Hkv + head) * a.dk + c] = y;
+      for (int j = 0; j < 8; ++j) {
+        float acc = 0.f;
+#pragma unroll
+        for (int kk = 0; kk < K; ++kk) acc = fmaf(win[(i - (K - 1) + kk) % K][j], wt[j][kk], acc);
+        y[j] = x[j] + round_through<T>(acc);                     // x + conv(x), the conv rounded as eager does
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float acc = 0.f;
+#pragma unroll
+        for (int kk = 0; kk < K; ++kk) acc = fmaf(tap(K - 1 - kk, j), wt[j][kk], acc);
+        y[j] = x[j] + round_through<T>(acc);
+      }
+    }
+    store8<T>(dst + (int64_t)t * dst_row, y);
+    if (which != 0) {
+      const int64_t cs = s_cs[ti];
+      if (cs >= 0) store8<T>(cache + (cs * a.Hkv + head) * a.dk + c, y);
     }
     if (t == e0 - 1 && state != nullptr && slot >= 0) {
       // this token closes its sequence: persist its last K-1 conv inputs, oldest first
-      float keep[K - 1];
 #pragma unroll
-      for (int j = 0; j < K - 1; ++j) keep[j] = tap(K - 2 - j);
+      for (int j = 0; j < 8; ++j) {
+        float keep[K - 1];
 #pragma unroll
-      for (int j = 0; j < K - 1; ++j) state[slot * state_ss + (int64_t)ch * (K - 1) + j] = from_f32<T>(keep[j]);
+        for (int kk = 0; kk < K - 1; ++kk) keep[kk] = tap(K - 2 - kk, j);
+#pragma unroll
+        for (int kk = 0; kk < K - 1; ++kk) state[slot * state_ss + (int64_t)(ch + j) * (K - 1) + kk] = from_f32<T>(keep[kk]);
+      }
     }
   }
 }
 
 template <typename T>
 int launch_prep(const PrepArgs& a, cudaStream_t st) {
-  dim3 grid((a.total + kPrepTok - 1) / kPrepTok, a.H + 2 * a.Hkv), block(128);
+  const int per_cta = kPrepTok * kPrepGroups;
+  dim3 grid((a.total + per_cta - 1) / per_cta, a.H + 2 * a.Hkv), block(128);
   switch (a.K) {
     case 2: qkv_prep_kernel<T, 2><<<grid, block, 0, st>>>(a); break;
     case 3: qkv_prep_kernel<T, 3><<<grid, block, 0, st>>>(a); break;
@@ -144,7 +244,13 @@ extern "C" int atma_qkv_prep_prefill(const void* q_gate, int64_t qg_row_stride, 
                                      void* k_cache, void* v_cache, const int64_t* slot_mapping, int total, int H,
                                      int Hkv, int dk, int K, float eps, int dtype, void* stream) {
   ATMA_REQUIRE(dtype_ok(dtype), "qkv_prep_prefill: unsupported dtype %d", dtype);
-  ATMA_REQUIRE(H > 0 && Hkv > 0 && dk > 0 && dk <= 128, "qkv_prep_prefill: needs head_dim <= 128 (got %d)", dk);
+  ATMA_REQUIRE(H > 0 && Hkv > 0 && dk > 0 && dk <= 128 && dk % 8 == 0,
+               "qkv_prep_prefill: needs head_dim <= 128 and a multiple of 8 (got %d)", dk);
+  ATMA_REQUIRE(qg_row_stride % 8 == 0 && qg_head_stride % 8 == 0 && k_row_stride % 8 == 0 && v_row_stride % 8 == 0 &&
+                   (uintptr_t)q_gate % 16 == 0 && (uintptr_t)k % 16 == 0 && (uintptr_t)v % 16 == 0 &&
+                   (uintptr_t)q_out % 16 == 0 && (uintptr_t)k_out % 16 == 0 && (uintptr_t)v_out % 16 == 0 &&
+                   (uintptr_t)k_cache % 16 == 0 && (uintptr_t)v_cache % 16 == 0,
+               "qkv_prep_prefill: rows must be 16-byte aligned (pointers and strides in multiples of 8 elements)");
   ATMA_REQUIRE(K >= 2 && K <= kPrepMaxK, "qkv_prep_prefill: kernel size %d not in 2..4", K);
   ATMA_REQUIRE(token_seq_start && token_seq_end && token_seq_slot, "qkv_prep_prefill: the per-token sequence arrays are required");
   ATMA_REQUIRE((k_cache == nullptr) == (v_cache == nullptr), "qkv_prep_prefill: pass both caches or neither");

@@ -253,6 +253,44 @@ def run_reference(args, rank):
     emit(line)
 
 
+def bench_prep(ab, dev, tokens, n_seqs, iters):
+    """The fused q/k/v preparation of a packed prefill (RMSNorm, three residual convs, state rows,
+    cache scatter) on `n_seqs` equal sequences.  Algorithmic bytes: the q half of the q|gate
+    projection, k, v read; q, k, v and the two cache rows written."""
+    from atma_b200.layer import PackedMaps
+    g = torch.Generator().manual_seed(1)
+    per = tokens // n_seqs
+    total = per * n_seqs
+    maps = PackedMaps([per] * n_seqs, list(range(n_seqs)), dev)
+    q_gate = torch.randn(total, H, 2 * DK, generator=g).bfloat16().to(dev)
+    k = torch.randn(total, HKV, DK, generator=g).bfloat16().to(dev)
+    v = torch.randn(total, HKV, DK, generator=g).bfloat16().to(dev)
+    w = [(torch.randn(C, 4, generator=g) * 0.3).bfloat16().to(dev) for C in (H * DK, HKV * DK, HKV * DK)]
+    st = [torch.zeros(n_seqs, C, 3, dtype=torch.bfloat16, device=dev) for C in (H * DK, HKV * DK, HKV * DK)]
+    kc = torch.zeros(total, HKV, DK, dtype=torch.bfloat16, device=dev)
+    vc = torch.zeros_like(kc)
+    # cache slots as the engine hands them out: 256-token pages in random order, rows in order inside a page
+    pages = torch.randperm((total + DEC_BLOCK - 1) // DEC_BLOCK, generator=g)
+    t_idx = torch.arange(total)
+    sm = (pages[t_idx // DEC_BLOCK] * DEC_BLOCK + t_idx % DEC_BLOCK).to(dev)
+    kc = torch.zeros(pages.numel() * DEC_BLOCK, HKV, DK, dtype=torch.bfloat16, device=dev)
+    vc = torch.zeros_like(kc)
+    run = lambda: ab.qkv_prep_prefill(q_gate, k, v, *w, *st, maps.token_seq_starts, maps.token_seq_ends,
+                                      maps.token_seq_slots, kc, vc, sm)
+    for _ in range(3):
+        run()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda._sleep(20_000_000)          # keep the GPU busy while the host queues the launches back to back
+    e0.record()
+    for _ in range(iters):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    nbytes = total * (2 * H + 5 * HKV) * DK * 2.0
+    return e0.elapsed_time(e1) / iters, nbytes, total
+
+
 def profile_case(which):
     """A small case of one kernel for an ncu capture: inputs larger than L2, well under 1 GB,
     five launches.  Prints the shape so that per-launch figures can be scaled."""
@@ -283,6 +321,10 @@ def profile_case(which):
             ab.polar_attention_decode(q, kc, vc, bt, cl, **P)
         info = {"kernel": "polar_decode_split_mma_kernel", "B": Bd, "context": ctx,
                 "bytes_per_launch": 2.0 * Bd * ctx * HKV * DK * 2}
+    elif which == "prep":
+        ms, nbytes, total = bench_prep(ab, dev, tokens=65536, n_seqs=8, iters=5)
+        info = {"kernel": "qkv_prep_kernel", "tokens": total, "bytes_per_launch": nbytes, "ms": ms,
+                "gbs": nbytes / (ms * 1e-3) / 1e9}
     else:
         B, T = 2, 16384
         q = torch.randn(B, T, H, DK, generator=g).bfloat16().to(dev)
@@ -494,7 +536,7 @@ def main():
                     help="N > 1: issue the context-parallel step launch by launch instead of replaying a CUDA graph")
     ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline leg (profiling runs)")
     ap.add_argument("--skip-decode", action="store_true", help="omit the decode leg (profiling runs)")
-    ap.add_argument("--profile", default=None, choices=["prefill", "decode", "scan"],
+    ap.add_argument("--profile", default=None, choices=["prefill", "decode", "scan", "prep"],
                     help="run a few launches of ONE kernel on a small case (a few hundred MB, larger than L2) "
                          "and exit; meant to be wrapped in ncu")
     args = ap.parse_args()
