@@ -64,7 +64,7 @@ constexpr int kAfLd = 66;      // fp32 A rows: even stride so that column pairs 
 constexpr int kTfLd = 17;
 
 template <bool kBf16>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 3)
 scan_local_mma_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ k, const uint16_t* __restrict__ v,
                       const float* __restrict__ g, const float* __restrict__ beta, uint8_t* __restrict__ rec_base,
                       float* __restrict__ gc_base, int Tlen, int H, int Hkv, int NC, int normalize_qk, float scale,
@@ -75,8 +75,8 @@ scan_local_mma_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict
   uint8_t* Vs = Qs + kC * kD * 2;
   float* Af = reinterpret_cast<float*>(Vs + kC * kD * 2);      // [64][66] strictly lower triangular A
   float* Tf = Af + kC * kAfLd;                                  // [4][16][17] inverses of the diagonal blocks
-  uint8_t* Gb = reinterpret_cast<uint8_t*>(Tf + 4 * 16 * kTfLd);  // [64][64] 16-bit, swizzled: the solve operator
-  float* lg = reinterpret_cast<float*>(Gb + kC * kC * 2);       // [64] inclusive log decay
+  uint8_t* Gb = Qs;                                             // [64][64] 16-bit, swizzled: the solve operator (Q is dead by then)
+  float* lg = Tf + 4 * 16 * kTfLd;                              // [64] inclusive log decay
   float* bt = lg + kC;                                          // [64] beta
   float* kinv = bt + kC;                                        // [64]
   float* qinv = kinv + kC;                                      // [64]
@@ -210,6 +210,35 @@ scan_local_mma_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict
   }
   __syncthreads();
 
+  // ---- emit Qg and Kt; turn K into -beta g K and V into beta V in place (right-hand sides) -------------
+  {
+    const float lgC = lg[kC - 1];
+    uint4* qg_out = reinterpret_cast<uint4*>(rec + kRecQg);
+    uint4* kt_out = reinterpret_cast<uint4*>(rec + kRecKt);
+    for (int i = tid; i < kC * 16; i += 128) {
+      const int r = i >> 4, ch = i & 15;
+      const float eg = __expf(lg[r]);
+      const float sq = eg * qinv[r], sk = __expf(lgC - lg[r]) * kinv[r];
+      const float sbk = -bt[r] * eg * kinv[r], sbv = bt[r];
+      uint4 uq = *reinterpret_cast<const uint4*>(Qs + tile_off(r, ch * 8, kD));
+      uint4* pk = reinterpret_cast<uint4*>(Ks + tile_off(r, ch * 8, kD));
+      uint4* pv = reinterpret_cast<uint4*>(Vs + tile_off(r, ch * 8, kD));
+      uint4 uk = *pk, uv = *pv, oq, okt, obk, obv;
+      const uint32_t *wq = &uq.x, *wk = &uk.x, *wv = &uv.x;
+      uint32_t *xq = &oq.x, *xkt = &okt.x, *xbk = &obk.x, *xbv = &obv.x;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 fq = unpack2<kBf16>(wq[e]), fk = unpack2<kBf16>(wk[e]), fv = unpack2<kBf16>(wv[e]);
+        xq[e] = pack2<kBf16>(fq.x * sq, fq.y * sq);
+        xkt[e] = pack2<kBf16>(fk.x * sk, fk.y * sk);
+        xbk[e] = pack2<kBf16>(fk.x * sbk, fk.y * sbk);
+        xbv[e] = pack2<kBf16>(fv.x * sbv, fv.y * sbv);
+      }
+      qg_out[i] = oq; kt_out[i] = okt;
+      *pk = obk; *pv = obv;
+    }
+  }
+
   // ---- inverses of the four 16x16 diagonal blocks of I + A by substitution (fp32) ----------------------
   if (tid < 64) {
     const int blk = tid >> 4, j = tid & 15;
@@ -255,34 +284,6 @@ scan_local_mma_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict
     }
   }
 
-  // ---- emit Qg and Kt; turn K into -beta g K and V into beta V in place (right-hand sides) -------------
-  {
-    const float lgC = lg[kC - 1];
-    uint4* qg_out = reinterpret_cast<uint4*>(rec + kRecQg);
-    uint4* kt_out = reinterpret_cast<uint4*>(rec + kRecKt);
-    for (int i = tid; i < kC * 16; i += 128) {
-      const int r = i >> 4, ch = i & 15;
-      const float eg = __expf(lg[r]);
-      const float sq = eg * qinv[r], sk = __expf(lgC - lg[r]) * kinv[r];
-      const float sbk = -bt[r] * eg * kinv[r], sbv = bt[r];
-      uint4 uq = *reinterpret_cast<const uint4*>(Qs + tile_off(r, ch * 8, kD));
-      uint4* pk = reinterpret_cast<uint4*>(Ks + tile_off(r, ch * 8, kD));
-      uint4* pv = reinterpret_cast<uint4*>(Vs + tile_off(r, ch * 8, kD));
-      uint4 uk = *pk, uv = *pv, oq, okt, obk, obv;
-      const uint32_t *wq = &uq.x, *wk = &uk.x, *wv = &uv.x;
-      uint32_t *xq = &oq.x, *xkt = &okt.x, *xbk = &obk.x, *xbv = &obv.x;
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float2 fq = unpack2<kBf16>(wq[e]), fk = unpack2<kBf16>(wk[e]), fv = unpack2<kBf16>(wv[e]);
-        xq[e] = pack2<kBf16>(fq.x * sq, fq.y * sq);
-        xkt[e] = pack2<kBf16>(fk.x * sk, fk.y * sk);
-        xbk[e] = pack2<kBf16>(fk.x * sbk, fk.y * sbk);
-        xbv[e] = pack2<kBf16>(fv.x * sbv, fv.y * sbv);
-      }
-      qg_out[i] = oq; kt_out[i] = okt;
-      *pk = obk; *pv = obv;
-    }
-  }
   __syncthreads();
 
   // ---- blocked forward solve: -W (warps 0,1) and U0 (warps 2,3), 64 columns per warp.  A solved
@@ -561,7 +562,7 @@ int gated_delta_scan_mma_factors(const void* q, const void* k, const void* v, in
   const int NC = (T + kC - 1) / kC;
   uint8_t* recs = static_cast<uint8_t*>(scratch);
   float* gcs = gc_array(scratch, B, H, NC);
-  const int smemA = 3 * kC * kD * 2 + (kC * kAfLd + 4 * 16 * kTfLd) * 4 + kC * kC * 2 + (4 * kC + 4) * 4;
+  const int smemA = 3 * kC * kD * 2 + (kC * kAfLd + 4 * 16 * kTfLd) * 4 + (4 * kC + 4) * 4;   // 70.4 KB: three CTAs per SM
   if (dtype == ATMA_BF16) {
     ATMA_CUDA_OK(cudaFuncSetAttribute(scan_local_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smemA));
     scan_local_mma_kernel<true><<<dim3(NC, H, B), 128, smemA, st>>>((const uint16_t*)q, (const uint16_t*)k, (const uint16_t*)v, g,
@@ -624,7 +625,7 @@ int gated_delta_scan_mma_varlen(const void* q, const void* k, const void* v, int
   int32_t* cu_chunks = reinterpret_cast<int32_t*>(recs + gated_delta_scan_mma_scratch_bytes(1, NCu * kC, H));
   varlen_chunk_offsets_kernel<<<1, 32, 0, st>>>(cu_seqlens, cu_chunks, n_seqs);
   VarLen var{cu_seqlens, cu_chunks, n_seqs, slots, has_initial, state_table, slot_stride};
-  const int smemA = 3 * kC * kD * 2 + (kC * kAfLd + 4 * 16 * kTfLd) * 4 + kC * kC * 2 + (4 * kC + 4) * 4;
+  const int smemA = 3 * kC * kD * 2 + (kC * kAfLd + 4 * 16 * kTfLd) * 4 + (4 * kC + 4) * 4;   // 70.4 KB: three CTAs per SM
   const bool bf = dtype == ATMA_BF16;
   if (bf) {
     ATMA_CUDA_OK(cudaFuncSetAttribute(scan_local_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smemA));

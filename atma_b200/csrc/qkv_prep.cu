@@ -6,21 +6,21 @@
 // (inference/models/atma.py:396-399,431-441,468-471; kernel/inference_ops_triton.py:139-160;
 // inference/layers/attention.py:30-56).
 //
-// One CTA = one head (of q, k or v) x 256 tokens.  Sixteen threads cover a head row with eight
-// channels each (16-byte accesses); such a group streams 32 tokens (plus the K-1 rows before
-// them): eight packed rows per thread are always in flight, the last K normalised rows sit in
-// registers, the row sums of squares are reduced with shuffles, and every output is written once.
-// The kernel is bandwidth-bound: each projection element comes from DRAM once (a (K-1)/32 halo
-// aside) and q, k, v plus the K/V cache rows go out once.
+// Sixteen threads cover a head row with eight channels each (16-byte accesses); such a group holds
+// 8 tokens plus the K-1 rows before them in registers, reduces the row sums of squares with
+// shuffles and writes every output once.  The eight groups of a CTA take up to eight heads of the
+// SAME tokens, so that a CTA touches whole token rows (neighbouring DRAM pages) rather than one
+// 256-byte piece per 4 KB.  The kernel is bandwidth-bound: each projection element comes from DRAM
+// once (the K-1 halo rows of a tile are its neighbour's rows, i.e. cache hits) and q, k, v plus
+// the K/V cache rows go out once.
 #include "common.cuh"
 
 namespace atma {
 
 namespace {
 
-constexpr int kPrepTok = 32;       // tokens per 16-thread group
-constexpr int kPrepGroups = 8;     // groups per CTA: a CTA covers 256 tokens of one head
-constexpr int kPrepAhead = 8;      // rows each thread keeps in flight
+constexpr int kPrepTok = 8;        // tokens per 16-thread group
+constexpr int kPrepGroups = 8;     // groups per CTA
 constexpr int kPrepMaxK = 4;
 
 struct PrepArgs {
@@ -34,6 +34,7 @@ struct PrepArgs {
   void* q_out; void* k_out; void* v_out;             // dense [total][heads][dk]
   void* k_cache; void* v_cache; const int64_t* slot_mapping;   // cache rows [slot][Hkv][dk]; may be null
   int total, H, Hkv, dk, K;
+  int nq, upc_q, upc_kv;                             // q-head chunks in grid.y; heads per chunk (1, 2, 4 or 8) for q and for k|v
   float eps;
 };
 
@@ -75,61 +76,45 @@ template <> __device__ __forceinline__ void store8<__half>(__half* p, const floa
   *reinterpret_cast<uint4*>(p) = u;
 }
 
-// a row fragment as it comes from memory (kept packed while it waits in the prefetch ring)
-template <typename T> struct RawRow { uint4 u; };
-template <> struct RawRow<float> { float4 lo, hi; };
-template <typename T> __device__ __forceinline__ void raw_load(RawRow<T>& r, const T* p) { r.u = *reinterpret_cast<const uint4*>(p); }
-template <> __device__ __forceinline__ void raw_load<float>(RawRow<float>& r, const float* p) {
-  r.lo = *reinterpret_cast<const float4*>(p); r.hi = *reinterpret_cast<const float4*>(p + 4);
-}
-template <typename T> __device__ __forceinline__ void raw_zero(RawRow<T>& r) { r.u = make_uint4(0u, 0u, 0u, 0u); }
-template <> __device__ __forceinline__ void raw_zero<float>(RawRow<float>& r) {
-  r.lo = make_float4(0.f, 0.f, 0.f, 0.f); r.hi = r.lo;
-}
-template <typename T> __device__ __forceinline__ void raw_unpack(const RawRow<T>& r, float (&o)[8]) {
-  load8<T>(reinterpret_cast<const T*>(&r.u), o);
-}
-template <> __device__ __forceinline__ void raw_unpack<float>(const RawRow<float>& r, float (&o)[8]) {
-  o[0] = r.lo.x; o[1] = r.lo.y; o[2] = r.lo.z; o[3] = r.lo.w; o[4] = r.hi.x; o[5] = r.hi.y; o[6] = r.hi.z; o[7] = r.hi.w;
-}
-
 template <typename T, int K>
 __global__ void __launch_bounds__(128, 3)
 qkv_prep_kernel(const PrepArgs a) {
-  constexpr int kCtaTok = kPrepTok * kPrepGroups;
+  constexpr int kCtaTok = kPrepTok * kPrepGroups;                // at most this many tokens per CTA
   __shared__ int s_s0[kCtaTok], s_e0[kCtaTok], s_slot[kCtaTok];
   __shared__ long long s_cs[kCtaTok];
   const int grp = threadIdx.x >> 4, li = threadIdx.x & 15;      // 16 threads x 8 channels cover one head row
-  const int t0 = (blockIdx.x * kPrepGroups + grp) * kPrepTok;   // this group's first token
-  for (int i = threadIdx.x; i < kCtaTok; i += 128) {             // the per-token maps of the CTA's tokens
-    const int t = blockIdx.x * kCtaTok + i;
+  // blockIdx.y < nq: a chunk of q heads; else a chunk of the 2*Hkv k and v heads.  The `upc` heads of a
+  // chunk sit side by side in the CTA (their rows of one token are neighbours in memory); with fewer
+  // than 8 heads per chunk the other groups take further 8-token tiles.
+  const bool is_q = (int)blockIdx.y < a.nq;
+  const int chunk = is_q ? blockIdx.y : blockIdx.y - a.nq;
+  const int n_units = is_q ? a.H : 2 * a.Hkv;
+  const int upc = is_q ? a.upc_q : a.upc_kv, tpc = kPrepGroups / upc;
+  const int unit = chunk * upc + grp % upc;
+  const int cta_t0 = blockIdx.x * tpc * kPrepTok;
+  const int t0 = cta_t0 + (grp / upc) * kPrepTok;
+  if (threadIdx.x < tpc * kPrepTok) {                            // the per-token maps of the CTA's tokens
+    const int t = cta_t0 + threadIdx.x;
     const bool ok = t < a.total;
-    s_s0[i] = ok ? a.seq_start[t] : 0;
-    s_e0[i] = ok ? a.seq_end[t] : 0;
-    s_slot[i] = ok ? a.seq_slot[t] : -1;
-    s_cs[i] = (ok && a.slot_mapping != nullptr) ? a.slot_mapping[t] : -1;
+    s_s0[threadIdx.x] = ok ? a.seq_start[t] : 0;
+    s_e0[threadIdx.x] = ok ? a.seq_end[t] : 0;
+    s_slot[threadIdx.x] = ok ? a.seq_slot[t] : -1;
+    s_cs[threadIdx.x] = (ok && a.slot_mapping != nullptr) ? a.slot_mapping[t] : -1;
   }
-  const int unit = blockIdx.y;                                   // [0,H): q heads, [H,H+Hkv): k heads, then v heads
-  const int which = unit < a.H ? 0 : (unit < a.H + a.Hkv ? 1 : 2);
-  const int head = which == 0 ? unit : (which == 1 ? unit - a.H : unit - a.H - a.Hkv);
-  const int heads = which == 0 ? a.H : a.Hkv;
+  const int which = is_q ? 0 : (unit < a.Hkv ? 1 : 2);
+  const int head = is_q ? unit : (unit < a.Hkv ? unit : unit - a.Hkv);
+  const int heads = is_q ? a.H : a.Hkv;
   const int c = li * 8;
-  const bool active = c < a.dk;
+  const bool active = c < a.dk && unit < n_units && t0 < a.total;
   const bool normalize = which != 2;
 
   const T* src; int64_t row_st;
   if (which == 0) { src = (const T*)a.qg + (int64_t)head * a.qg_head; row_st = a.qg_row; }
   else if (which == 1) { src = (const T*)a.k + (int64_t)head * a.dk; row_st = a.k_row; }
   else { src = (const T*)a.v + (int64_t)head * a.dk; row_st = a.v_row; }
-  src += c;
-  T* dst = (T*)(which == 0 ? a.q_out : (which == 1 ? a.k_out : a.v_out)) + (int64_t)head * a.dk + c;
+  T* dst = (T*)(which == 0 ? a.q_out : (which == 1 ? a.k_out : a.v_out)) + (int64_t)head * a.dk;
   const int64_t dst_row = (int64_t)heads * a.dk;
   const int ch = head * a.dk + c;                                // first of this thread's conv channels
-  T* cache = (T*)(which == 1 ? a.k_cache : a.v_cache);
-  T* state = (T*)a.state[which];
-  const T* init = (const T*)a.init[which];
-  const int64_t state_ss = a.state_ss[which];
-  const float inv_dk = 1.0f / (float)a.dk;
 
   float wt[8][K];
 #pragma unroll
@@ -138,44 +123,50 @@ qkv_prep_kernel(const PrepArgs a) {
     for (int kk = 0; kk < K; ++kk)
       wt[j][kk] = active ? to_f32(((const T*)a.w[which])[(int64_t)(ch + j) * K + kk]) : 0.f;
 
-  // ---- stream the rows t0-(K-1) .. t0+kPrepTok-1: a ring of kPrepAhead packed rows in flight, a
-  //      window of the last K normalised rows in registers ----------------------------------------------
-  RawRow<T> ring[kPrepAhead];
-  auto fetch = [&](RawRow<T>& r, int row) {                      // row index relative to t0-(K-1)
-    const int t = t0 - (K - 1) + row;
-    if (active && t >= 0 && t < a.total && row < kPrepTok + K - 1) raw_load<T>(r, src + (int64_t)t * row_st);
-    else raw_zero<T>(r);
-  };
-#pragma unroll
-  for (int i = 0; i < kPrepAhead; ++i) fetch(ring[i], i);
-  __syncthreads();                                               // the token maps are in shared memory
-
-  float win[K][8];
+  // ---- rows t0-(K-1) .. t0+kPrepTok-1, normalised ------------------------------------------------------
+  float x[kPrepTok + K - 1][8];
 #pragma unroll
   for (int i = 0; i < kPrepTok + K - 1; ++i) {
-    float (&x)[8] = win[i % K];
-    raw_unpack<T>(ring[i % kPrepAhead], x);
-    fetch(ring[i % kPrepAhead], i + kPrepAhead);
-    if (normalize) {
+    const int t = t0 - (K - 1) + i;
+    if (active && t >= 0 && t < a.total) load8<T>(src + (int64_t)t * row_st + c, x[i]);
+    else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[i][j] = 0.f;
+    }
+  }
+  if (normalize) {
+    const float inv_dk = 1.0f / (float)a.dk;
+#pragma unroll
+    for (int i = 0; i < kPrepTok + K - 1; ++i) {
       float ss = 0.f;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) ss = fmaf(x[j], x[j], ss);
+      for (int j = 0; j < 8; ++j) ss = fmaf(x[i][j], x[i][j], ss);
 #pragma unroll
       for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);     // the 16 threads of the row
       const float r = rsqrtf(ss * inv_dk + a.eps);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) x[j] = round_through<T>(x[j] * r);                 // the eager op rounds to T here
+      for (int j = 0; j < 8; ++j) x[i][j] = round_through<T>(x[i][j] * r);           // the eager op rounds to T here
     }
-    if (i < K - 1) continue;                                     // still filling the window
-    const int ti = grp * kPrepTok + (i - (K - 1));
-    const int t = t0 + (i - (K - 1));
-    if (!active || t >= a.total) continue;
+  }
+  __syncthreads();                                               // the token maps are in shared memory
+  if (!active) return;
+
+  T* state = (T*)a.state[which];
+  const T* init = (const T*)a.init[which];
+  const int64_t state_ss = a.state_ss[which];
+  T* cache = (T*)(which == 1 ? a.k_cache : a.v_cache);
+
+#pragma unroll
+  for (int i = 0; i < kPrepTok; ++i) {
+    const int t = t0 + i;
+    if (t >= a.total) break;
+    const int ti = t - cta_t0;
     const int s0 = s_s0[ti], e0 = s_e0[ti], slot = s_slot[ti];
     const bool from_state = init != nullptr && slot >= 0;
     // channel j's input `back` rows before token t as this sequence sees it: its own rows, else
     // its saved state, else 0
     auto tap = [&](int back, int j) -> float {
-      if (t - back >= s0) return win[(i - back) % K][j];
+      if (t - back >= s0) return x[i + (K - 1) - back][j];
       if (from_state) return to_f32(init[slot * state_ss + (int64_t)(ch + j) * (K - 1) + (K - 1) - (s0 - (t - back))]);
       return 0.f;
     };
@@ -185,8 +176,8 @@ qkv_prep_kernel(const PrepArgs a) {
       for (int j = 0; j < 8; ++j) {
         float acc = 0.f;
 #pragma unroll
-        for (int kk = 0; kk < K; ++kk) acc = fmaf(win[(i - (K - 1) + kk) % K][j], wt[j][kk], acc);
-        y[j] = x[j] + round_through<T>(acc);                     // x + conv(x), the conv rounded as eager does
+        for (int kk = 0; kk < K; ++kk) acc = fmaf(x[i + kk][j], wt[j][kk], acc);
+        y[j] = x[i + K - 1][j] + round_through<T>(acc);          // x + conv(x), the conv rounded as eager does
       }
     } else {
 #pragma unroll
@@ -194,10 +185,10 @@ qkv_prep_kernel(const PrepArgs a) {
         float acc = 0.f;
 #pragma unroll
         for (int kk = 0; kk < K; ++kk) acc = fmaf(tap(K - 1 - kk, j), wt[j][kk], acc);
-        y[j] = x[j] + round_through<T>(acc);
+        y[j] = x[i + K - 1][j] + round_through<T>(acc);
       }
     }
-    store8<T>(dst + (int64_t)t * dst_row, y);
+    store8<T>(dst + (int64_t)t * dst_row + c, y);
     if (which != 0) {
       const int64_t cs = s_cs[ti];
       if (cs >= 0) store8<T>(cache + (cs * a.Hkv + head) * a.dk + c, y);
@@ -218,8 +209,10 @@ qkv_prep_kernel(const PrepArgs a) {
 
 template <typename T>
 int launch_prep(const PrepArgs& a, cudaStream_t st) {
-  const int per_cta = kPrepTok * kPrepGroups;
-  dim3 grid((a.total + per_cta - 1) / per_cta, a.H + 2 * a.Hkv), block(128);
+  const int tok_q = kPrepGroups / a.upc_q * kPrepTok, tok_kv = kPrepGroups / a.upc_kv * kPrepTok;
+  const int nx = ((a.total + tok_q - 1) / tok_q > (a.total + tok_kv - 1) / tok_kv) ? (a.total + tok_q - 1) / tok_q
+                                                                                     : (a.total + tok_kv - 1) / tok_kv;
+  dim3 grid(nx, a.nq + (2 * a.Hkv + a.upc_kv - 1) / a.upc_kv), block(128);
   switch (a.K) {
     case 2: qkv_prep_kernel<T, 2><<<grid, block, 0, st>>>(a); break;
     case 3: qkv_prep_kernel<T, 3><<<grid, block, 0, st>>>(a); break;
@@ -269,6 +262,10 @@ extern "C" int atma_qkv_prep_prefill(const void* q_gate, int64_t qg_row_stride, 
   a.q_out = q_out; a.k_out = k_out; a.v_out = v_out;
   a.k_cache = k_cache; a.v_cache = v_cache; a.slot_mapping = k_cache ? slot_mapping : nullptr;
   a.total = total; a.H = H; a.Hkv = Hkv; a.dk = dk; a.K = K; a.eps = eps;
+  auto pow2_at_most_8 = [](int n) { int p = 1; while (p < n && p < 8) p <<= 1; return p; };
+  a.upc_q = pow2_at_most_8(H);
+  a.upc_kv = pow2_at_most_8(2 * Hkv);
+  a.nq = (H + a.upc_q - 1) / a.upc_q;
   int rc = ATMA_OK;
   ATMA_DISPATCH_DTYPE(dtype, T, { rc = launch_prep<T>(a, (cudaStream_t)stream); });
   return rc;
