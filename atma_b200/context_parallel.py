@@ -428,3 +428,78 @@ class CapturedPrefill:
             self.graph.replay()
             return self.outputs
         return cp_global_layer_prefill(self.static, self.params, group=self.group, polar_mode=self.polar_mode)
+
+
+class HostFedCapturedPrefill:
+    """Context-parallel steps fed from pinned host memory: ``depth`` captured steps with their own
+    input buffers on a three-stream pipeline (copy-in | graph replay | copy-out), so that the PCIe
+    copies of neighbouring steps hide behind the replay.  Every rank must construct it, call
+    ``submit`` the same number of times and ``close`` it before the process group goes away.
+
+    ``submit(host_shard)`` takes a ``GlobalLayerShard`` of pinned tensors and returns a ticket;
+    ``results(ticket)`` waits for that step's copies and returns the pinned outputs
+    [c_lo, mag_lo, c_hi, mag_hi, o_lo, o_hi, S] (reused ``depth`` submits later)."""
+
+    FIELDS = ("q", "k", "v", "g", "beta")
+
+    def __init__(self, shard, params, *, group=None, polar_mode=None, depth=2):
+        dev = shard.q[0].device
+        self.device, self.depth = dev, depth
+        self.caps = [CapturedPrefill(shard, params, group=group, polar_mode=polar_mode) for _ in range(depth)]
+        self.copy_in, self.compute, self.copy_out = (torch.cuda.Stream(device=dev) for _ in range(3))
+        self.in_free = [None] * depth
+        self.out_done = [None] * depth
+        self.out_host = [None] * depth
+        self.step = 0
+
+    @staticmethod
+    def _flat(outputs):
+        polar, o, S = outputs
+        return [polar[0][0], polar[0][1], polar[1][0], polar[1][1], o[0], o[1], S]
+
+    def submit(self, host_shard):
+        slot = self.step % self.depth
+        self.step += 1
+        cap = self.caps[slot]
+        with torch.cuda.stream(self.copy_in):
+            if self.in_free[slot] is not None:
+                self.copy_in.wait_event(self.in_free[slot])
+            for f in self.FIELDS:
+                for dst, src in zip(getattr(cap.static, f), getattr(host_shard, f)):
+                    dst.copy_(src, non_blocking=True)
+            arrived = torch.cuda.Event()
+            arrived.record(self.copy_in)
+        with torch.cuda.stream(self.compute):
+            self.compute.wait_event(arrived)
+            if self.out_done[slot] is not None:                 # the step's output buffers were read out
+                self.compute.wait_event(self.out_done[slot])
+            outs = self._flat(cap.replay())
+            computed = torch.cuda.Event()
+            computed.record(self.compute)
+        self.in_free[slot] = computed
+        if self.out_host[slot] is None:
+            self.out_host[slot] = [torch.empty(x.shape, dtype=x.dtype, pin_memory=True) for x in outs]
+        with torch.cuda.stream(self.copy_out):
+            self.copy_out.wait_event(computed)
+            for h, d in zip(self.out_host[slot], outs):
+                h.copy_(d, non_blocking=True)
+            done = torch.cuda.Event()
+            done.record(self.copy_out)
+        self.out_done[slot] = done
+        return self.step - 1
+
+    def results(self, ticket):
+        if ticket < self.step - self.depth or ticket >= self.step:
+            raise ValueError("that step's result slot has been reused (or the step was never submitted)")
+        self.out_done[ticket % self.depth].synchronize()
+        return self.out_host[ticket % self.depth]
+
+    def drain(self, stream=None):
+        stream = stream or torch.cuda.current_stream(self.device)
+        for s in (self.copy_in, self.compute, self.copy_out):
+            stream.wait_stream(s)
+
+    def close(self):
+        torch.cuda.synchronize(self.device)
+        for cap in self.caps:
+            cap.close()

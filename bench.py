@@ -433,30 +433,51 @@ def run_context_parallel(args, ab, rank, local_rank, world, device, peaks):
     clocks = sampler.stop()
     ms = e0.elapsed_time(e1) / args.steps
 
-    # (3) end to end: pinned host shard -> the step's input buffers, step, all results -> pinned host
-    out_host = None
+    # (3) end to end: every step copies its pinned host shard in and all results back out.  With the graph:
+    #     two captured steps on a three-stream pipeline (copy-in | replay | copy-out); without: one stream.
+    host_shard = cp.GlobalLayerShard(positions=sh.positions, **{f: host[f] for f in fields})
+    if graph_used:
+        pipe = cp.HostFedCapturedPrefill(dev_shard, params)
+        for _ in range(3):
+            pipe.submit(host_shard)
+        pipe.drain()
+        barrier()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for s_ in (pipe.copy_in, pipe.compute, pipe.copy_out):
+            s_.wait_event(s0)
+        for _ in range(args.steps):
+            ticket = pipe.submit(host_shard)
+        pipe.drain()
+        s1.record()
+        barrier()
+        out_host = pipe.results(ticket)
+        e2e_api = "atma_b200.context_parallel.HostFedCapturedPrefill.submit"
+    else:
+        out_host = None
 
-    def e2e_step():
-        nonlocal out_host
-        for f in fields:
-            for dst, src in zip(getattr(static, f), host[f]):
+        def e2e_step():
+            nonlocal out_host
+            for f in fields:
+                for dst, src in zip(getattr(static, f), host[f]):
+                    dst.copy_(src, non_blocking=True)
+            polar, o, S = run_step()
+            outs = [polar[0][0], polar[0][1], polar[1][0], polar[1][1], o[0], o[1], S]
+            if out_host is None:
+                out_host = [torch.empty(x.shape, dtype=x.dtype, pin_memory=True) for x in outs]
+            for dst, src in zip(out_host, outs):
                 dst.copy_(src, non_blocking=True)
-        polar, o, S = run_step()
-        outs = [polar[0][0], polar[0][1], polar[1][0], polar[1][1], o[0], o[1], S]
-        if out_host is None:
-            out_host = [torch.empty(x.shape, dtype=x.dtype, pin_memory=True) for x in outs]
-        for dst, src in zip(out_host, outs):
-            dst.copy_(src, non_blocking=True)
 
-    for _ in range(2):
-        e2e_step()
-    barrier()
-    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    s0.record()
-    for _ in range(args.steps):
-        e2e_step()
-    s1.record()
-    barrier()
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for _ in range(args.steps):
+            e2e_step()
+        s1.record()
+        barrier()
+        e2e_api = "atma_b200.context_parallel.cp_global_layer_prefill"
     e2e_ms = s0.elapsed_time(s1) / args.steps
     h2d = sum(x.numel() * x.element_size() for f in fields for x in host[f])
     d2h = sum(x.numel() * x.element_size() for x in out_host)
@@ -467,6 +488,9 @@ def run_context_parallel(args, ab, rank, local_rank, world, device, peaks):
     dist.all_reduce(bytes_t)
     h2d, d2h = bytes_t.tolist()
     del dev_shard, static, run_step
+    if graph_used:
+        pipe.close()
+        del pipe
     if not args.no_graph:
         cap.close()
         del cap
@@ -486,7 +510,7 @@ def run_context_parallel(args, ab, rank, local_rank, world, device, peaks):
                                "query segment, gated-delta state handed over as an affine-map prefix)",
                    "tokens": T_PREFILL, "heads": H, "kv_heads": HKV, "head_dim": DK, "chunk": CHUNK, "window": None,
                    "l2": "per-GPU inputs shrink with N; at N=8 they are 34 MB, below L2", "polar_kernel": "tcgen05"},
-        "e2e": {"value": T_PREFILL / (e2e_ms * 1e-3), "unit": "tok/s", "ms_per_step": e2e_ms,
+        "e2e": {"value": T_PREFILL / (e2e_ms * 1e-3), "unit": "tok/s", "ms_per_step": e2e_ms, "api": e2e_api,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         # per rank and step: 2 Polar launches (one per query segment), the chunk-factor kernel and
         # 2 recurrence launches of this library; NCCL and torch's small copy kernels are not counted

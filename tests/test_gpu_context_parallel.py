@@ -67,6 +67,19 @@ def _worker(rank, world, port, ret):
         cap.close()
         torch.cuda.synchronize()
         ret[f"stage{rank}"] = "graph released"
+        # the host-fed pipeline: three steps from pinned host memory through two captured steps
+        host_shard = cp.GlobalLayerShard(positions=shard.positions,
+                                         **{f: [x.cpu().pin_memory() for x in getattr(shard, f)] for f in ("q", "k", "v", "g", "beta")})
+        pipe = cp.HostFedCapturedPrefill(shard, pg, polar_mode="gather")
+        want = [polar[0][0], polar[0][1], polar[1][0], polar[1][1], o[0], o[1], S]
+        fed = True
+        for step in range(3):
+            ticket = pipe.submit(host_shard)
+            got = pipe.results(ticket)
+            fed = fed and all(torch.equal(a, b.cpu()) for a, b in zip(got, want))
+        ret[f"fed{rank}"] = bool(fed)
+        pipe.close()
+        ret[f"stage{rank}"] = "pipeline released"
     finally:
         dist.destroy_process_group()
 
@@ -104,3 +117,4 @@ def test_two_rank_context_parallel_matches_one_gpu():
             assert rel(ret[f"gather{rank}"]["mag"][part], m_ref[:, :, a:b]) < 2e-2
         assert rel(r["S"], S_ref[0]) < 2e-2
         assert ret[f"graph{rank}"], "graph replay differs from the launch-by-launch step (or capture failed)"
+        assert ret[f"fed{rank}"], "the host-fed pipeline differs from the launch-by-launch step"
