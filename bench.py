@@ -62,13 +62,17 @@ def scan_flops(T):
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons, sampled while the timed region runs."""
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    """nvidia-smi clocks and throttle reasons, sampled every 20 ms.  The sampler is started before the
+    warm-up steps (nvidia-smi needs a moment to come up) and the samples are then cut to the timed
+    region by their timestamps; if the timed region was too short to catch one, the samples of the
+    warm-up steps (the same load, directly before) are used and ``window`` says so."""
+    Q = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index):
         self.gpu, self.proc, self.path = gpu_index, None, None
+        self.t_begin = self.t_end = None
 
     def start(self):
         try:
@@ -80,31 +84,45 @@ class ClockSampler:
         except Exception:
             self.proc = None
 
+    def mark_begin(self):
+        self.t_begin = time.time()
+
+    def mark_end(self):
+        self.t_end = time.time()
+
     def stop(self):
+        import datetime
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         if self.proc is None:
             return out
+        if self.t_end is None:
+            self.t_end = time.time()
+        time.sleep(0.05)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
+        rows = []
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in open(self.path):
             f = [x.strip() for x in line.split(",")]
             if len(f) < 9:
                 continue
             try:
-                sm.append(float(f[1])); mx.append(float(f[2]))
+                ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                rows.append((ts, float(f[1]), float(f[2]), [n for n, val in zip(names, f[5:9]) if val.lower().startswith("active")]))
             except ValueError:
                 continue
-            for n, val in zip(names, f[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(n)
         os.unlink(self.path)
-        if sm:
-            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        inside = [r for r in rows if self.t_begin is not None and self.t_begin - 0.01 <= r[0] <= self.t_end + 0.03]
+        window = "timed region"
+        if not inside:
+            inside = [r for r in rows if r[0] <= self.t_end + 0.03][-10:]
+            window = "warm-up steps directly before the timed region (it was shorter than the sampling period)"
+        if inside:
+            out.update(sm_mhz=statistics.median(r[1] for r in inside), sm_max_mhz=max(r[2] for r in inside),
+                       reasons=sorted({n for r in inside for n in r[3]}), samples=len(inside), window=window)
         return out
 
 
@@ -419,17 +437,19 @@ def run_context_parallel(args, ab, rank, local_rank, world, device, peaks):
         run_step, static, graph_used = cap.replay, cap.static, cap.captured
         if not cap.captured and rank == 0:
             print(f"[bench] graph capture failed, running eagerly: {getattr(cap, 'error', None)!r}", file=sys.stderr)
-    for _ in range(args.warmup):
-        run_step()
     sampler = ClockSampler(local_rank)
-    barrier()
     sampler.start()
+    for _ in range(max(args.warmup, 50)):                       # also gives the clock sampler time to come up
+        run_step()
+    barrier()
+    sampler.mark_begin()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(args.steps):
         run_step()
     e1.record()
     barrier()
+    sampler.mark_end()
     clocks = sampler.stop()
     ms = e0.elapsed_time(e1) / args.steps
 
@@ -599,11 +619,12 @@ def main():
         torch.cuda.synchronize()
 
     # ---- kernel-resident timing ("value") -------------------------------------------------------
-    for _ in range(args.warmup):
-        prefill_step(ab, dev_in, n_keys, params)
     sampler = ClockSampler(local_rank)
-    barrier()
     sampler.start()
+    for _ in range(max(args.warmup, 10)):                       # also gives the clock sampler time to come up
+        prefill_step(ab, dev_in, n_keys, params)
+    barrier()
+    sampler.mark_begin()
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -611,6 +632,7 @@ def main():
         prefill_step(ab, dev_in, n_keys, params, ev[i])
     e1.record()
     barrier()
+    sampler.mark_end()
     clocks = sampler.stop()
     ms = e0.elapsed_time(e1) / args.steps
     polar_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / args.steps
