@@ -150,3 +150,45 @@ def test_elementwise_bit_exact(golden):
     torch.testing.assert_close(capped, g["capped"])
     assert (capped != g["capped"]).float().mean() < 2e-3
     assert max_abs(oracle.softcap_logits_oracle(g["logits32"]), g["capped32"]) < 2e-6
+
+
+def test_qkv_prep_oracle_against_conv1d_per_sequence():
+    """The op-by-op restatement of the packed q/k/v preparation (rms_norm, x + conv(x), state rows,
+    cache scatter) against torch's own conv1d run sequence by sequence - an independent statement of
+    inference/models/atma.py:396-399,431-441,468-471."""
+    import torch.nn.functional as F
+    import oracle
+    g = torch.Generator().manual_seed(4)
+    H, Hkv, dk, K = 2, 1, 16, 4
+    lens, slots = [5, 2, 9], [1, -1, 0]
+    total = sum(lens)
+    qg = torch.randn(total, H, 2 * dk, generator=g)
+    k = torch.randn(total, Hkv, dk, generator=g)
+    v = torch.randn(total, Hkv, dk, generator=g)
+    w = [torch.randn(C, K, generator=g) for C in (H * dk, Hkv * dk, Hkv * dk)]
+    st = [torch.zeros(3, C, K - 1) for C in (H * dk, Hkv * dk, Hkv * dk)]
+    s0, e0, sl, pos = [], [], [], 0
+    for n, s in zip(lens, slots):
+        s0 += [pos] * n; e0 += [pos + n] * n; sl += [s] * n
+        pos += n
+    kc, vc = torch.zeros(total + 2, Hkv, dk), torch.zeros(total + 2, Hkv, dk)
+    sm = torch.randperm(total + 2, generator=g)[:total]
+    sm[4] = -1
+    q_o, k_o, v_o = oracle.qkv_prep_prefill_oracle(qg, k, v, *w, *st, torch.tensor(s0), torch.tensor(e0), torch.tensor(sl), kc, vc, sm)
+    xs = [F.rms_norm(qg[..., :dk], (dk,)).reshape(total, -1), F.rms_norm(k, (dk,)).reshape(total, -1), v.reshape(total, -1)]
+    pos = 0
+    for n, slot in zip(lens, slots):
+        for x, wi, got, table in zip(xs, w, (q_o, k_o, v_o), st):
+            seg = x[pos:pos + n].t()[None]                                        # (1, C, n)
+            conv = F.conv1d(F.pad(seg, (K - 1, 0)), wi[:, None, :], groups=wi.shape[0])[0].t()
+            torch.testing.assert_close(got[pos:pos + n].reshape(n, -1), x[pos:pos + n] + conv, atol=1e-5, rtol=1e-5)
+            if slot >= 0:
+                want = F.pad(seg, (K - 1, 0))[0][:, -(K - 1):]
+                torch.testing.assert_close(table[slot], want)
+        pos += n
+    assert torch.equal(st[0][2], torch.zeros_like(st[0][2]))                      # no sequence owns row 2
+    for t in range(total):
+        if sm[t] >= 0:
+            assert torch.equal(kc[sm[t]], k_o[t]) and torch.equal(vc[sm[t]], v_o[t])
+    unused = [i for i in range(total + 2) if i not in sm.tolist()]
+    assert torch.equal(kc[unused], torch.zeros(len(unused), Hkv, dk))
