@@ -275,6 +275,7 @@ extern "C" int atma_gated_delta_scan_varlen(const void* q, const void* k, const 
                "gated_delta_scan_varlen: needs 16-bit inputs with dk = dv = 128 (got dtype %d, dk %d, dv %d)", dtype, dk, dv);
   ATMA_REQUIRE(n_seqs >= 0 && total_tokens >= 0 && H > 0 && Hkv > 0 && H % Hkv == 0, "gated_delta_scan_varlen: bad shape");
   ATMA_REQUIRE(total_tokens / kScanC + n_seqs < (1 << 30), "gated_delta_scan_varlen: too many chunks");
+  ATMA_REQUIRE(n_seqs <= 65535, "gated_delta_scan_varlen: at most 65535 sequences per call (got %d)", n_seqs);
   if (n_seqs == 0) return ATMA_OK;
   ATMA_REQUIRE(cu_seqlens != nullptr, "gated_delta_scan_varlen: cu_seqlens is required");
   ATMA_REQUIRE(state_table == nullptr || slots != nullptr, "gated_delta_scan_varlen: a state table needs slots");

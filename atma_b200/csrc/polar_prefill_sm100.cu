@@ -57,11 +57,6 @@ struct Params {
 };
 
 __device__ int g_sm100_status = 0;
-#ifdef ATMA_SM100_DEBUG
-__device__ float g_dbg_s[2][128][128];      // raw S of the first key tile, CTA (0,0,0)
-__device__ float g_dbg_o[2][128][128];      // final O
-__device__ float g_dbg_st[2][128][8];
-#endif
 
 struct Barriers {
   uint64_t q_full[2];
@@ -369,10 +364,6 @@ polar_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
       tmem_ld_wait();
 #pragma unroll
       for (int i = 0; i < kBN; ++i) reg_fence(r[i]);
-#ifdef ATMA_SM100_DEBUG
-      if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && j == my_lo)
-        for (int i = 0; i < kBN; ++i) g_dbg_s[t][r_in_tile][i] = __uint_as_float(r[i]);
-#endif
       if (!full) {                                                  // diagonal / window-edge / ragged tile
 #pragma unroll
         for (int i = 0; i < kBN; ++i) {
@@ -472,21 +463,11 @@ polar_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
         const float p_n = ex2(a_n - m_fin);
         const float Z = Lf + p_n;
         const float* vn = p.v_null + h * kDK;
-#ifdef ATMA_SM100_DEBUG
-        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
-          float* d = g_dbg_st[t][r_in_tile];
-          d[0] = m_used; d[1] = L; d[2] = Q2; d[3] = sc2; d[4] = (float)h; d[5] = alpha; d[6] = (float)my_row + (row_ok ? 0.5f : 0.f); d[7] = (float)(b * p.c_sb + h * p.c_sh + (int64_t)(seq_row0 + my_row) * p.c_st);
-        }
-#endif
         float sq = 0.f;
 #pragma unroll 1
         for (int ch = 0; ch < 4; ++ch) {
           uint32_t r[32];
           if (have_o) tmem_ld32(tO + ch * 32, r);
-#ifdef ATMA_SM100_DEBUG
-          if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0)
-            for (int i = 0; i < 32; ++i) g_dbg_o[t][r_in_tile][ch * 32 + i] = have_o ? __uint_as_float(r[i]) : -777.f;
-#endif
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const float s = (have_o ? __uint_as_float(r[i]) * alpha : 0.f) + p_n * vn[ch * 32 + i];
@@ -617,19 +598,6 @@ int sm100_status_fetch_and_clear(int* out) {
 
 }  // namespace atma
 
-#ifdef ATMA_SM100_DEBUG
-extern "C" int atma_debug_fetch(float* s_out, float* o_out) {
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(s_out, atma::g_dbg_s, sizeof(float) * 2 * 128 * 128);
-  cudaMemcpyFromSymbol(o_out, atma::g_dbg_o, sizeof(float) * 2 * 128 * 128);
-  return 0;
-}
-extern "C" int atma_debug_fetch_stats(float* st_out) {
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(st_out, atma::g_dbg_st, sizeof(float) * 2 * 128 * 8);
-  return 0;
-}
-#endif
 
 // Non-zero if a tensor-core kernel gave up on a bounded wait since the last call (synchronises
 // the device; clears the flag).
