@@ -6,21 +6,23 @@
 // (inference/models/atma.py:396-399,431-441,468-471; kernel/inference_ops_triton.py:139-160;
 // inference/layers/attention.py:30-56).
 //
-// Sixteen threads cover a head row with eight channels each (16-byte accesses); such a group holds
-// 8 tokens plus the K-1 rows before them in registers, reduces the row sums of squares with
-// shuffles and writes every output once.  The eight groups of a CTA take up to eight heads of the
-// SAME tokens, so that a CTA touches whole token rows (neighbouring DRAM pages) rather than one
-// 256-byte piece per 4 KB.  The kernel is bandwidth-bound: each projection element comes from DRAM
-// once (the K-1 halo rows of a tile are its neighbour's rows, i.e. cache hits) and q, k, v plus
-// the K/V cache rows go out once.
+// One CTA = 32 tokens x up to eight heads (of q, or of k and v).  The tile, plus the K-1 rows
+// before it, is staged in shared memory with 16-byte asynchronous copies (whole token rows, so
+// neighbouring DRAM pages).  A group of 16 threads x 8 channels then walks a run of consecutive
+// tokens of one head: each row is read from the tile once, normalised in registers (row sums by
+// shuffles), kept in a K-row register window for the taps, and q, k, v and the cache rows are written once.  Three
+// CTAs per SM keep ~200 KB of copies in flight, so the kernel is bandwidth-bound: each projection
+// element comes from DRAM once (the K-1 halo rows of a tile are its neighbour's rows, i.e. cache
+// hits) and every output goes out once.
 #include "common.cuh"
 
 namespace atma {
 
 namespace {
 
-constexpr int kPrepTok = 8;        // tokens per 16-thread group
-constexpr int kPrepGroups = 8;     // groups per CTA
+constexpr int kPrepTok = 32;       // tokens per CTA
+constexpr int kPrepHeads = 8;      // heads per CTA (the rows of one token are neighbours in memory)
+constexpr int kPrepThreads = 256;
 constexpr int kPrepMaxK = 4;
 
 struct PrepArgs {
@@ -34,7 +36,7 @@ struct PrepArgs {
   void* q_out; void* k_out; void* v_out;             // dense [total][heads][dk]
   void* k_cache; void* v_cache; const int64_t* slot_mapping;   // cache rows [slot][Hkv][dk]; may be null
   int total, H, Hkv, dk, K;
-  int nq, upc_q, upc_kv;                             // q-head chunks in grid.y; heads per chunk (1, 2, 4 or 8) for q and for k|v
+  int nq;                                            // q-head chunks in grid.y (the k|v chunks follow)
   float eps;
 };
 
@@ -76,97 +78,134 @@ template <> __device__ __forceinline__ void store8<__half>(__half* p, const floa
   *reinterpret_cast<uint4*>(p) = u;
 }
 
+// 16-byte asynchronous copy global -> shared; src_bytes = 0 zero-fills the destination
+__device__ __forceinline__ void prep_cp_async16(void* smem_dst, const void* gsrc, bool valid) {
+  const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+  const int n = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gsrc), "r"(n) : "memory");
+}
+
 template <typename T, int K>
-__global__ void __launch_bounds__(128, 3)
+__global__ void __launch_bounds__(kPrepThreads, 2)
 qkv_prep_kernel(const PrepArgs a) {
-  constexpr int kCtaTok = kPrepTok * kPrepGroups;                // at most this many tokens per CTA
-  __shared__ int s_s0[kCtaTok], s_e0[kCtaTok], s_slot[kCtaTok];
-  __shared__ long long s_cs[kCtaTok];
-  const int grp = threadIdx.x >> 4, li = threadIdx.x & 15;      // 16 threads x 8 channels cover one head row
-  // blockIdx.y < nq: a chunk of q heads; else a chunk of the 2*Hkv k and v heads.  The `upc` heads of a
-  // chunk sit side by side in the CTA (their rows of one token are neighbours in memory); with fewer
-  // than 8 heads per chunk the other groups take further 8-token tiles.
+  // shared tile: rows t0-(K-1) .. t0+kPrepTok-1 of the chunk's (up to 8) heads, [row][head][dk] in T
+  extern __shared__ __align__(16) uint8_t prep_smem[];
+  T* tile = reinterpret_cast<T*>(prep_smem);
+  __shared__ int s_s0[kPrepTok], s_e0[kPrepTok], s_slot[kPrepTok];
+  __shared__ long long s_cs[kPrepTok];
+  constexpr int kRows = kPrepTok + K - 1;
+  constexpr int kVec = 16 / (int)sizeof(T);                      // elements per 16-byte piece
+  const int tid = threadIdx.x;
+  // blockIdx.y < nq: a chunk of q heads; else a chunk of the 2*Hkv k and v heads
   const bool is_q = (int)blockIdx.y < a.nq;
   const int chunk = is_q ? blockIdx.y : blockIdx.y - a.nq;
   const int n_units = is_q ? a.H : 2 * a.Hkv;
-  const int upc = is_q ? a.upc_q : a.upc_kv, tpc = kPrepGroups / upc;
-  const int unit = chunk * upc + grp % upc;
-  const int cta_t0 = blockIdx.x * tpc * kPrepTok;
-  const int t0 = cta_t0 + (grp / upc) * kPrepTok;
-  if (threadIdx.x < tpc * kPrepTok) {                            // the per-token maps of the CTA's tokens
-    const int t = cta_t0 + threadIdx.x;
-    const bool ok = t < a.total;
-    s_s0[threadIdx.x] = ok ? a.seq_start[t] : 0;
-    s_e0[threadIdx.x] = ok ? a.seq_end[t] : 0;
-    s_slot[threadIdx.x] = ok ? a.seq_slot[t] : -1;
-    s_cs[threadIdx.x] = (ok && a.slot_mapping != nullptr) ? a.slot_mapping[t] : -1;
-  }
-  const int which = is_q ? 0 : (unit < a.Hkv ? 1 : 2);
-  const int head = is_q ? unit : (unit < a.Hkv ? unit : unit - a.Hkv);
-  const int heads = is_q ? a.H : a.Hkv;
-  const int c = li * 8;
-  const bool active = c < a.dk && unit < n_units && t0 < a.total;
-  const bool normalize = which != 2;
+  const int u0 = chunk * kPrepHeads;
+  const int nu = min(kPrepHeads, n_units - u0);                  // heads in this CTA
+  const int t0 = blockIdx.x * kPrepTok;
+  const int dk = a.dk, row_elems = kPrepHeads * dk;
+  const int pieces = dk / kVec;                                  // 16-byte pieces per head row
 
-  const T* src; int64_t row_st;
-  if (which == 0) { src = (const T*)a.qg + (int64_t)head * a.qg_head; row_st = a.qg_row; }
-  else if (which == 1) { src = (const T*)a.k + (int64_t)head * a.dk; row_st = a.k_row; }
-  else { src = (const T*)a.v + (int64_t)head * a.dk; row_st = a.v_row; }
-  T* dst = (T*)(which == 0 ? a.q_out : (which == 1 ? a.k_out : a.v_out)) + (int64_t)head * a.dk;
-  const int64_t dst_row = (int64_t)heads * a.dk;
-  const int ch = head * a.dk + c;                                // first of this thread's conv channels
+  auto unit_src = [&](int u, const T*& src, int64_t& row_st, int& which, int& head) {
+    if (is_q) { which = 0; head = u; src = (const T*)a.qg + (int64_t)head * a.qg_head; row_st = a.qg_row; }
+    else if (u < a.Hkv) { which = 1; head = u; src = (const T*)a.k + (int64_t)head * dk; row_st = a.k_row; }
+    else { which = 2; head = u - a.Hkv; src = (const T*)a.v + (int64_t)head * dk; row_st = a.v_row; }
+  };
+
+  // ---- stage the tile: every 16-byte piece by one asynchronous copy (whole rows per pass of the CTA) ---
+  {
+    const int per_row = nu * pieces;                              // 16-byte pieces per tile row (<= 256)
+    const int rows_per_pass = kPrepThreads / per_row;
+    const int r_off = tid / per_row, j = tid - r_off * per_row;
+    const int ul = j / pieces, pc = j - ul * pieces;
+    if (r_off < rows_per_pass) {
+      const T* src; int64_t row_st; int which, head;
+      unit_src(u0 + ul, src, row_st, which, head);
+      src += pc * kVec;
+      T* dst = tile + ul * dk + pc * kVec;
+      for (int r = r_off; r < kRows; r += rows_per_pass) {
+        const int t = t0 - (K - 1) + r;
+        const bool ok = t >= 0 && t < a.total;
+        prep_cp_async16(dst + r * row_elems, src + (ok ? (int64_t)t * row_st : 0), ok);
+      }
+    }
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  if (tid < kPrepTok) {                                          // the per-token maps of the CTA's tokens
+    const int t = t0 + tid;
+    const bool ok = t < a.total;
+    s_s0[tid] = ok ? a.seq_start[t] : 0;
+    s_e0[tid] = ok ? a.seq_end[t] : 0;
+    s_slot[tid] = ok ? a.seq_slot[t] : -1;
+    s_cs[tid] = (ok && a.slot_mapping != nullptr) ? a.slot_mapping[t] : -1;
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();
+
+  // ---- each 16-thread group walks a run of consecutive tokens of one head: the last K normalised
+  //      rows stay in registers, so every tile row is read (and normalised) once per group ---------------
+  const int grp = tid >> 4, li = tid & 15;                      // 16 threads x 8 channels cover one head row
+  constexpr int kGroups = kPrepThreads / 16;
+  const int gph = kGroups / nu;                                  // groups per head (2 with eight heads)
+  const int ul = grp % nu, part = grp / nu;
+  const int tpg = (kPrepTok + gph - 1) / gph;                    // tokens per group (<= kPrepTok / 2)
+  const int i_begin = part * tpg, i_end = min(kPrepTok, i_begin + tpg);
+  const int c = li * 8;
+  const bool lane_on = c < dk;
+  const uint32_t half_mask = 0xffffu << (16 * (grp & 1));       // the two head rows of a warp are independent
+  if (part >= gph || i_begin >= i_end) return;
+
+  const T* src_unused; int64_t row_st_unused; int which, head;
+  unit_src(u0 + ul, src_unused, row_st_unused, which, head);
+  const bool normalize = which != 2;
+  const int heads = which == 0 ? a.H : a.Hkv;
+  const int ch = head * dk + c;                                  // first of this thread's conv channels
+  T* state = (T*)a.state[which];
+  const T* init = (const T*)a.init[which];
+  const int64_t state_ss = a.state_ss[which];
+  T* dst = (T*)(which == 0 ? a.q_out : (which == 1 ? a.k_out : a.v_out)) + head * dk + c;
+  T* cache = (which == 0 || a.k_cache == nullptr) ? nullptr : (T*)(which == 1 ? a.k_cache : a.v_cache) + head * dk + c;
+  const int64_t dst_row = (int64_t)heads * dk, cache_row = (int64_t)a.Hkv * dk;
+  const float inv_dk = 1.0f / (float)dk;
 
   float wt[8][K];
 #pragma unroll
   for (int j = 0; j < 8; ++j)
 #pragma unroll
-    for (int kk = 0; kk < K; ++kk)
-      wt[j][kk] = active ? to_f32(((const T*)a.w[which])[(int64_t)(ch + j) * K + kk]) : 0.f;
+    for (int kk = 0; kk < K; ++kk) wt[j][kk] = lane_on ? to_f32(((const T*)a.w[which])[(int64_t)(ch + j) * K + kk]) : 0.f;
 
-  // ---- rows t0-(K-1) .. t0+kPrepTok-1, normalised ------------------------------------------------------
-  float x[kPrepTok + K - 1][8];
+  const T* trow = tile + i_begin * row_elems + ul * dk + c;      // tile row i_begin <-> token t0 + i_begin - (K-1)
+  float win[K][8];
+  constexpr int kMaxRows = kPrepTok / 2 + K - 1;
 #pragma unroll
-  for (int i = 0; i < kPrepTok + K - 1; ++i) {
-    const int t = t0 - (K - 1) + i;
-    if (active && t >= 0 && t < a.total) load8<T>(src + (int64_t)t * row_st + c, x[i]);
+  for (int rl = 0; rl < kMaxRows; ++rl) {
+    if (rl >= i_end - i_begin + K - 1) break;
+    float (&x)[8] = win[rl % K];
+    if (lane_on) load8<T>(trow + rl * row_elems, x);
     else {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) x[i][j] = 0.f;
+      for (int j = 0; j < 8; ++j) x[j] = 0.f;
     }
-  }
-  if (normalize) {
-    const float inv_dk = 1.0f / (float)a.dk;
-#pragma unroll
-    for (int i = 0; i < kPrepTok + K - 1; ++i) {
+    if (normalize) {
       float ss = 0.f;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) ss = fmaf(x[i][j], x[i][j], ss);
+      for (int j = 0; j < 8; ++j) ss = fmaf(x[j], x[j], ss);
 #pragma unroll
-      for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);     // the 16 threads of the row
-      const float r = rsqrtf(ss * inv_dk + a.eps);
+      for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(half_mask, ss, o, 16);
+      const float rs = rsqrtf(ss * inv_dk + a.eps);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) x[i][j] = round_through<T>(x[i][j] * r);           // the eager op rounds to T here
+      for (int j = 0; j < 8; ++j) x[j] = round_through<T>(x[j] * rs);                // the eager op rounds to T here
     }
-  }
-  __syncthreads();                                               // the token maps are in shared memory
-  if (!active) return;
-
-  T* state = (T*)a.state[which];
-  const T* init = (const T*)a.init[which];
-  const int64_t state_ss = a.state_ss[which];
-  T* cache = (T*)(which == 1 ? a.k_cache : a.v_cache);
-
-#pragma unroll
-  for (int i = 0; i < kPrepTok; ++i) {
+    if (rl < K - 1 || !lane_on) continue;                        // still filling the window
+    const int i = i_begin + rl - (K - 1);
     const int t = t0 + i;
     if (t >= a.total) break;
-    const int ti = t - cta_t0;
-    const int s0 = s_s0[ti], e0 = s_e0[ti], slot = s_slot[ti];
+    const int s0 = s_s0[i], e0 = s_e0[i], slot = s_slot[i];
     const bool from_state = init != nullptr && slot >= 0;
-    // channel j's input `back` rows before token t as this sequence sees it: its own rows, else
-    // its saved state, else 0
+    // channel j of the row `back` tokens before t as this sequence sees it: its own rows, else its
+    // saved state, else 0
     auto tap = [&](int back, int j) -> float {
-      if (t - back >= s0) return x[i + (K - 1) - back][j];
+      if (t - back >= s0) return win[(rl - back) % K][j];
       if (from_state) return to_f32(init[slot * state_ss + (int64_t)(ch + j) * (K - 1) + (K - 1) - (s0 - (t - back))]);
       return 0.f;
     };
@@ -176,8 +215,8 @@ qkv_prep_kernel(const PrepArgs a) {
       for (int j = 0; j < 8; ++j) {
         float acc = 0.f;
 #pragma unroll
-        for (int kk = 0; kk < K; ++kk) acc = fmaf(x[i + kk][j], wt[j][kk], acc);
-        y[j] = x[i + K - 1][j] + round_through<T>(acc);          // x + conv(x), the conv rounded as eager does
+        for (int kk = 0; kk < K; ++kk) acc = fmaf(win[(rl - (K - 1) + kk) % K][j], wt[j][kk], acc);
+        y[j] = x[j] + round_through<T>(acc);                     // x + conv(x), the conv rounded as eager does
       }
     } else {
 #pragma unroll
@@ -185,13 +224,13 @@ qkv_prep_kernel(const PrepArgs a) {
         float acc = 0.f;
 #pragma unroll
         for (int kk = 0; kk < K; ++kk) acc = fmaf(tap(K - 1 - kk, j), wt[j][kk], acc);
-        y[j] = x[i + K - 1][j] + round_through<T>(acc);
+        y[j] = x[j] + round_through<T>(acc);
       }
     }
-    store8<T>(dst + (int64_t)t * dst_row + c, y);
-    if (which != 0) {
-      const int64_t cs = s_cs[ti];
-      if (cs >= 0) store8<T>(cache + (cs * a.Hkv + head) * a.dk + c, y);
+    store8<T>(dst + t * dst_row, y);
+    if (cache != nullptr) {
+      const int64_t cs = s_cs[i];
+      if (cs >= 0) store8<T>(cache + cs * cache_row, y);
     }
     if (t == e0 - 1 && state != nullptr && slot >= 0) {
       // this token closes its sequence: persist its last K-1 conv inputs, oldest first
@@ -209,15 +248,16 @@ qkv_prep_kernel(const PrepArgs a) {
 
 template <typename T>
 int launch_prep(const PrepArgs& a, cudaStream_t st) {
-  const int tok_q = kPrepGroups / a.upc_q * kPrepTok, tok_kv = kPrepGroups / a.upc_kv * kPrepTok;
-  const int nx = ((a.total + tok_q - 1) / tok_q > (a.total + tok_kv - 1) / tok_kv) ? (a.total + tok_q - 1) / tok_q
-                                                                                     : (a.total + tok_kv - 1) / tok_kv;
-  dim3 grid(nx, a.nq + (2 * a.Hkv + a.upc_kv - 1) / a.upc_kv), block(128);
-  switch (a.K) {
-    case 2: qkv_prep_kernel<T, 2><<<grid, block, 0, st>>>(a); break;
-    case 3: qkv_prep_kernel<T, 3><<<grid, block, 0, st>>>(a); break;
-    default: qkv_prep_kernel<T, 4><<<grid, block, 0, st>>>(a); break;
-  }
+  const int smem = (kPrepTok + a.K - 1) * kPrepHeads * a.dk * (int)sizeof(T);
+  dim3 grid((a.total + kPrepTok - 1) / kPrepTok, a.nq + (2 * a.Hkv + kPrepHeads - 1) / kPrepHeads), block(kPrepThreads);
+#define ATMA_PREP_CASE(KK)                                                                                 \
+  case KK: {                                                                                               \
+    auto kern = qkv_prep_kernel<T, KK>;                                                                    \
+    ATMA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));           \
+    kern<<<grid, block, smem, st>>>(a);                                                                    \
+  } break;
+  switch (a.K) { ATMA_PREP_CASE(2) ATMA_PREP_CASE(3) ATMA_PREP_CASE(4) }
+#undef ATMA_PREP_CASE
   return launch_status("qkv_prep_prefill");
 }
 
@@ -262,10 +302,7 @@ extern "C" int atma_qkv_prep_prefill(const void* q_gate, int64_t qg_row_stride, 
   a.q_out = q_out; a.k_out = k_out; a.v_out = v_out;
   a.k_cache = k_cache; a.v_cache = v_cache; a.slot_mapping = k_cache ? slot_mapping : nullptr;
   a.total = total; a.H = H; a.Hkv = Hkv; a.dk = dk; a.K = K; a.eps = eps;
-  auto pow2_at_most_8 = [](int n) { int p = 1; while (p < n && p < 8) p <<= 1; return p; };
-  a.upc_q = pow2_at_most_8(H);
-  a.upc_kv = pow2_at_most_8(2 * Hkv);
-  a.nq = (H + a.upc_q - 1) / a.upc_q;
+  a.nq = (H + kPrepHeads - 1) / kPrepHeads;
   int rc = ATMA_OK;
   ATMA_DISPATCH_DTYPE(dtype, T, { rc = launch_prep<T>(a, (cudaStream_t)stream); });
   return rc;

@@ -306,7 +306,19 @@ def bench_prep(ab, dev, tokens, n_seqs, iters):
     e1.record()
     torch.cuda.synchronize()
     nbytes = total * (2 * H + 5 * HKV) * DK * 2.0
-    return e0.elapsed_time(e1) / iters, nbytes, total
+    ms = e0.elapsed_time(e1) / iters
+    # the same timing method on a plain device copy of the q|gate projection, as a reference point
+    dst = torch.empty_like(q_gate)
+    dst.copy_(q_gate)
+    torch.cuda.synchronize()
+    torch.cuda._sleep(20_000_000)
+    e0.record()
+    for _ in range(iters):
+        dst.copy_(q_gate)
+    e1.record()
+    torch.cuda.synchronize()
+    bench_prep.copy_gbs = 2.0 * q_gate.numel() * 2 / (e0.elapsed_time(e1) / iters * 1e-3) / 1e9
+    return ms, nbytes, total
 
 
 def profile_case(which):
@@ -342,7 +354,7 @@ def profile_case(which):
     elif which == "prep":
         ms, nbytes, total = bench_prep(ab, dev, tokens=65536, n_seqs=8, iters=5)
         info = {"kernel": "qkv_prep_kernel", "tokens": total, "bytes_per_launch": nbytes, "ms": ms,
-                "gbs": nbytes / (ms * 1e-3) / 1e9}
+                "gbs": nbytes / (ms * 1e-3) / 1e9, "plain_copy_gbs_same_method": bench_prep.copy_gbs}
     else:
         B, T = 2, 16384
         q = torch.randn(B, T, H, DK, generator=g).bfloat16().to(dev)
