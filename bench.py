@@ -263,8 +263,10 @@ def run_reference(args, rank):
     line = {"impl": "reference", "metric": METRIC, "value": val, "unit": "tok/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "global-layer mixing prefill (Polar + gated-delta scan), CPU sample",
-                       "tokens": sample_T, "heads": H, "kv_heads": HKV, "head_dim": DK, "chunk": CHUNK},
+            # the same workload as the GPU arm; each step times a bounded sample of it (see cpu_baseline.sample)
+            "config": {"workload": f"global-layer mixing prefill: Polar attention + gated-delta scan, one {T_PREFILL}-token sequence",
+                       "tokens": T_PREFILL, "heads": H, "kv_heads": HKV, "head_dim": DK, "chunk": CHUNK, "window": None,
+                       "sample_tokens": sample_T},
             "cpu_baseline": {"value": val, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample},
             "e2e": {"value": val, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
