@@ -85,6 +85,46 @@ __device__ __forceinline__ void prep_cp_async16(void* smem_dst, const void* gsrc
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gsrc), "r"(n) : "memory");
 }
 
+// A run of RUN consecutive tokens of one head that needs no sequence-boundary handling: rows come
+// from the shared tile, the last K normalised rows stay in registers, outputs go out once.
+template <typename T, int K, int RUN>
+__device__ __forceinline__ void prep_plain_run(const T* trow, int row_elems, const float (&wt)[8][K], bool normalize,
+                                               float inv_dk, float eps, uint32_t half_mask, T* dst, int64_t dst_row,
+                                               T* cache, int64_t cache_row, const long long* s_cs) {
+  long long cs[RUN];
+#pragma unroll
+  for (int i = 0; i < RUN; ++i) cs[i] = s_cs != nullptr ? s_cs[i] : -1;
+  float win[K][8];
+#pragma unroll
+  for (int rl = 0; rl < RUN + K - 1; ++rl) {
+    float (&x)[8] = win[rl % K];
+    load8<T>(trow + rl * row_elems, x);
+    if (normalize) {
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss = fmaf(x[j], x[j], ss);
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(half_mask, ss, o, 16);
+      const float rs = rsqrtf(ss * inv_dk + eps);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] = round_through<T>(x[j] * rs);                // the eager op rounds to T here
+    }
+    if (rl >= K - 1) {
+      const int i = rl - (K - 1);
+      float y[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float acc = 0.f;
+#pragma unroll
+        for (int kk = 0; kk < K; ++kk) acc = fmaf(win[(rl - (K - 1) + kk) % K][j], wt[j][kk], acc);
+        y[j] = x[j] + round_through<T>(acc);                     // x + conv(x), the conv rounded as eager does
+      }
+      store8<T>(dst + i * dst_row, y);
+      if (cs[i] >= 0) store8<T>(cache + cs[i] * cache_row, y);
+    }
+  }
+}
+
 template <typename T, int K>
 __global__ void __launch_bounds__(kPrepThreads, 2)
 qkv_prep_kernel(const PrepArgs a) {
@@ -177,6 +217,27 @@ qkv_prep_kernel(const PrepArgs a) {
   const T* trow = tile + i_begin * row_elems + ul * dk + c;      // tile row i_begin <-> token t0 + i_begin - (K-1)
   float win[K][8];
   constexpr int kMaxRows = kPrepTok / 2 + K - 1;
+
+  // ---- fast path: a full run (16 tokens with eight heads per CTA, 8 with four) that lies inside one
+  //      sequence, not at its start or end: straight-line code, so the rows' load -> reduce -> scale
+  //      chains overlap.  Both head rows of a warp share the code, so the decision is per warp. -----------
+  {
+    const int run = i_end - i_begin;
+    const int t_first = t0 + i_begin, t_last = t_first + run - 1;
+    const bool plain = (run == 16 || run == 8) && t_last < a.total && lane_on && s_s0[i_begin] <= t_first - (K - 1) &&
+                       s_e0[i_begin] > t_last + 1 && s_s0[i_begin] == s_s0[i_begin + run - 1];
+    const unsigned active = __activemask();
+    if (__all_sync(active, plain)) {
+      const long long* cs = cache != nullptr ? s_cs + i_begin : nullptr;
+      if (run == 16)
+        prep_plain_run<T, K, 16>(trow, row_elems, wt, normalize, inv_dk, a.eps, half_mask, dst + t_first * dst_row, dst_row,
+                                 cache, cache_row, cs);
+      else
+        prep_plain_run<T, K, 8>(trow, row_elems, wt, normalize, inv_dk, a.eps, half_mask, dst + t_first * dst_row, dst_row,
+                                cache, cache_row, cs);
+      return;
+    }
+  }
 #pragma unroll
   for (int rl = 0; rl < kMaxRows; ++rl) {
     if (rl >= i_end - i_begin + K - 1) break;
