@@ -10,10 +10,11 @@
 // before it, is staged in shared memory with 16-byte asynchronous copies (whole token rows, so
 // neighbouring DRAM pages).  A group of 16 threads x 8 channels then walks a run of consecutive
 // tokens of one head: each row is read from the tile once, normalised in registers (row sums by
-// shuffles), kept in a K-row register window for the taps, and q, k, v and the cache rows are written once.  Three
-// CTAs per SM keep ~200 KB of copies in flight, so the kernel is bandwidth-bound: each projection
-// element comes from DRAM once (the K-1 halo rows of a tile are its neighbour's rows, i.e. cache
-// hits) and every output goes out once.
+// shuffles), kept in a K-row register window for the taps, and q, k, v and the cache rows are
+// written once.  Runs that lie inside one sequence take a straight-line path without per-row
+// branches.  Two CTAs per SM keep ~140 KB of copies in flight; each projection element comes from
+// DRAM once (the K-1 halo rows of a tile are its neighbour's rows, i.e. cache hits) and every
+// output goes out once.
 #include "common.cuh"
 
 namespace atma {
