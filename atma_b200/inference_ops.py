@@ -143,3 +143,44 @@ def qkv_prep_prefill(q_gate, k, v, w_q, w_k, w_v, state_q, state_k, state_v, tok
         _lib.ptr(k_cache), _lib.ptr(v_cache), _lib.ptr(slot_mapping) if k_cache is not None else None,
         total, H, Hkv, dk, K, float(eps), _lib.dtype_code(q_gate), _lib.stream_ptr()))
     return q_out, k_out, v_out
+
+
+@torch.no_grad()
+def sigmoid_gate_mul(x, gate):
+    """x * sigmoid(gate) for (tokens, H, dk) operands with arbitrary (row, head) strides and a
+    contiguous last dim - e.g. x = the Polar content c and gate = the gate half of the q|gate
+    projection, read in place (inference/models/atma.py:552-558).  Returns (tokens, H, dk) dense."""
+    _lib.require_cuda(x, "sigmoid_gate_mul")
+    lib = _lib.load()
+    if x.shape != gate.shape or x.ndim != 3:
+        raise ValueError("x and gate must both be (tokens, H, dk)")
+    if x.stride(2) != 1:
+        x = x.contiguous()
+    if gate.stride(2) != 1 or gate.dtype != x.dtype:
+        gate = gate.to(x.dtype).contiguous()
+    rows, H, dk = x.shape
+    out = torch.empty((rows, H, dk), device=x.device, dtype=x.dtype)
+    _lib.check(lib.atma_sigmoid_gate_mul(_lib.ptr(x), x.stride(0), x.stride(1), _lib.ptr(gate), gate.stride(0),
+                                         gate.stride(1), _lib.ptr(out), rows, H, dk, _lib.dtype_code(x), _lib.stream_ptr()))
+    return out
+
+
+@torch.no_grad()
+def rms_sigmoid_gate(r, gate, eps=None):
+    """RMSNorm(r) over the head dim (affine-free) times sigmoid(gate): r (tokens, H, dk),
+    gate (tokens, H*dk); the memory read-out before ``mem.proj``
+    (inference/models/atma.py:373-375).  Returns (tokens, H*dk)."""
+    _lib.require_cuda(r, "rms_sigmoid_gate")
+    lib = _lib.load()
+    rows, H, dk = r.shape
+    if gate.shape != (rows, H * dk):
+        raise ValueError("gate must be (tokens, H*dk)")
+    r = r.contiguous()
+    if gate.stride(1) != 1 or gate.dtype != r.dtype:
+        gate = gate.to(r.dtype).contiguous()
+    if eps is None:
+        eps = torch.finfo(torch.float32).eps
+    out = torch.empty((rows, H * dk), device=r.device, dtype=r.dtype)
+    _lib.check(lib.atma_rms_sigmoid_gate(_lib.ptr(r), _lib.ptr(gate), gate.stride(0), _lib.ptr(out), rows, H, dk,
+                                         float(eps), _lib.dtype_code(r), _lib.stream_ptr()))
+    return out

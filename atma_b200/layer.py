@@ -9,6 +9,7 @@ the per-token maps its model runner builds (inference/engine/model_runner.py:395
     Polar attention                polar_attention_packed_fwd  un-expanded KV heads, one launch for all sequences
     memory branch                  packed_gated_delta_prefill  one call for all sequences, state rows in place,
                                                                on a side stream beside the attention
+    gate epilogues                 sigmoid_gate_mul, rms_sigmoid_gate   one pass each
     combine                        W_o(c * sigmoid(gate)) + W_mu(mag) + mem.proj(RMSNorm(r) * sigmoid(mem.gate x))
 
 The reference expands K/V to H heads, loops over the sequences for the memory branch and runs
@@ -19,7 +20,7 @@ import torch
 import torch.nn.functional as F
 
 from .gated_delta import packed_gated_delta_prefill
-from .inference_ops import qkv_prep_prefill
+from .inference_ops import qkv_prep_prefill, rms_sigmoid_gate, sigmoid_gate_mul
 from .mixing import _side_stream
 from .polar import polar_attention_packed_fwd
 
@@ -80,15 +81,14 @@ def global_attention_prefill_packed(x, sd, maps, *, num_heads, num_kv_heads, hea
             g = F.logsigmoid(_linear(x, sd, P + "mem.w_gamma").float() + mem_gamma_bias)
             beta = torch.sigmoid(_linear(x, sd, P + "mem.w_beta").float() + mem_beta_bias)
             r = packed_gated_delta_prefill(q, k, v, g, beta, maps.cu_seqlens, mem_state_table, maps.seq_slots)
-            r = F.rms_norm(r, (dk,)).reshape(total, H * dk)
-            mem_out = _linear(r * torch.sigmoid(_linear(x, sd, P + "mem.gate")), sd, P + "mem.proj")
+            mem_out = _linear(rms_sigmoid_gate(r, _linear(x, sd, P + "mem.gate")), sd, P + "mem.proj")
 
     c, mag = polar_attention_packed_fwd(q, k, v, maps.tile_seq_starts, maps.tile_q_starts, maps.tile_seq_lens,
                                         window=window, v_null=sd[P + "v_null"], null_base=sd[P + "null_base"],
                                         null_slope_raw=sd[P + "null_slope_raw"], len_gain_raw=sd[P + "len_gain_raw"],
                                         mag_beta_raw=sd[P + "mag_beta_raw"])
-    gate = q_gate[..., dk:].reshape(total, H * dk)
-    out = _linear(c.reshape(total, H * dk) * torch.sigmoid(gate), sd, P + "proj") + _linear(mag, sd, P + "mu_proj")
+    gated = sigmoid_gate_mul(c, q_gate[..., dk:]).view(total, H * dk)       # the gate half is read in place
+    out = _linear(gated, sd, P + "proj") + _linear(mag, sd, P + "mu_proj")
     if has_mem:
         if side is not cur:
             cur.wait_stream(side)

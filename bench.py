@@ -353,6 +353,27 @@ def profile_case(which):
             ab.polar_attention_decode(q, kc, vc, bt, cl, **P)
         info = {"kernel": "polar_decode_split_mma_kernel", "B": Bd, "context": ctx,
                 "bytes_per_launch": 2.0 * Bd * ctx * HKV * DK * 2}
+    elif which == "epilogue":
+        total = 65536
+        q_gate = torch.randn(total, H, 2 * DK, generator=g).bfloat16().to(dev)
+        c = torch.randn(total, H, DK, generator=g).bfloat16().to(dev)
+        gate2 = torch.randn(total, H * DK, generator=g).bfloat16().to(dev)
+        res = {}
+        for name, fn, nbytes in (("sigmoid_gate_mul", lambda: ab.sigmoid_gate_mul(c, q_gate[..., DK:]), 3.0 * c.numel() * 2),
+                                 ("rms_sigmoid_gate", lambda: ab.rms_sigmoid_gate(c, gate2), 3.0 * c.numel() * 2)):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda._sleep(20_000_000)
+            e0.record()
+            for _ in range(5):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / 5
+            res[name] = {"ms": ms, "bytes_per_launch": nbytes, "gbs": nbytes / (ms * 1e-3) / 1e9}
+        info = {"kernel": "sigmoid_gate_mul_kernel, rms_sigmoid_gate_kernel", "tokens": total, **res}
     elif which == "prep":
         ms, nbytes, total = bench_prep(ab, dev, tokens=65536, n_seqs=8, iters=5)
         info = {"kernel": "qkv_prep_kernel", "tokens": total, "bytes_per_launch": nbytes, "ms": ms,
@@ -594,7 +615,7 @@ def main():
                     help="N > 1: issue the context-parallel step launch by launch instead of replaying a CUDA graph")
     ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline leg (profiling runs)")
     ap.add_argument("--skip-decode", action="store_true", help="omit the decode leg (profiling runs)")
-    ap.add_argument("--profile", default=None, choices=["prefill", "decode", "scan", "prep"],
+    ap.add_argument("--profile", default=None, choices=["prefill", "decode", "scan", "prep", "epilogue"],
                     help="run a few launches of ONE kernel on a small case (a few hundred MB, larger than L2) "
                          "and exit; meant to be wrapped in ncu")
     args = ap.parse_args()

@@ -284,6 +284,26 @@ int atma_qkv_prep_prefill(const void* q_gate, int64_t qg_row_stride, int64_t qg_
                           void* k_cache, void* v_cache, const int64_t* slot_mapping,
                           int total, int H, int Hkv, int dk, int K, float eps, int dtype, void* stream);
 
+/* ----------------------------------------------------------------------------------
+ * Gate epilogues of a global layer's mixing output (next-step fusions; the reference runs each
+ * as three eager ops).
+ * atma_sigmoid_gate_mul: out[r][h][c] = x[r][h][c] * sigmoid(gate[r][h][c]) - the
+ *   `c_flat * torch.sigmoid(gate)` of `_combine` (inference/models/atma.py:552-558).  x and gate
+ *   with (row, head) element strides, so the gate half of the q|gate projection is read in place
+ *   and c may be the (tokens, H, dk) or the (H, tokens, dk) layout; out dense [rows][H][dk].
+ * atma_rms_sigmoid_gate: out[r][h*dk+c] = RMSNorm_dk(x[r][h][:])[c] * sigmoid(gate[r][h*dk+c])
+ *   - the memory read-out `F.rms_norm(r, (dk,)) * torch.sigmoid(mem.gate(x))`
+ *   (inference/models/atma.py:373-375; model/blocks.py:486-489).  x dense [rows][H][dk], gate
+ *   [rows][H*dk] with a row stride; affine-free norm; dk <= 128.
+ * Both round to the activation dtype after the sigmoid, after the norm and after the product,
+ * as the separate ops do.  head_dim a multiple of 8; pointers 16-byte aligned.
+ * ---------------------------------------------------------------------------------- */
+int atma_sigmoid_gate_mul(const void* x, int64_t x_row_stride, int64_t x_head_stride,
+                          const void* gate, int64_t gate_row_stride, int64_t gate_head_stride,
+                          void* out, int rows, int H, int dk, int dtype, void* stream);
+int atma_rms_sigmoid_gate(const void* x, const void* gate, int64_t gate_row_stride, void* out,
+                          int rows, int H, int dk, float eps, int dtype, void* stream);
+
 /* ------------------------------------------------------------------------------------
  * Scatter new K/V rows into the paged cache.  Replaces inference/layers/attention.py:7-27
  * behind store_kvcache (:30-56).  key, value [N][D] with row strides (D = Hkv*dk

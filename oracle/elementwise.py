@@ -47,3 +47,16 @@ def linear_head_rms_oracle(x, weight, bias, *, num_heads, head_dim=128, gated=Fa
     qn = qh * torch.rsqrt(qh.square().mean(-1, keepdim=True) + eps)
     out = torch.cat([qn, y[..., head_dim:]], dim=-1) if gated else qn
     return out.reshape(x.shape[0], num_heads * width)
+
+
+def sigmoid_gate_mul_oracle(x, gate):
+    """x * torch.sigmoid(gate) as eager runs it (inference/models/atma.py:555-556)."""
+    return x * torch.sigmoid(gate)
+
+
+def rms_sigmoid_gate_oracle(r, gate):
+    """F.rms_norm(r, (dk,)) flattened over heads, times torch.sigmoid(gate)
+    (inference/models/atma.py:373-375).  r (tokens, H, dk); gate (tokens, H*dk)."""
+    import torch.nn.functional as F
+    rows, H, dk = r.shape
+    return F.rms_norm(r, (dk,)).reshape(rows, H * dk) * torch.sigmoid(gate)

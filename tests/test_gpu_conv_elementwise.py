@@ -199,3 +199,37 @@ def test_qkv_prep_prefill_equals_the_separate_kernels():
         assert (got.reshape(want.shape) != want).float().mean() < 0.02
     for a, b in zip(st_f, st_u):
         assert max_rel(a, b) < 8e-3
+
+
+# ---- gate epilogues ---------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_sigmoid_gate_mul_reads_the_gate_half_in_place(dtype):
+    """c * sigmoid(gate) with gate = the second half of the q|gate projection (a strided view) and c in
+    the (H, tokens, dk) layout viewed as (tokens, H, dk): equals the eager expression on the CPU."""
+    g = torch.Generator().manual_seed(8)
+    tokens, H, dk = 77, 8, 128
+    q_gate = torch.randn(tokens, H, 2 * dk, generator=g).to(dtype)
+    c_ht = torch.randn(H, tokens, dk, generator=g).to(dtype)
+    want = oracle.sigmoid_gate_mul_oracle(c_ht.transpose(0, 1), q_gate[..., dk:])
+    got = atma_b200.sigmoid_gate_mul(c_ht.cuda().transpose(0, 1), q_gate.cuda()[..., dk:])
+    assert got.shape == (tokens, H, dk) and got.is_contiguous()
+    if dtype == torch.float32:
+        assert max_abs(got, want) < 1e-5
+    else:
+        assert max_rel(got, want) < 8e-3 and (got.cpu() != want).float().mean() < 0.02
+
+
+@pytest.mark.parametrize("dtype,dk", [(torch.bfloat16, 128), (torch.float16, 64), (torch.float32, 128), (torch.bfloat16, 32)])
+def test_rms_sigmoid_gate_matches_eager(dtype, dk):
+    g = torch.Generator().manual_seed(9)
+    tokens, H = 203, 4
+    r = (torch.randn(tokens, H, dk, generator=g) * 3).to(dtype)
+    gate_wide = torch.randn(tokens, H * dk + 16, generator=g).to(dtype)
+    gate = gate_wide[:, :H * dk]                                  # a row stride larger than the width
+    want = oracle.rms_sigmoid_gate_oracle(r, gate)
+    got = atma_b200.rms_sigmoid_gate(r.cuda(), gate_wide.cuda()[:, :H * dk])
+    assert got.shape == (tokens, H * dk)
+    if dtype == torch.float32:
+        assert max_abs(got, want) < 1e-5
+    else:
+        assert max_rel(got, want) < 8e-3 and (got.cpu() != want).float().mean() < 0.03
