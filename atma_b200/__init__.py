@@ -11,13 +11,13 @@ from .polar import (polar_attention_fwd, polar_attention_packed_fwd, polar_atten
                     polar_prefill_raw)
 from .gated_delta import gated_delta_decode_step, chunk_gated_delta_rule, packed_gated_delta_prefill
 from .causal_conv1d import causal_conv1d_decode_step, causal_conv1d_fn
-from .inference_ops import squared_relu_gate, packed_causal_conv1d, softcap_logits, linear_head_rms, qkv_prep_prefill, sigmoid_gate_mul, rms_sigmoid_gate
+from .inference_ops import squared_relu_gate, packed_causal_conv1d, softcap_logits, linear_head_rms, qkv_prep_prefill, sigmoid_gate_mul, rms_sigmoid_gate, lfm2_conv_decode_step, lfm2_conv_packed
 from .kvcache import store_kvcache
 
 __all__ = [
     "polar_attention_fwd", "polar_attention_packed_fwd", "polar_attention_decode", "polar_prefill_raw",
     "gated_delta_decode_step", "chunk_gated_delta_rule", "packed_gated_delta_prefill",
     "causal_conv1d_decode_step", "causal_conv1d_fn",
-    "squared_relu_gate", "packed_causal_conv1d", "softcap_logits", "linear_head_rms", "qkv_prep_prefill", "sigmoid_gate_mul", "rms_sigmoid_gate",
+    "squared_relu_gate", "packed_causal_conv1d", "softcap_logits", "linear_head_rms", "qkv_prep_prefill", "sigmoid_gate_mul", "rms_sigmoid_gate", "lfm2_conv_decode_step", "lfm2_conv_packed",
     "store_kvcache",
 ]

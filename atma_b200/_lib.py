@@ -93,6 +93,10 @@ _SIGNATURES = {
     "atma_sigmoid_gate_mul": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p,
                                       c_int, c_int, c_int, c_int, c_void_p]),
     "atma_rms_sigmoid_gate": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p]),
+    "atma_lfm2_conv_decode_step": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64,
+                                           c_int, c_int, c_int, c_int, c_void_p]),
+    "atma_lfm2_conv_packed": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64,
+                                      c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "atma_store_kvcache": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
                                    c_int, c_int, c_int, c_void_p]),
     "atma_squared_relu_gate": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_int,

@@ -1,0 +1,161 @@
+// The gated short convolution of the local (LFM2) layers, fused around the depthwise causal conv:
+//   projected = in_proj(x) = [B | C | x'] ;  y = C * conv(B * x')
+// (inference/models/atma.py:631-673).  The reference runs chunk, B*x', the conv (decode step or
+// packed prefill) and C*conv as separate ops; here the projection is read once, the gated input
+// B*x' never reaches memory (only its last K-1 values, the conv state), and y is written once.
+// Rounding to the activation dtype happens where the separate ops round: after B*x', after the
+// conv, after the product with C.
+#include "common.cuh"
+
+namespace atma {
+
+namespace {
+
+// ---- decode step: one token per sequence, in place on the slot-indexed state table -----------------
+template <typename T, int K>
+__global__ void lfm2_conv_step_kernel(const T* __restrict__ proj, int64_t proj_sb, const T* __restrict__ w,
+                                      const int64_t* __restrict__ slots, T* __restrict__ state, int64_t state_ss,
+                                      T* __restrict__ out, int64_t out_sb, int D) {
+  const int b = blockIdx.x;
+  const int d = blockIdx.y * blockDim.x + threadIdx.x;
+  if (d >= D) return;
+  const T* p = proj + b * proj_sb;
+  const float bv = to_f32(p[d]), cv = to_f32(p[D + d]), xv = to_f32(p[2 * D + d]);
+  const T xg = from_f32<T>(bv * xv);                            // the gated conv input, as eager materialises it
+  const int64_t slot = slots[b];
+  float acc = to_f32(xg) * to_f32(w[d * K + (K - 1)]);
+  if (slot >= 0) {
+    T* s = state + slot * state_ss + (int64_t)d * (K - 1);
+    T old[K - 1];
+#pragma unroll
+    for (int j = 0; j < K - 1; ++j) old[j] = s[j];
+#pragma unroll
+    for (int j = 0; j < K - 1; ++j) acc = fmaf(to_f32(old[j]), to_f32(w[d * K + j]), acc);
+#pragma unroll
+    for (int j = 0; j + 1 < K - 1; ++j) s[j] = old[j + 1];
+    s[K - 2] = xg;
+  }
+  out[b * out_sb + d] = from_f32<T>(cv * round_through<T>(acc));
+}
+
+// ---- packed prefill: thread = one channel x a run of consecutive tokens ---------------------------------
+constexpr int kLfmTokPerThread = 16;
+
+template <typename T, int K>
+__global__ void lfm2_conv_packed_kernel(const T* __restrict__ proj, int64_t proj_st, const T* __restrict__ w,
+                                        T* __restrict__ out, int64_t out_st, T* __restrict__ state,
+                                        const T* __restrict__ init_state, int64_t state_ss,
+                                        const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_end,
+                                        const int32_t* __restrict__ seq_slot, int total, int D) {
+  const int d = blockIdx.y * blockDim.x + threadIdx.x;
+  const int t0 = blockIdx.x * kLfmTokPerThread;
+  if (d >= D) return;
+  float wt[K];
+#pragma unroll
+  for (int j = 0; j < K; ++j) wt[j] = to_f32(w[d * K + j]);
+  auto gated = [&](int t) -> float {                            // B * x' of packed row t, rounded to T
+    const T* p = proj + (int64_t)t * proj_st;
+    return round_through<T>(to_f32(p[d]) * to_f32(p[2 * D + d]));
+  };
+  // the gated inputs of rows t0-(K-1) .. t0-1 (only used where they belong to the token's own sequence)
+  float win[K];
+#pragma unroll
+  for (int j = 0; j < K - 1; ++j) {
+    const int t = t0 - (K - 1) + j;
+    win[j] = t >= 0 ? gated(t) : 0.f;
+  }
+  const int t1 = min(t0 + kLfmTokPerThread, total);
+  for (int t = t0; t < t1; ++t) {
+    const int s0 = seq_start[t], e0 = seq_end[t], slot = seq_slot[t];
+    win[K - 1] = gated(t);
+    // input `back` rows before t as this sequence sees it: its own rows, else its saved state, else 0
+    auto tap = [&](int back) -> float {
+      if (t - back >= s0) return win[K - 1 - back];
+      if (init_state != nullptr && slot >= 0)
+        return to_f32(init_state[slot * state_ss + (int64_t)d * (K - 1) + (K - 1) - (s0 - (t - back))]);
+      return 0.f;
+    };
+    float acc = 0.f;
+#pragma unroll
+    for (int j = 0; j < K; ++j) acc = fmaf(tap(K - 1 - j), wt[j], acc);
+    const float cv = to_f32(proj[(int64_t)t * proj_st + D + d]);
+    out[(int64_t)t * out_st + d] = from_f32<T>(cv * round_through<T>(acc));
+    if (t == e0 - 1 && slot >= 0 && state != nullptr) {
+      float keep[K - 1];
+#pragma unroll
+      for (int j = 0; j < K - 1; ++j) keep[j] = tap(K - 2 - j);
+#pragma unroll
+      for (int j = 0; j < K - 1; ++j) state[slot * state_ss + (int64_t)d * (K - 1) + j] = from_f32<T>(keep[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < K - 1; ++j) win[j] = win[j + 1];
+  }
+}
+
+template <typename T>
+int launch_lfm2_step(const void* proj, int64_t proj_sb, const void* w, const int64_t* slots, void* state,
+                     int64_t state_ss, void* out, int64_t out_sb, int B, int D, int K, cudaStream_t st) {
+  dim3 grid(B, (D + 255) / 256), block(256);
+  switch (K) {
+    case 2: lfm2_conv_step_kernel<T, 2><<<grid, block, 0, st>>>((const T*)proj, proj_sb, (const T*)w, slots, (T*)state, state_ss, (T*)out, out_sb, D); break;
+    case 3: lfm2_conv_step_kernel<T, 3><<<grid, block, 0, st>>>((const T*)proj, proj_sb, (const T*)w, slots, (T*)state, state_ss, (T*)out, out_sb, D); break;
+    case 4: lfm2_conv_step_kernel<T, 4><<<grid, block, 0, st>>>((const T*)proj, proj_sb, (const T*)w, slots, (T*)state, state_ss, (T*)out, out_sb, D); break;
+    default: return fail(ATMA_ERR_UNSUPPORTED, "lfm2_conv_decode_step: kernel size %d not in 2..4", K);
+  }
+  return launch_status("lfm2_conv_decode_step");
+}
+
+template <typename T>
+int launch_lfm2_packed(const void* proj, int64_t proj_st, const void* w, void* out, int64_t out_st, void* state,
+                       const void* init_state, int64_t state_ss, const int32_t* s0, const int32_t* e0, const int32_t* sl,
+                       int total, int D, int K, cudaStream_t st) {
+  dim3 grid((total + kLfmTokPerThread - 1) / kLfmTokPerThread, (D + 127) / 128), block(128);
+#define ATMA_CASE(KK)                                                                                               \
+  case KK:                                                                                                          \
+    lfm2_conv_packed_kernel<T, KK><<<grid, block, 0, st>>>((const T*)proj, proj_st, (const T*)w, (T*)out, out_st,  \
+                                                           (T*)state, (const T*)init_state, state_ss, s0, e0, sl,  \
+                                                           total, D);                                               \
+    break;
+  switch (K) {
+    ATMA_CASE(2) ATMA_CASE(3) ATMA_CASE(4)
+    default: return fail(ATMA_ERR_UNSUPPORTED, "lfm2_conv_packed: kernel size %d not in 2..4", K);
+  }
+#undef ATMA_CASE
+  return launch_status("lfm2_conv_packed");
+}
+
+}  // namespace
+}  // namespace atma
+
+using namespace atma;
+
+extern "C" int atma_lfm2_conv_decode_step(const void* projected, int64_t proj_row_stride, const void* weight,
+                                          const int64_t* slots, void* state, int64_t state_slot_stride, void* out,
+                                          int64_t out_row_stride, int B, int D, int K, int dtype, void* stream) {
+  ATMA_REQUIRE(dtype_ok(dtype), "lfm2_conv_decode_step: unsupported dtype %d", dtype);
+  if (B <= 0 || D <= 0) return ATMA_OK;
+  ATMA_REQUIRE(slots != nullptr && state != nullptr, "lfm2_conv_decode_step: slots and the state table are required");
+  int rc = ATMA_OK;
+  ATMA_DISPATCH_DTYPE(dtype, T, {
+    rc = launch_lfm2_step<T>(projected, proj_row_stride, weight, slots, state, state_slot_stride, out, out_row_stride, B, D, K,
+                             (cudaStream_t)stream);
+  });
+  return rc;
+}
+
+extern "C" int atma_lfm2_conv_packed(const void* projected, int64_t proj_row_stride, const void* weight, void* out,
+                                     int64_t out_row_stride, void* state, const void* init_state,
+                                     int64_t state_slot_stride, const int32_t* token_seq_start,
+                                     const int32_t* token_seq_end, const int32_t* token_seq_slot, int total, int D,
+                                     int K, int dtype, void* stream) {
+  ATMA_REQUIRE(dtype_ok(dtype), "lfm2_conv_packed: unsupported dtype %d", dtype);
+  ATMA_REQUIRE(init_state == nullptr || init_state != state, "lfm2_conv_packed: init_state must not alias state");
+  if (total <= 0 || D <= 0) return ATMA_OK;
+  ATMA_REQUIRE(token_seq_start && token_seq_end && token_seq_slot, "lfm2_conv_packed: the per-token sequence arrays are required");
+  int rc = ATMA_OK;
+  ATMA_DISPATCH_DTYPE(dtype, T, {
+    rc = launch_lfm2_packed<T>(projected, proj_row_stride, weight, out, out_row_stride, state, init_state, state_slot_stride,
+                               token_seq_start, token_seq_end, token_seq_slot, total, D, K, (cudaStream_t)stream);
+  });
+  return rc;
+}

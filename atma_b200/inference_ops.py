@@ -184,3 +184,61 @@ def rms_sigmoid_gate(r, gate, eps=None):
     _lib.check(lib.atma_rms_sigmoid_gate(_lib.ptr(r), _lib.ptr(gate), gate.stride(0), _lib.ptr(out), rows, H, dk,
                                          float(eps), _lib.dtype_code(r), _lib.stream_ptr()))
     return out
+
+
+def _check_conv_state(state_table, dt, K):
+    if state_table.dtype != dt or state_table.stride(2) != 1 or state_table.stride(1) != K - 1:
+        raise ValueError("state_table must be (max_seqs, D, K-1) with dense rows in the activation dtype")
+
+
+@torch.no_grad()
+def lfm2_conv_decode_step(projected, weight, slots, state_table):
+    """One decode step of the local layers' gated short conv: projected (B, 3*D) = [B | C | x'] as
+    ``in_proj`` returns it, weight (D, K), slots (B,), state_table (max_seqs, D, K-1) updated IN
+    PLACE.  Returns C * conv(B * x') (B, D) - what inference/models/atma.py:633-636,668-673 feed
+    to ``out_proj``."""
+    _lib.require_cuda(projected, "lfm2_conv_decode_step")
+    lib = _lib.load()
+    Bn, D3 = projected.shape
+    D, K = weight.shape
+    if D3 != 3 * D:
+        raise ValueError("projected must be (B, 3*D)")
+    if projected.stride(1) != 1:
+        projected = projected.contiguous()
+    weight = weight.to(projected.dtype).contiguous()
+    _check_conv_state(state_table, projected.dtype, K)
+    slots = slots.to(torch.int64).contiguous()
+    out = torch.empty((Bn, D), device=projected.device, dtype=projected.dtype)
+    _lib.check(lib.atma_lfm2_conv_decode_step(_lib.ptr(projected), projected.stride(0), _lib.ptr(weight), _lib.ptr(slots),
+                                              _lib.ptr(state_table), state_table.stride(0), _lib.ptr(out), out.stride(0),
+                                              Bn, D, K, _lib.dtype_code(projected), _lib.stream_ptr()))
+    return out
+
+
+@torch.no_grad()
+def lfm2_conv_packed(projected, weight, state_table, token_seq_starts, token_seq_ends, token_seq_slots,
+                     initial_state=None):
+    """The same block over packed ragged prompts (inference/models/atma.py:648-653): projected
+    (tokens, 3*D); each sequence's row of ``state_table`` receives its last K-1 gated inputs.
+    ``initial_state`` (a table of the same layout, not the one being written) continues cached
+    prefixes; None = fresh prompts.  Returns C * conv(B * x') (tokens, D)."""
+    _lib.require_cuda(projected, "lfm2_conv_packed")
+    lib = _lib.load()
+    total, D3 = projected.shape
+    D, K = weight.shape
+    if D3 != 3 * D:
+        raise ValueError("projected must be (tokens, 3*D)")
+    if projected.stride(1) != 1:
+        projected = projected.contiguous()
+    weight = weight.to(projected.dtype).contiguous()
+    _check_conv_state(state_table, projected.dtype, K)
+    if initial_state is not None and (initial_state.stride() != state_table.stride() or initial_state.dtype != state_table.dtype):
+        raise ValueError("initial_state must have the layout of state_table")
+    i32 = lambda t: t.to(device=projected.device, dtype=torch.int32).contiguous()
+    s0, e0, sl = i32(token_seq_starts), i32(token_seq_ends), i32(token_seq_slots)
+    out = torch.empty((total, D), device=projected.device, dtype=projected.dtype)
+    _lib.check(lib.atma_lfm2_conv_packed(_lib.ptr(projected), projected.stride(0), _lib.ptr(weight), _lib.ptr(out),
+                                         out.stride(0), _lib.ptr(state_table), _lib.ptr(initial_state), state_table.stride(0),
+                                         _lib.ptr(s0), _lib.ptr(e0), _lib.ptr(sl), total, D, K,
+                                         _lib.dtype_code(projected), _lib.stream_ptr()))
+    return out

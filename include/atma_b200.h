@@ -304,6 +304,27 @@ int atma_sigmoid_gate_mul(const void* x, int64_t x_row_stride, int64_t x_head_st
 int atma_rms_sigmoid_gate(const void* x, const void* gate, int64_t gate_row_stride, void* out,
                           int rows, int H, int dk, float eps, int dtype, void* stream);
 
+/* ----------------------------------------------------------------------------------
+ * Gated short convolution of the local (LFM2) layers, fused around the depthwise conv:
+ *   projected = in_proj(x) = [B | C | x'] (row of 3*D);  y = C * conv(B * x')
+ * (inference/models/atma.py:631-673: chunk, B*x', _gpu_conv_step / packed_causal_conv1d, C*conv).
+ * _decode_step: one token per sequence; state [rows][D][K-1] updated in place at DEVICE int64
+ *   slots (slot < 0: no state is read or written), holds the last K-1 GATED inputs, oldest first.
+ * _packed: ragged prefill with the per-token maps of atma_packed_causal_conv1d; each sequence's
+ *   row of `state` receives its last K-1 gated inputs; init_state (same layout, must not alias
+ *   state) is the left context of every sequence with a slot >= 0, NULL = fresh prompts.
+ * out [rows][D]; weight [D][K], K in 2..4; strides in elements.
+ * ---------------------------------------------------------------------------------- */
+int atma_lfm2_conv_decode_step(const void* projected, int64_t proj_row_stride, const void* weight,
+                               const int64_t* slots, void* state, int64_t state_slot_stride,
+                               void* out, int64_t out_row_stride, int B, int D, int K, int dtype,
+                               void* stream);
+int atma_lfm2_conv_packed(const void* projected, int64_t proj_row_stride, const void* weight,
+                          void* out, int64_t out_row_stride, void* state, const void* init_state,
+                          int64_t state_slot_stride, const int32_t* token_seq_start,
+                          const int32_t* token_seq_end, const int32_t* token_seq_slot,
+                          int total, int D, int K, int dtype, void* stream);
+
 /* ------------------------------------------------------------------------------------
  * Scatter new K/V rows into the paged cache.  Replaces inference/layers/attention.py:7-27
  * behind store_kvcache (:30-56).  key, value [N][D] with row strides (D = Hkv*dk

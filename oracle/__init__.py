@@ -17,7 +17,8 @@ from .polar import (polar_params_host, polar_materialized, polar_streaming,
 from .gated_delta import (gated_delta_sequential, gated_delta_chunked,
                           gated_delta_step, chunk_gated_delta_rule_oracle)
 from .conv import (causal_conv1d_prefill, causal_conv1d_step,
-                   packed_causal_conv1d_oracle, store_kvcache_oracle, qkv_prep_prefill_oracle)
+                   packed_causal_conv1d_oracle, store_kvcache_oracle, qkv_prep_prefill_oracle,
+                   lfm2_conv_step_oracle, lfm2_conv_packed_oracle)
 from .elementwise import (squared_relu_gate_oracle, softcap_logits_oracle, linear_head_rms_oracle,
                           sigmoid_gate_mul_oracle, rms_sigmoid_gate_oracle)
 
@@ -27,6 +28,7 @@ __all__ = [
     "gated_delta_sequential", "gated_delta_chunked", "gated_delta_step",
     "chunk_gated_delta_rule_oracle",
     "causal_conv1d_prefill", "causal_conv1d_step", "packed_causal_conv1d_oracle", "qkv_prep_prefill_oracle",
+    "lfm2_conv_step_oracle", "lfm2_conv_packed_oracle",
     "store_kvcache_oracle",
     "squared_relu_gate_oracle", "softcap_logits_oracle", "linear_head_rms_oracle",
     "sigmoid_gate_mul_oracle", "rms_sigmoid_gate_oracle",

@@ -107,3 +107,33 @@ def qkv_prep_prefill_oracle(q_gate, k, v, w_q, w_k, w_v, state_q, state_k, state
     if k_cache is not None:
         store_kvcache_oracle(k_out, v_out, k_cache, v_cache, slot_mapping)
     return q_out, k_out, v_out
+
+
+def lfm2_conv_step_oracle(projected, weight, slots, state_table):
+    """Decode step of the local layers' gated conv, op by op (inference/models/atma.py:633-636,668-673):
+    chunk, B*x', conv step on the slot-indexed table (MUTATED), C*conv.  Returns (B, D) in the input dtype."""
+    Bv, Cv, xp = projected.chunk(3, dim=-1)
+    x_gated = Bv * xp
+    conv = causal_conv1d_step(x_gated, weight, slots, state_table).to(projected.dtype)
+    return Cv * conv
+
+
+def lfm2_conv_packed_oracle(projected, weight, state_table, token_seq_starts, token_seq_ends, token_seq_slots,
+                            initial_state=None):
+    """Packed prefill of the same block (inference/models/atma.py:648-653), sequence by sequence."""
+    Bv, Cv, xp = projected.chunk(3, dim=-1)
+    x_gated = Bv * xp
+    total = projected.shape[0]
+    conv = torch.zeros(total, weight.shape[0], dtype=torch.float32)
+    done = set()
+    for t in range(total):
+        s, e, slot = int(token_seq_starts[t]), int(token_seq_ends[t]), int(token_seq_slots[t])
+        if (s, e) in done:
+            continue
+        done.add((s, e))
+        init = initial_state[slot] if (initial_state is not None and slot >= 0) else None
+        o, fin = causal_conv1d_prefill(x_gated[s:e], weight, init)
+        conv[s:e] = o
+        if slot >= 0:
+            state_table[slot] = fin.to(state_table.dtype)
+    return Cv * conv.to(projected.dtype)

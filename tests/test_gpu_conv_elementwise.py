@@ -233,3 +233,53 @@ def test_rms_sigmoid_gate_matches_eager(dtype, dk):
         assert max_abs(got, want) < 1e-5
     else:
         assert max_rel(got, want) < 8e-3 and (got.cpu() != want).float().mean() < 0.03
+
+
+# ---- gated short conv of the local layers (chunk, B*x', conv, C*conv in one pass) ------------------------------
+@pytest.mark.parametrize("dtype,K", [(torch.bfloat16, 3), (torch.float16, 4), (torch.float32, 3), (torch.bfloat16, 2)])
+def test_lfm2_conv_decode_step_matches_the_op_by_op_oracle(dtype, K):
+    g = torch.Generator().manual_seed(K)
+    B, D, rows = 5, 384, 9
+    proj = torch.randn(B, 3 * D, generator=g).to(dtype)
+    w = (torch.randn(D, K, generator=g) * 0.5).to(dtype)
+    table = torch.randn(rows, D, K - 1, generator=g).to(dtype)
+    slots = torch.tensor([4, 0, 7, 2, 8])
+    ref_table = table.clone()
+    want = oracle.lfm2_conv_step_oracle(proj, w, slots, ref_table)
+    tg = table.cuda()
+    got = atma_b200.lfm2_conv_decode_step(proj.cuda(), w.cuda(), slots.cuda(), tg)
+    if dtype == torch.float32:
+        assert max_abs(got, want) < 1e-5 and max_abs(tg, ref_table) < 1e-6
+    else:
+        assert max_rel(got, want) < 8e-3 and (got.cpu() != want).float().mean() < 0.03
+        assert torch.equal(tg.cpu(), ref_table)                    # the state holds the rounded B*x' exactly
+    untouched = [r for r in range(rows) if r not in slots.tolist()]
+    assert torch.equal(tg.cpu()[untouched], table[untouched])
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("continued", [False, True])
+def test_lfm2_conv_packed_matches_the_op_by_op_oracle(dtype, continued):
+    g = torch.Generator().manual_seed(12)
+    lens, slots, D, K, rows = [1, 40, 17, 2, 33], [3, 0, -1, 5, 1], 256, 3, 6
+    total = sum(lens)
+    proj = torch.randn(total, 3 * D, generator=g).to(dtype)
+    w = (torch.randn(D, K, generator=g) * 0.5).to(dtype)
+    table = torch.randn(rows, D, K - 1, generator=g).to(dtype)
+    s0, e0, sl, pos = [], [], [], 0
+    for n, s in zip(lens, slots):
+        s0 += [pos] * n; e0 += [pos + n] * n; sl += [s] * n
+        pos += n
+    s0, e0, sl = (torch.tensor(x, dtype=torch.int32) for x in (s0, e0, sl))
+    init = table.clone() if continued else None
+    ref_table = table.clone()
+    want = oracle.lfm2_conv_packed_oracle(proj, w, ref_table, s0, e0, sl, initial_state=init)
+    tg = table.cuda()
+    got = atma_b200.lfm2_conv_packed(proj.cuda(), w.cuda(), tg, s0.cuda(), e0.cuda(), sl.cuda(),
+                                     initial_state=None if init is None else init.cuda())
+    if dtype == torch.float32:
+        assert max_abs(got, want) < 1e-5 and max_abs(tg, ref_table) < 1e-6
+    else:
+        assert max_rel(got, want) < 8e-3 and (got.cpu() != want).float().mean() < 0.03
+        assert torch.equal(tg.cpu(), ref_table)
+    assert torch.equal(tg.cpu()[[2, 4]], table[[2, 4]])             # rows no sequence owns
