@@ -78,6 +78,10 @@ _SIGNATURES = {
     "atma_gated_delta_scan_varlen": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                              c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
                                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]),
+    "atma_gated_delta_scan_varlen_snapshots": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                                       c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                       c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_int,
+                                                       c_void_p]),
     "atma_gated_delta_scan_varlen_scratch_bytes": (c_int64, [c_int64, c_int, c_int, c_int, c_int]),
     "atma_causal_conv1d_decode_step": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64,
                                                c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p]),

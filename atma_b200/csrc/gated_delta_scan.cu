@@ -234,7 +234,8 @@ int gated_delta_scan_mma_varlen(const void* q, const void* k, const void* v, int
                                 const int32_t* cu_seqlens, int n_seqs, int64_t total_tokens, const float* initial_state,
                                 float* final_state, float* state_table, int64_t slot_stride, const int64_t* slots,
                                 const int32_t* has_initial, void* o, void* scratch, int H, int Hkv, int normalize_qk,
-                                float scale, cudaStream_t st);
+                                float scale, float* snapshots, const int32_t* snap_offsets, int snap_chunks,
+                                cudaStream_t st);
 
 }  // namespace atma
 
@@ -265,17 +266,20 @@ extern "C" int64_t atma_gated_delta_scan_varlen_scratch_bytes(int64_t total_toke
   return gated_delta_scan_mma_varlen_scratch_bytes(total_tokens, n_seqs, H);
 }
 
-extern "C" int atma_gated_delta_scan_varlen(const void* q, const void* k, const void* v, int dtype, const float* g,
+static int scan_varlen_impl(const void* q, const void* k, const void* v, int dtype, const float* g,
                                             const float* beta, const int32_t* cu_seqlens, int n_seqs,
                                             int64_t total_tokens, const float* initial_state, float* final_state,
                                             float* state_table, int64_t slot_stride, const int64_t* slots,
                                             const int32_t* has_initial, void* o, void* scratch, int H, int Hkv, int dk,
-                                            int dv, int normalize_qk, float scale, void* stream) {
+                                            int dv, int normalize_qk, float scale, float* snapshots,
+                                            const int32_t* snap_offsets, int snap_every_tokens, void* stream) {
   ATMA_REQUIRE(gated_delta_scan_mma_supported(dtype, dk, dv),
                "gated_delta_scan_varlen: needs 16-bit inputs with dk = dv = 128 (got dtype %d, dk %d, dv %d)", dtype, dk, dv);
   ATMA_REQUIRE(n_seqs >= 0 && total_tokens >= 0 && H > 0 && Hkv > 0 && H % Hkv == 0, "gated_delta_scan_varlen: bad shape");
   ATMA_REQUIRE(total_tokens / kScanC + n_seqs < (1 << 30), "gated_delta_scan_varlen: too many chunks");
   ATMA_REQUIRE(n_seqs <= 65535, "gated_delta_scan_varlen: at most 65535 sequences per call (got %d)", n_seqs);
+  ATMA_REQUIRE(snapshots == nullptr || (snap_offsets != nullptr && snap_every_tokens > 0 && snap_every_tokens % kScanC == 0),
+               "gated_delta_scan_varlen: snapshots need offsets and a spacing that is a multiple of %d tokens", kScanC);
   if (n_seqs == 0) return ATMA_OK;
   ATMA_REQUIRE(cu_seqlens != nullptr, "gated_delta_scan_varlen: cu_seqlens is required");
   ATMA_REQUIRE(state_table == nullptr || slots != nullptr, "gated_delta_scan_varlen: a state table needs slots");
@@ -285,7 +289,31 @@ extern "C" int atma_gated_delta_scan_varlen(const void* q, const void* k, const 
                    (uintptr_t)v % 16 == 0, "gated_delta_scan_varlen: scratch must be 256-byte and inputs 16-byte aligned");
   return gated_delta_scan_mma_varlen(q, k, v, dtype, g, beta, cu_seqlens, n_seqs, total_tokens, initial_state, final_state,
                                      state_table, slot_stride, slots, has_initial, o, scratch, H, Hkv, normalize_qk, scale,
-                                     (cudaStream_t)stream);
+                                     snapshots, snap_offsets, snapshots ? snap_every_tokens / kScanC : 0, (cudaStream_t)stream);
+}
+
+extern "C" int atma_gated_delta_scan_varlen(const void* q, const void* k, const void* v, int dtype, const float* g,
+                                            const float* beta, const int32_t* cu_seqlens, int n_seqs,
+                                            int64_t total_tokens, const float* initial_state, float* final_state,
+                                            float* state_table, int64_t slot_stride, const int64_t* slots,
+                                            const int32_t* has_initial, void* o, void* scratch, int H, int Hkv, int dk,
+                                            int dv, int normalize_qk, float scale, void* stream) {
+  return scan_varlen_impl(q, k, v, dtype, g, beta, cu_seqlens, n_seqs, total_tokens, initial_state, final_state, state_table,
+                          slot_stride, slots, has_initial, o, scratch, H, Hkv, dk, dv, normalize_qk, scale, nullptr, nullptr, 0,
+                          stream);
+}
+
+extern "C" int atma_gated_delta_scan_varlen_snapshots(const void* q, const void* k, const void* v, int dtype, const float* g,
+                                                      const float* beta, const int32_t* cu_seqlens, int n_seqs,
+                                                      int64_t total_tokens, float* state_table, int64_t slot_stride,
+                                                      const int64_t* slots, const int32_t* has_initial, void* o,
+                                                      void* scratch, int H, int Hkv, int dk, int dv, int normalize_qk,
+                                                      float scale, float* snapshots, const int32_t* snap_offsets,
+                                                      int snap_every_tokens, void* stream) {
+  ATMA_REQUIRE(snapshots != nullptr, "gated_delta_scan_varlen_snapshots: the snapshot buffer is required");
+  return scan_varlen_impl(q, k, v, dtype, g, beta, cu_seqlens, n_seqs, total_tokens, nullptr, nullptr, state_table, slot_stride,
+                          slots, has_initial, o, scratch, H, Hkv, dk, dv, normalize_qk, scale, snapshots, snap_offsets,
+                          snap_every_tokens, stream);
 }
 
 extern "C" int64_t atma_gated_delta_scan_scratch_bytes(int B, int T, int H, int dk, int dv) {

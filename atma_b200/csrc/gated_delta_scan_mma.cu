@@ -46,6 +46,11 @@ struct VarLen {
   const int32_t* has_initial;  // device [n_seqs] or nullptr (= every sequence starts from its table row)
   float* state_table;          // [rows][H][dk][dv] fp32, or nullptr
   int64_t slot_stride;         // elements between table rows
+  // state snapshots for prefix reuse: after every snap_chunks chunks that lie wholly inside the
+  // sequence, the fp32 state goes to snapshots[snap_offsets[seq] + j] ([...][H][dk][dv]); nullptr = none
+  float* snapshots;
+  const int32_t* snap_offsets; // device [n_seqs]
+  int snap_chunks;
 };
 
 __global__ void varlen_chunk_offsets_kernel(const int32_t* __restrict__ cu_seqlens, int32_t* __restrict__ cu_chunks, int n_seqs) {
@@ -523,6 +528,22 @@ scan_seq_mma_kernel(const uint8_t* __restrict__ rec_base, const float* __restric
           *reinterpret_cast<uint32_t*>(Sb + tile_off(32 * warp + 16 * mt + gq + 8 * hh, 8 * nt + 2 * tq, NCOL)) =
               pack2<kBf16>(S[mt][nt][2 * hh], S[mt][nt][2 * hh + 1]);
     __syncthreads();                                           // stage s and Ub free; new Sb complete
+    if (packed && var.snapshots != nullptr) {                  // state after a whole page of tokens
+      const int done = c - c_begin + 1;
+      if (done % var.snap_chunks == 0 && tok_base + (int64_t)done * kC <= tok_end) {
+        float* snap = var.snapshots + (((int64_t)var.snap_offsets[b] + done / var.snap_chunks - 1) * H + h) * kD * kD +
+                      slice * NCOL;
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+              const int kr = 32 * warp + 16 * mt + gq + 8 * hh, col = 8 * nt + 2 * tq;
+              *reinterpret_cast<float2*>(snap + (int64_t)kr * kD + col) = make_float2(S[mt][nt][2 * hh], S[mt][nt][2 * hh + 1]);
+            }
+      }
+    }
   }
   cp_async_wait<0>();
   if (s_out) {
@@ -618,13 +639,14 @@ int gated_delta_scan_mma_varlen(const void* q, const void* k, const void* v, int
                                 const int32_t* cu_seqlens, int n_seqs, int64_t total_tokens, const float* initial_state,
                                 float* final_state, float* state_table, int64_t slot_stride, const int64_t* slots,
                                 const int32_t* has_initial, void* o, void* scratch, int H, int Hkv, int normalize_qk,
-                                float scale, cudaStream_t st) {
+                                float scale, float* snapshots, const int32_t* snap_offsets, int snap_chunks,
+                                cudaStream_t st) {
   const int NCu = (int)(total_tokens / kC) + n_seqs;          // upper bound on the chunk count
   uint8_t* recs = static_cast<uint8_t*>(scratch);
   float* gcs = gc_array(scratch, 1, H, NCu);
   int32_t* cu_chunks = reinterpret_cast<int32_t*>(recs + gated_delta_scan_mma_scratch_bytes(1, NCu * kC, H));
   varlen_chunk_offsets_kernel<<<1, 32, 0, st>>>(cu_seqlens, cu_chunks, n_seqs);
-  VarLen var{cu_seqlens, cu_chunks, n_seqs, slots, has_initial, state_table, slot_stride};
+  VarLen var{cu_seqlens, cu_chunks, n_seqs, slots, has_initial, state_table, slot_stride, snapshots, snap_offsets, snap_chunks};
   const int smemA = 3 * kC * kD * 2 + (kC * kAfLd + 4 * 16 * kTfLd) * 4 + (4 * kC + 4) * 4;   // 70.4 KB: three CTAs per SM
   const bool bf = dtype == ATMA_BF16;
   if (bf) {

@@ -66,7 +66,8 @@ def _varlen_supported(q, dk, dv):
 
 @torch.no_grad()
 def _scan_varlen(q, k, v, g, beta, cu_seqlens, scale, use_qk_l2norm_in_kernel, *, initial_state=None,
-                 want_final=False, state_table=None, slots=None, has_initial=None):
+                 want_final=False, state_table=None, slots=None, has_initial=None, snapshots=None,
+                 snapshot_offsets=None, snapshot_every=0):
     """Packed batch through one factor launch and one recurrence launch (16-bit, dk = dv = 128)."""
     lib = _lib.load()
     total, H, dk = q.shape
@@ -92,6 +93,14 @@ def _scan_varlen(q, k, v, g, beta, cu_seqlens, scale, use_qk_l2norm_in_kernel, *
             has_initial = has_initial.to(device=q.device, dtype=torch.int32).contiguous()
         slot_stride = state_table.stride(0)
     scratch = _scan_scratch(q.device, max(256, lib.atma_gated_delta_scan_varlen_scratch_bytes(total, n_seqs, H, dk, dv)))
+    if snapshots is not None:
+        off = snapshot_offsets.to(device=q.device, dtype=torch.int32).contiguous()
+        _lib.check(lib.atma_gated_delta_scan_varlen_snapshots(
+            _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.dtype_code(q), _lib.ptr(g), _lib.ptr(beta), _lib.ptr(cu), n_seqs,
+            total, _lib.ptr(state_table), slot_stride, _lib.ptr(slots), _lib.ptr(has_initial), _lib.ptr(o),
+            _lib.ptr(scratch), H, Hkv, dk, dv, 1 if use_qk_l2norm_in_kernel else 0, float(scale), _lib.ptr(snapshots),
+            _lib.ptr(off), int(snapshot_every), _lib.stream_ptr()))
+        return o, None
     _lib.check(lib.atma_gated_delta_scan_varlen(
         _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.dtype_code(q), _lib.ptr(g), _lib.ptr(beta), _lib.ptr(cu), n_seqs,
         total, _lib.ptr(initial_state), _lib.ptr(final), _lib.ptr(state_table), slot_stride, _lib.ptr(slots),
@@ -102,7 +111,7 @@ def _scan_varlen(q, k, v, g, beta, cu_seqlens, scale, use_qk_l2norm_in_kernel, *
 
 @torch.no_grad()
 def packed_gated_delta_prefill(q, k, v, g, beta, cu_seqlens, state_table, slots, has_initial=None, scale=1.0,
-                               use_qk_l2norm_in_kernel=True):
+                               use_qk_l2norm_in_kernel=True, snapshot_every=None, seqlens=None):
     """The memory branch of a packed (several sequences, one token axis) prefill in one call.
 
     The reference loops over the sequences, calls the scan once per sequence with that
@@ -113,9 +122,29 @@ def packed_gated_delta_prefill(q, k, v, g, beta, cu_seqlens, state_table, slots,
     q (total,H,dk); k, v (total,H or Hkv,d); g, beta (total,H); cu_seqlens (n+1,) int, on the
     host or the device; state_table (rows,H,dk,dv) fp32, updated IN PLACE at rows ``slots``
     (n,); has_initial (n,) bool/int or None (= every sequence continues from its row).
-    Returns o (total,H,dv) in q's dtype."""
+    Returns o (total,H,dv) in q's dtype.
+
+    ``snapshot_every`` (tokens, a multiple of 64 - e.g. the KV page size) with ``seqlens`` (host
+    list of the sequence lengths) also returns the memory state after every full page of each
+    sequence: (o, snapshots (n_pages_total, H, dk, dv) fp32, page_offsets list) where sequence
+    i's j-th page boundary is row page_offsets[i] + j.  With these a request that reuses cached
+    K/V pages can start its memory from the matching state instead of from zero
+    (16-bit inputs with dk = dv = 128 only)."""
     _lib.require_cuda(q, "packed_gated_delta_prefill")
     dk, dv = q.shape[-1], v.shape[-1]
+    if snapshot_every is not None:
+        if not _varlen_supported(q, dk, dv) or seqlens is None or snapshot_every % 64 != 0:
+            raise ValueError("state snapshots need 16-bit inputs with dk = dv = 128, the host-side seqlens and a "
+                             "spacing that is a multiple of 64 tokens")
+        counts = [int(n) // snapshot_every for n in seqlens]
+        offsets = [0]
+        for cnt in counts:
+            offsets.append(offsets[-1] + cnt)
+        snaps = torch.empty((max(offsets[-1], 1), q.shape[1], dk, dv), device=q.device, dtype=torch.float32)
+        o, _ = _scan_varlen(q, k, v, g, beta, cu_seqlens, scale, use_qk_l2norm_in_kernel, state_table=state_table,
+                            slots=slots, has_initial=has_initial, snapshots=snaps,
+                            snapshot_offsets=torch.tensor(offsets[:-1], dtype=torch.int32), snapshot_every=snapshot_every)
+        return o, snaps[:offsets[-1]], offsets[:-1]
     if _varlen_supported(q, dk, dv):
         o, _ = _scan_varlen(q, k, v, g, beta, cu_seqlens, scale, use_qk_l2norm_in_kernel, state_table=state_table,
                             slots=slots, has_initial=has_initial)

@@ -225,6 +225,22 @@ int atma_gated_delta_scan_varlen(const void* q, const void* k, const void* v, in
 int64_t atma_gated_delta_scan_varlen_scratch_bytes(int64_t total_tokens, int n_seqs, int H,
                                                    int dk, int dv);
 
+/* The packed prefill with state snapshots for prefix reuse (the reference's engine shares K/V
+ * pages across requests but restarts the memory state from zero, docs/inference.md:72-75,
+ * inference/models/atma.py:477-479; a state saved at page boundaries makes the reuse exact).
+ * As atma_gated_delta_scan_varlen with a state table, plus: after every snap_every_tokens tokens
+ * (a multiple of 64, e.g. the cache page size) that lie wholly inside sequence i, the fp32 state
+ * [H][dk][dv] is written to snapshots[snap_offsets[i] + j], j = 0, 1, ... (snap_offsets: DEVICE
+ * int32 [n_seqs]; the caller sizes snapshots as sum_i floor(len_i / snap_every_tokens) rows). */
+int atma_gated_delta_scan_varlen_snapshots(const void* q, const void* k, const void* v, int dtype,
+                                           const float* g, const float* beta,
+                                           const int32_t* cu_seqlens, int n_seqs, int64_t total_tokens,
+                                           float* state_table, int64_t slot_stride, const int64_t* slots,
+                                           const int32_t* has_initial, void* o, void* scratch,
+                                           int H, int Hkv, int dk, int dv, int normalize_qk, float scale,
+                                           float* snapshots, const int32_t* snap_offsets,
+                                           int snap_every_tokens, void* stream);
+
 /* ------------------------------------------------------------------------------------
  * Depthwise causal conv, one decode step, in place on a slot-indexed state table.
  * Replaces kernel/causal_conv1d_triton.py:17-42 behind causal_conv1d_decode_step (:46-63).

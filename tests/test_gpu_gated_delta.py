@@ -197,3 +197,37 @@ def test_packed_prefill_updates_the_slot_table_in_place():
                                                     beta=bc[None, a:b], scale=1.0, initial_state=expect[0][None],
                                                     output_final_state=True, use_qk_l2norm_in_kernel=True)
     assert torch.equal(o2[a:b], o_ref[0]) and torch.equal(table2[0], S_ref[0])
+
+
+def test_packed_prefill_state_snapshots_give_exact_prefix_reuse():
+    """Snapshots at every 256-token page boundary == the final state of a scan over exactly that prefix
+    (bit-identical: same kernels, same chunks), and a second request that shares the first two pages
+    and starts from the page-2 snapshot reproduces the outputs of the full-length scan."""
+    lens, H, Hkv, d, page = [700, 256, 90, 513], 8, 2, 128, 256
+    q, k, v, glog, beta, cu = _packed_inputs(lens, H, Hkv, d, torch.bfloat16, seed=31)
+    qc, kc, vc, gc, bc = q.cuda(), k.cuda(), v.cuda(), glog.cuda(), beta.cuda()
+    table = torch.zeros(5, H, d, d, device="cuda")
+    slots = torch.tensor([3, 1, 0, 4])
+    o, snaps, offs = atma_b200.packed_gated_delta_prefill(qc, kc, vc, gc, bc, cu, table, slots, snapshot_every=page,
+                                                         seqlens=lens)
+    assert offs == [0, 2, 3, 3] and snaps.shape == (5, H, d, d)
+    plain_table = torch.zeros_like(table)
+    o_plain = atma_b200.packed_gated_delta_prefill(qc, kc, vc, gc, bc, cu, plain_table, slots)
+    assert torch.equal(o, o_plain) and torch.equal(table, plain_table)       # snapshots do not disturb the scan
+    for i, n in enumerate(lens):
+        a = int(cu[i])
+        for j in range(n // page):
+            _, S_ref = atma_b200.chunk_gated_delta_rule(q=qc[None, a:a + (j + 1) * page], k=kc[None, a:a + (j + 1) * page],
+                                                        v=vc[None, a:a + (j + 1) * page], g=gc[None, a:a + (j + 1) * page],
+                                                        beta=bc[None, a:a + (j + 1) * page], scale=1.0,
+                                                        output_final_state=True, use_qk_l2norm_in_kernel=True)
+            assert torch.equal(snaps[offs[i] + j], S_ref[0]), (i, j)
+    # prefix reuse: sequence 0's tokens 512..699 scanned from the page-2 snapshot
+    a = int(cu[0])
+    table2 = torch.zeros_like(table)
+    table2[2] = snaps[offs[0] + 1]
+    tail = slice(a + 2 * page, a + lens[0])
+    o_tail = atma_b200.packed_gated_delta_prefill(qc[tail], kc[tail], vc[tail], gc[tail], bc[tail],
+                                                  torch.tensor([0, lens[0] - 2 * page], dtype=torch.int32), table2,
+                                                  torch.tensor([2]))
+    assert torch.equal(o_tail, o[tail]) and torch.equal(table2[2], table[3])
