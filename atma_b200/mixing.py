@@ -26,14 +26,23 @@ def _side_stream(device):
 
 @torch.no_grad()
 def global_layer_mixing(q, k, v, g, beta, n_keys, polar_params, *, window=None, initial_state=None,
-                        overlap=True, events=None):
+                        overlap=True, events=None, inputs_ready=None):
     """q (B,T,H,dk); k, v (B,T,Hkv,dk) post-conv, un-expanded KV heads; g (log decay), beta (B,T,H).
     Returns (c (B,H,T,dk), mag (B,H,T), o (B,T,H,dv), S (B,H,dk,dv)).  ``events`` = four CUDA events
-    recorded around the Polar kernel (on the current stream) and the scan (on its stream)."""
+    recorded around the Polar kernel (on the current stream) and the scan (on its stream).
+
+    ``inputs_ready``: a CUDA event after which the inputs are valid.  Without it the memory branch
+    waits for everything queued on the current stream so far - also for the previous step's
+    attention kernel when steps are issued back to back.  With it the branch waits for the event
+    only, so the recurrence of step i+1 runs under the tail of step i's attention kernel."""
     cur = torch.cuda.current_stream(q.device)
     side = _side_stream(q.device) if overlap else cur
     if overlap:
-        side.wait_stream(cur)
+        if inputs_ready is not None:
+            side.wait_event(inputs_ready)
+            cur.wait_event(inputs_ready)
+        else:
+            side.wait_stream(cur)
     with torch.cuda.stream(side):
         if events:
             events[2].record(side)
@@ -105,7 +114,8 @@ class HostFedMixing:
         with torch.cuda.stream(self.compute):
             self.compute.wait_event(arrived)
             c, mag, o, S = global_layer_mixing(dev["q"], dev["k"], dev["v"], dev["g"], dev["beta"], n_keys,
-                                               polar_params, window=window, initial_state=initial_state)
+                                               polar_params, window=window, initial_state=initial_state,
+                                               inputs_ready=arrived)
             computed = torch.cuda.Event()
             computed.record(self.compute)
         self.in_free[slot] = computed

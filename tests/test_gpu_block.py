@@ -144,3 +144,31 @@ def test_packed_global_attention_prefill_matches_oracle_per_sequence():
     for a, b in zip(conv_g, conv_ref):
         assert max_rel(a, b) < 2e-2
     assert max_rel(kc, kc_ref) < 2e-2 and max_rel(vc, vc_ref) < 2e-2
+
+
+@pytest.mark.gpu
+def test_mixing_steps_issued_back_to_back_with_an_inputs_ready_event():
+    """With ``inputs_ready`` the memory branch of a step may run under the previous step's attention
+    kernel; four steps on different inputs must still give exactly the results of isolated calls."""
+    from atma_b200.mixing import global_layer_mixing
+    dev = torch.device("cuda", 0)
+    B, T, H, Hkv, dk = 1, 2048, 8, 2, 128
+    params = dict(v_null=torch.zeros(H, dk, device=dev), null_base=torch.full((H,), -2.0, device=dev),
+                  null_slope_raw=torch.full((H,), -1.0, device=dev), len_gain_raw=torch.full((H,), -2.0, device=dev),
+                  mag_beta_raw=torch.full((H,), 0.5, device=dev))
+    n_keys = torch.arange(1, T + 1, dtype=torch.float32, device=dev)
+    gen = torch.Generator(device=dev).manual_seed(5)
+    steps = [dict(q=torch.randn(B, T, H, dk, device=dev, generator=gen).bfloat16(),
+                  k=torch.randn(B, T, Hkv, dk, device=dev, generator=gen).bfloat16(),
+                  v=torch.randn(B, T, Hkv, dk, device=dev, generator=gen).bfloat16(),
+                  g=torch.nn.functional.logsigmoid(torch.randn(B, T, H, device=dev, generator=gen) + 3.9),
+                  beta=torch.sigmoid(torch.randn(B, T, H, device=dev, generator=gen))) for _ in range(4)]
+    want = [global_layer_mixing(s["q"], s["k"], s["v"], s["g"], s["beta"], n_keys, params) for s in steps]
+    torch.cuda.synchronize()
+    ready = torch.cuda.Event()
+    ready.record()
+    got = [global_layer_mixing(s["q"], s["k"], s["v"], s["g"], s["beta"], n_keys, params, inputs_ready=ready) for s in steps]
+    torch.cuda.synchronize()
+    for a, b in zip(got, want):
+        for x, y in zip(a, b):
+            assert torch.equal(x, y)
