@@ -2,7 +2,7 @@
 
 Run once, in a container where the reference checkout is mounted:
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <path to the reference checkout>
 
 It imports the reference's own pure-PyTorch oracle on the CPU (model/blocks.py,
 model/reference.py, scripts/titans_proto.py and the CPU branches of
@@ -159,4 +159,6 @@ def main(ref_root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_golden.py <path to the reference checkout>")
+    main(sys.argv[1])
