@@ -6,24 +6,24 @@
 // (inference/models/atma.py:396-399,431-441,468-471; kernel/inference_ops_triton.py:139-160;
 // inference/layers/attention.py:30-56).
 //
-// One CTA = 32 tokens x up to eight heads (of q, or of k and v).  The tile, plus the K-1 rows
+// One CTA = 16 tokens x up to eight heads (of q, or of k and v).  The tile, plus the K-1 rows
 // before it, is staged in shared memory with 16-byte asynchronous copies (whole token rows, so
 // neighbouring DRAM pages).  A group of 16 threads x 8 channels then walks a run of consecutive
 // tokens of one head: each row is read from the tile once, normalised in registers (row sums by
 // shuffles), kept in a K-row register window for the taps, and q, k, v and the cache rows are
 // written once.  Runs that lie inside one sequence take a straight-line path without per-row
-// branches.  Two CTAs per SM keep ~140 KB of copies in flight; each projection element comes from
-// DRAM once (the K-1 halo rows of a tile are its neighbour's rows, i.e. cache hits) and every
-// output goes out once.
+// branches.  Four CTAs per SM (39 KB of shared memory, 128 registers each) overlap one tile's
+// copies with another's arithmetic; each projection element comes from DRAM once (the K-1 halo
+// rows of a tile are its neighbour's rows, i.e. cache hits) and every output goes out once.
 #include "common.cuh"
 
 namespace atma {
 
 namespace {
 
-constexpr int kPrepTok = 32;       // tokens per CTA
+constexpr int kPrepTok = 16;       // tokens per CTA
 constexpr int kPrepHeads = 8;      // heads per CTA (the rows of one token are neighbours in memory)
-constexpr int kPrepThreads = 256;
+constexpr int kPrepThreads = 128;   // 8 groups of 16 threads: eight heads x one run of 16 tokens
 constexpr int kPrepMaxK = 4;
 
 struct PrepArgs {
@@ -79,6 +79,17 @@ template <> __device__ __forceinline__ void store8<__half>(__half* p, const floa
   *reinterpret_cast<uint4*>(p) = u;
 }
 
+// round eight fp32 values through T and back, two per conversion instruction for the 16-bit types
+template <typename T> __device__ __forceinline__ void round8(float (&v)[8]) {
+  if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(__floats2bfloat162_rn(v[2 * i], v[2 * i + 1])); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+  } else if constexpr (std::is_same<T, __half>::value) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = __half22float2(__floats2half2_rn(v[2 * i], v[2 * i + 1])); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+  }
+}
+
 // 16-byte asynchronous copy global -> shared; src_bytes = 0 zero-fills the destination
 __device__ __forceinline__ void prep_cp_async16(void* smem_dst, const void* gsrc, bool valid) {
   const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
@@ -108,7 +119,8 @@ __device__ __forceinline__ void prep_plain_run(const T* trow, int row_elems, con
       for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(half_mask, ss, o, 16);
       const float rs = rsqrtf(ss * inv_dk + eps);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) x[j] = round_through<T>(x[j] * rs);                // the eager op rounds to T here
+      for (int j = 0; j < 8; ++j) x[j] *= rs;
+      round8<T>(x);                                              // the eager op rounds to T here
     }
     if (rl >= K - 1) {
       const int i = rl - (K - 1);
@@ -118,8 +130,11 @@ __device__ __forceinline__ void prep_plain_run(const T* trow, int row_elems, con
         float acc = 0.f;
 #pragma unroll
         for (int kk = 0; kk < K; ++kk) acc = fmaf(win[(rl - (K - 1) + kk) % K][j], wt[j][kk], acc);
-        y[j] = x[j] + round_through<T>(acc);                     // x + conv(x), the conv rounded as eager does
+        y[j] = acc;
       }
+      round8<T>(y);                                              // the conv rounded as eager does, then x + conv(x)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) y[j] += x[j];
       store8<T>(dst + i * dst_row, y);
       if (cs[i] >= 0) store8<T>(cache + cs[i] * cache_row, y);
     }
@@ -127,7 +142,7 @@ __device__ __forceinline__ void prep_plain_run(const T* trow, int row_elems, con
 }
 
 template <typename T, int K>
-__global__ void __launch_bounds__(kPrepThreads, 2)
+__global__ void __launch_bounds__(kPrepThreads, 4)
 qkv_prep_kernel(const PrepArgs a) {
   // shared tile: rows t0-(K-1) .. t0+kPrepTok-1 of the chunk's (up to 8) heads, [row][head][dk] in T
   extern __shared__ __align__(16) uint8_t prep_smem[];
@@ -189,7 +204,7 @@ qkv_prep_kernel(const PrepArgs a) {
   constexpr int kGroups = kPrepThreads / 16;
   const int gph = kGroups / nu;                                  // groups per head (2 with eight heads)
   const int ul = grp % nu, part = grp / nu;
-  const int tpg = (kPrepTok + gph - 1) / gph;                    // tokens per group (<= kPrepTok / 2)
+  const int tpg = (kPrepTok + gph - 1) / gph;                    // tokens per group (<= 16)
   const int i_begin = part * tpg, i_end = min(kPrepTok, i_begin + tpg);
   const int c = li * 8;
   const bool lane_on = c < dk;
@@ -217,7 +232,7 @@ qkv_prep_kernel(const PrepArgs a) {
 
   const T* trow = tile + i_begin * row_elems + ul * dk + c;      // tile row i_begin <-> token t0 + i_begin - (K-1)
   float win[K][8];
-  constexpr int kMaxRows = kPrepTok / 2 + K - 1;
+  constexpr int kMaxRows = kPrepTok + K - 1;
 
   // ---- fast path: a full run (16 tokens with eight heads per CTA, 8 with four) that lies inside one
   //      sequence, not at its start or end: straight-line code, so the rows' load -> reduce -> scale
