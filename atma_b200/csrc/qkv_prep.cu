@@ -362,6 +362,7 @@ extern "C" int atma_qkv_prep_prefill(const void* q_gate, int64_t qg_row_stride, 
                    (uintptr_t)k_cache % 16 == 0 && (uintptr_t)v_cache % 16 == 0,
                "qkv_prep_prefill: rows must be 16-byte aligned (pointers and strides in multiples of 8 elements)");
   ATMA_REQUIRE(K >= 2 && K <= kPrepMaxK, "qkv_prep_prefill: kernel size %d not in 2..4", K);
+  if (total <= 0) return ATMA_OK;
   ATMA_REQUIRE(token_seq_start && token_seq_end && token_seq_slot, "qkv_prep_prefill: the per-token sequence arrays are required");
   ATMA_REQUIRE((k_cache == nullptr) == (v_cache == nullptr), "qkv_prep_prefill: pass both caches or neither");
   ATMA_REQUIRE((init_q == nullptr || init_q != state_q) && (init_k == nullptr || init_k != state_k) &&

@@ -283,3 +283,23 @@ def test_lfm2_conv_packed_matches_the_op_by_op_oracle(dtype, continued):
         assert max_rel(got, want) < 8e-3 and (got.cpu() != want).float().mean() < 0.03
         assert torch.equal(tg.cpu(), ref_table)
     assert torch.equal(tg.cpu()[[2, 4]], table[[2, 4]])             # rows no sequence owns
+
+
+def test_empty_inputs_are_accepted_by_the_fused_entries():
+    """Zero tokens / zero rows: every fused entry returns an empty result and touches nothing."""
+    dev = "cuda"
+    bf = torch.bfloat16
+    z = lambda *s: torch.zeros(*s, dtype=bf, device=dev)
+    i32 = torch.zeros(0, dtype=torch.int32, device=dev)
+    st = [z(2, 512, 3), z(2, 256, 3), z(2, 256, 3)]
+    q, k, v = atma_b200.qkv_prep_prefill(z(0, 4, 256), z(0, 2, 128), z(0, 2, 128), z(512, 4), z(256, 4), z(256, 4), *st, i32, i32, i32)
+    assert q.shape == (0, 4, 128) and k.shape == (0, 2, 128) and v.shape == (0, 2, 128)
+    assert atma_b200.sigmoid_gate_mul(z(0, 4, 128), z(0, 4, 128)).shape == (0, 4, 128)
+    assert atma_b200.rms_sigmoid_gate(z(0, 4, 128), z(0, 512)).shape == (0, 512)
+    assert atma_b200.lfm2_conv_decode_step(z(0, 768), z(256, 3), torch.zeros(0, dtype=torch.long, device=dev), z(2, 256, 2)).shape == (0, 256)
+    assert atma_b200.lfm2_conv_packed(z(0, 768), z(256, 3), z(2, 256, 2), i32, i32, i32).shape == (0, 256)
+    table = torch.ones(2, 4, 128, 128, device=dev)
+    o = atma_b200.packed_gated_delta_prefill(z(0, 4, 128), z(0, 2, 128), z(0, 2, 128), torch.zeros(0, 4, device=dev),
+                                             torch.zeros(0, 4, device=dev), torch.zeros(1, dtype=torch.int32), table,
+                                             torch.zeros(0, dtype=torch.long))
+    assert o.shape == (0, 4, 128) and bool((table == 1).all())
