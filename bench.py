@@ -205,13 +205,37 @@ def bench_decode(ab, device, steps, warmup, peaks):
                                    gamma, beta, state, slots)
     e1.record()
     torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / steps
+    eager_ms = e0.elapsed_time(e1) / steps
     polar_ms = sum(a.elapsed_time(b) for a, b in pe) / steps
+    # the step as the engine runs it: captured once, replayed (inference/engine/model_runner.py:254-310)
+    ms, graphed = eager_ms, False
+    try:
+        side = torch.cuda.Stream(device=device)
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(side):
+            step()
+        torch.cuda.current_stream(device).wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step()
+        for _ in range(warmup):
+            graph.replay()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(steps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ms, graphed = e0.elapsed_time(e1) / steps, True
+        del graph
+    except Exception as exc:                                     # noqa: BLE001 - the eager timing stands
+        print(f"[bench] decode step not captured: {exc!r}", file=sys.stderr)
     kv_bytes = 2.0 * DEC_B * DEC_CTX * HKV * DK * 2
     state_bytes = 2.0 * DEC_B * H * DK * DK * 4
     return {
         "metric": "global_layer_decode_tok_s_at_b64_ctx32k", "value": DEC_B / (ms * 1e-3), "unit": "tok/s",
-        "ms_per_step": ms, "config": {"batch": DEC_B, "context": DEC_CTX, "block_size": DEC_BLOCK, "layers": 1},
+        "ms_per_step": ms, "ms_per_step_eager": eager_ms, "cuda_graph": graphed,
+        "config": {"batch": DEC_B, "context": DEC_CTX, "block_size": DEC_BLOCK, "layers": 1},
         "roofline": {"kernel": "polar_decode (split + merge)", "bound": "hbm",
                      "achieved": kv_bytes / (polar_ms * 1e-3) / 1e9, "peak": peaks["hbm"], "unit": "GB/s",
                      "frac": kv_bytes / (polar_ms * 1e-3) / 1e9 / peaks["hbm"],
