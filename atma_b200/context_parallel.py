@@ -324,13 +324,14 @@ GATHER_LIMIT_BYTES = 8 << 30
 
 
 @torch.no_grad()
-def cp_global_layer_prefill(shard, params, *, backend=None, group=None, overlap=None, polar_mode=None):
+def cp_global_layer_prefill(shard, params, *, backend=None, group=None, overlap=None, polar_mode=None, window=None):
     """Polar pass + gated-delta prefix scan for one rank's shard.  Returns
     ([(c, mag) lo, hi], [o lo, hi], final memory state).  On CUDA tensors the memory branch runs
     beside the attention on a side stream (``overlap``, default on for CUDA).  ``polar_mode``:
     "gather" (all-gather K/V, one launch per query segment), "ring" (K/V blocks travel a ring,
     2N+1 launches with carried statistics; memory per GPU stays O(T/N)), default: gather while
-    the whole sequence's K/V is below ``GATHER_LIMIT_BYTES``."""
+    the whole sequence's K/V is below ``GATHER_LIMIT_BYTES``.  ``window``: sliding-window attention
+    (keys older than ``window`` positions are masked, as in the reference's local Polar layers)."""
     tr = lambda x: x.transpose(1, 2)
     dev = shard.q[0].device
     if overlap is None:
@@ -350,7 +351,7 @@ def cp_global_layer_prefill(shard, params, *, backend=None, group=None, overlap=
         raise ValueError(f"polar_mode must be 'gather' or 'ring', not {polar_mode!r}")
     polar_fn = gathered_polar_prefill if polar_mode == "gather" else ring_polar_prefill
     polar = polar_fn([tr(x) for x in shard.q], [tr(x) for x in shard.k], [tr(x) for x in shard.v],
-                     shard.positions, params, backend=backend, group=group)
+                     shard.positions, params, backend=backend, group=group, window=window)
     if overlap:
         cur.wait_stream(side)
         for t in (*o, S):
@@ -373,10 +374,11 @@ class CapturedPrefill:
     overwritten by the next replay.
     """
 
-    def __init__(self, shard, params, *, group=None, warmup=3, polar_mode=None):
+    def __init__(self, shard, params, *, group=None, warmup=3, polar_mode=None, window=None):
         dev = shard.q[0].device
         self.group = group
         self.polar_mode = polar_mode
+        self.window = window
         self.static = GlobalLayerShard(positions=list(shard.positions),
                                        **{f: [x.clone() for x in getattr(shard, f)]
                                           for f in ("q", "k", "v", "g", "beta")})
@@ -385,7 +387,7 @@ class CapturedPrefill:
         side.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(side):                      # warm up off the default stream: lazy
             for _ in range(warmup):                        # initialisation must not land in the capture
-                cp_global_layer_prefill(self.static, params, group=group, polar_mode=polar_mode)
+                cp_global_layer_prefill(self.static, params, group=group, polar_mode=polar_mode, window=window)
         torch.cuda.current_stream(dev).wait_stream(side)
         torch.cuda.synchronize(dev)
         dist.barrier(group=group)
@@ -395,7 +397,7 @@ class CapturedPrefill:
         try:
             with torch.cuda.graph(self.graph, capture_error_mode="thread_local"):
                 try:
-                    self.outputs = cp_global_layer_prefill(self.static, params, group=group, polar_mode=polar_mode)
+                    self.outputs = cp_global_layer_prefill(self.static, params, group=group, polar_mode=polar_mode, window=window)
                 except Exception as inner:                 # noqa: BLE001 - keep the first error: ending the
                     self.error = inner                     # capture after it reports "unjoined work" instead
                     raise
@@ -427,7 +429,8 @@ class CapturedPrefill:
         if self.captured:
             self.graph.replay()
             return self.outputs
-        return cp_global_layer_prefill(self.static, self.params, group=self.group, polar_mode=self.polar_mode)
+        return cp_global_layer_prefill(self.static, self.params, group=self.group, polar_mode=self.polar_mode,
+                                       window=self.window)
 
 
 class HostFedCapturedPrefill:
@@ -442,10 +445,10 @@ class HostFedCapturedPrefill:
 
     FIELDS = ("q", "k", "v", "g", "beta")
 
-    def __init__(self, shard, params, *, group=None, polar_mode=None, depth=2):
+    def __init__(self, shard, params, *, group=None, polar_mode=None, depth=2, window=None):
         dev = shard.q[0].device
         self.device, self.depth = dev, depth
-        self.caps = [CapturedPrefill(shard, params, group=group, polar_mode=polar_mode) for _ in range(depth)]
+        self.caps = [CapturedPrefill(shard, params, group=group, polar_mode=polar_mode, window=window) for _ in range(depth)]
         self.copy_in, self.compute, self.copy_out = (torch.cuda.Stream(device=dev) for _ in range(3))
         self.in_free = [None] * depth
         self.out_done = [None] * depth

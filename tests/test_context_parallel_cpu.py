@@ -53,7 +53,7 @@ def _inputs(T, H, Hkv, dk):
     return t, params, x
 
 
-def _worker(rank, world, port, T, mode, ret):
+def _worker(rank, world, port, T, mode, window, ret):
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
@@ -61,7 +61,7 @@ def _worker(rank, world, port, T, mode, ret):
         H, Hkv, dk = 4, 2, 16
         t, params, x = _inputs(T, H, Hkv, dk)
         shard = cp.shard_sequence(t, rank, world)
-        polar, o, S = cp.cp_global_layer_prefill(shard, params, backend=OracleBackend(), polar_mode=mode)
+        polar, o, S = cp.cp_global_layer_prefill(shard, params, backend=OracleBackend(), polar_mode=mode, window=window)
         halos = cp.cp_conv_halos([x[a:b] for a, b in shard.positions], 4)
         ret[rank] = dict(pos=shard.positions, c=[p[0] for p in polar], mag=[p[1] for p in polar], o=o, S=S, halos=halos)
     finally:
@@ -76,17 +76,18 @@ def _free_port():
     return port
 
 
-@pytest.mark.parametrize("world,T,mode", [(2, 64, "ring"), (3, 96, "ring"), (2, 64, "gather"), (3, 96, "gather")])
-def test_context_parallel_matches_single_process(world, T, mode):
+@pytest.mark.parametrize("world,T,mode,window", [(2, 64, "ring", None), (3, 96, "ring", None), (2, 64, "gather", None),
+                                                 (3, 96, "gather", None), (2, 64, "ring", 20), (2, 64, "gather", 20)])
+def test_context_parallel_matches_single_process(world, T, mode, window):
     H, Hkv, dk = 4, 2, 16
     t, params, x = _inputs(T, H, Hkv, dk)
     n = torch.arange(1, T + 1, dtype=torch.float32)
-    c_ref, m_ref = oracle.polar_prefill_oracle(t["q"].transpose(1, 2), t["k"].transpose(1, 2), t["v"].transpose(1, 2), n, params)
+    c_ref, m_ref = oracle.polar_prefill_oracle(t["q"].transpose(1, 2), t["k"].transpose(1, 2), t["v"].transpose(1, 2), n, params, window=window)
     ke, ve = t["k"].repeat_interleave(H // Hkv, 2), t["v"].repeat_interleave(H // Hkv, 2)
     o_ref, S_ref = oracle.chunk_gated_delta_rule_oracle(t["q"], ke, ve, t["g"], t["beta"], chunk=8)
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_worker, args=(world, _free_port(), T, mode, ret), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), T, mode, window, ret), nprocs=world, join=True)
     assert len(ret) == world
     for rank in range(world):
         r = ret[rank]
