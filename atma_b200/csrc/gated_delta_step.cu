@@ -44,6 +44,16 @@ gated_delta_step_kernel(const T* __restrict__ q, const T* __restrict__ k, const 
     return;
   }
 
+  // the state slice first: its loads are in flight while q and k are normalised
+  float* sp = state + slot * state_ss + h * state_sh;
+  float4 S[kStepMaxRowsPerThread];
+#pragma unroll
+  for (int i = 0; i < kStepMaxRowsPerThread; ++i) {
+    const int row = rg + i * RSTRIDE;
+    S[i] = (row < dk && col_ok) ? *reinterpret_cast<const float4*>(sp + (int64_t)row * dv + col)
+                                : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+
   // q, k -> shared, with their L2 norms (F.normalize: x / max(||x||, eps))
   float qs = 0.f, ks = 0.f;
   for (int i = tid; i < dk; i += blockDim.x) {
@@ -65,14 +75,12 @@ gated_delta_step_kernel(const T* __restrict__ q, const T* __restrict__ k, const 
   const float qinv = s_norm[0], kinv = s_norm[1];
   const float gm = gamma[b * H + h], bt = beta[b * H + h];
 
-  float* sp = state + slot * state_ss + h * state_sh;
-  float4 S[kStepMaxRowsPerThread];
   float4 pred = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
   for (int i = 0; i < kStepMaxRowsPerThread; ++i) {
     const int row = rg + i * RSTRIDE;
     if (row < dk && col_ok) {
-      float4 s = *reinterpret_cast<const float4*>(sp + (int64_t)row * dv + col);
+      float4 s = S[i];
       s.x *= gm; s.y *= gm; s.z *= gm; s.w *= gm;
       const float kn = s_k[row] * kinv;
       pred.x = fmaf(kn, s.x, pred.x); pred.y = fmaf(kn, s.y, pred.y);
