@@ -95,3 +95,32 @@ def test_decode_split_heuristic():
     assert decode_num_splits(1, 2, 32768) == 31                             # under one wave: as many as allowed
     assert decode_num_splits(1, 2, 256) == 1
     assert decode_num_splits(4096, 2, 32768) == 1
+
+
+def test_compat_shim_resolves_the_reference_import_paths():
+    """With the shim installed the reference's own import statements (inference/models/atma.py:31-80,
+    model/blocks.py:24) resolve to this library's functions."""
+    import importlib
+    import sys
+    import atma_b200
+    from atma_b200 import compat
+    saved_path, saved_mods = list(sys.path), {k: v for k, v in sys.modules.items() if k.split(".")[0] in ("kernel", "fla")}
+    for k in saved_mods:
+        del sys.modules[k]
+    try:
+        compat.install()
+        pt = importlib.import_module("kernel.polar_triton")
+        assert pt.polar_attention_fwd is atma_b200.polar_attention_fwd and pt.polar_attention_decode is atma_b200.polar_attention_decode
+        assert pt.polar_attention_packed_fwd is atma_b200.polar_attention_packed_fwd and hasattr(pt, "HAS_TRITON")
+        assert importlib.import_module("kernel.gated_delta_triton").gated_delta_decode_step is atma_b200.gated_delta_decode_step
+        assert importlib.import_module("kernel.causal_conv1d_triton").causal_conv1d_decode_step is atma_b200.causal_conv1d_decode_step
+        ops = importlib.import_module("kernel.inference_ops_triton")
+        assert ops.squared_relu_gate is atma_b200.squared_relu_gate and ops.softcap_logits is atma_b200.softcap_logits
+        assert ops.packed_causal_conv1d is atma_b200.packed_causal_conv1d and ops.linear_head_rms is atma_b200.linear_head_rms
+        from fla.ops.gated_delta_rule import chunk_gated_delta_rule
+        assert chunk_gated_delta_rule is atma_b200.chunk_gated_delta_rule
+    finally:
+        sys.path[:] = saved_path
+        for k in [m for m in sys.modules if m.split(".")[0] in ("kernel", "fla")]:
+            del sys.modules[k]
+        sys.modules.update(saved_mods)
