@@ -40,7 +40,7 @@ DEC_B, DEC_CTX, DEC_BLOCK = 64, 32768, 256
 METRIC = "global_layer_prefill_tok_s_at_64k"
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) from the committed ncu captures of the
 # small --profile cases (profiles/polar_prefill_sm100_T16384.md, profiles/polar_decode_b16_ctx16384.md).
-PREFILL_TRAFFIC_T16K = 53.9e6
+PREFILL_TRAFFIC_64K = 336.0e6      # read 231 MB + write 105 MB, captured on the 64K launch itself
 DECODE_TRAFFIC_RATIO = 273.2 / 268.4
 
 
@@ -784,9 +784,9 @@ def main():
         "clocks": clocks,
         "roofline": {"kernel": "polar_prefill", "bound": "tensor", "achieved": achieved_tf, "peak": peak_tf,
                      "unit": "TFLOP/s", "frac": achieved_tf / peak_tf,
-                     # ncu capture at T=16384: 53.9 MB of DRAM traffic (inputs read once, most of the output
-                     # still in L2 when the kernel ends); scaled by the token count to this launch.
-                     "traffic": PREFILL_TRAFFIC_T16K * (T_PREFILL / 16384),
+                     # ncu capture of this very launch (dram__bytes_read.sum + dram__bytes_write.sum, one pass):
+                     # 336 MB = the algorithmic input and output bytes; other lengths scale by the token count.
+                     "traffic": PREFILL_TRAFFIC_64K * (T_PREFILL / 65536),
                      "algorithmic_flops": polar_flops(T_PREFILL), "kernel_ms": polar_ms,
                      "kernel_ms_alone": polar_iso_ms, "kernel_ms_alone_all": polar_iso_all,
                      # the timed region runs under the power cap (see clocks); against the seconds-long cuBLAS figure:
