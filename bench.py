@@ -38,8 +38,9 @@ H, HKV, DK, CHUNK = 8, 2, 128, 64
 T_PREFILL = 65536
 DEC_B, DEC_CTX, DEC_BLOCK = 64, 32768, 256
 METRIC = "global_layer_prefill_tok_s_at_64k"
-# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) from the committed ncu captures of the
-# small --profile cases (profiles/polar_prefill_sm100_T16384.md, profiles/polar_decode_b16_ctx16384.md).
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) from the committed ncu captures
+# (profiles/polar_prefill_sm100_T16384.md: the 64K launch itself; profiles/polar_decode_b16_ctx16384.md:
+# a small case, scaled by the cache bytes).
 PREFILL_TRAFFIC_64K = 336.0e6      # read 231 MB + write 105 MB, captured on the 64K launch itself
 DECODE_TRAFFIC_RATIO = 273.2 / 268.4
 
