@@ -39,10 +39,10 @@ T_PREFILL = 65536
 DEC_B, DEC_CTX, DEC_BLOCK = 64, 32768, 256
 METRIC = "global_layer_prefill_tok_s_at_64k"
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) from the committed ncu captures
-# (profiles/polar_prefill_sm100_T16384.md: the 64K launch itself; profiles/polar_decode_b16_ctx16384.md:
-# a small case, scaled by the cache bytes).
+# (profiles/polar_prefill_sm100_T16384.md and profiles/polar_decode_b16_ctx16384.md: the two DRAM counters
+# captured on the bench launches themselves).
 PREFILL_TRAFFIC_64K = 336.0e6      # read 231 MB + write 105 MB, captured on the 64K launch itself
-DECODE_TRAFFIC_RATIO = 273.2 / 268.4
+DECODE_TRAFFIC_RATIO = 2155.3 / 2147.5   # read 2147.8 MB + write 5.8-9.3 MB on the 64 x 32K launch itself
 
 
 def measured_peaks():
@@ -240,8 +240,8 @@ def bench_decode(ab, device, steps, warmup, peaks):
         "roofline": {"kernel": "polar_decode (split + merge)", "bound": "hbm",
                      "achieved": kv_bytes / (polar_ms * 1e-3) / 1e9, "peak": peaks["hbm"], "unit": "GB/s",
                      "frac": kv_bytes / (polar_ms * 1e-3) / 1e9 / peaks["hbm"],
-                     # ncu capture at B=16 x 16K context: 273.2 MB moved for 268.4 MB algorithmic (x1.018);
-                     # traffic is proportional to the cache bytes, so it is scaled to this launch.
+                     # ncu capture of the 64 x 32K launch (two DRAM counters, one pass): 2155 MB moved for 2147.5 MB
+                     # algorithmic; a sharded batch scales it by its cache bytes.
                      "traffic": kv_bytes * DECODE_TRAFFIC_RATIO,
                      "algorithmic_bytes": kv_bytes, "kernel_ms": polar_ms, "peak_source": peaks["source"]},
         "step_bytes": kv_bytes + state_bytes,
