@@ -21,6 +21,8 @@ from .conv import (causal_conv1d_prefill, causal_conv1d_step,
                    lfm2_conv_step_oracle, lfm2_conv_packed_oracle)
 from .elementwise import (squared_relu_gate_oracle, softcap_logits_oracle, linear_head_rms_oracle,
                           sigmoid_gate_mul_oracle, rms_sigmoid_gate_oracle)
+from .model import (block_oracle, model_oracle, lfm2_mix_oracle, memory_readout_oracle, polar_mix_oracle,
+                    mlp_oracle)
 
 __all__ = [
     "polar_params_host", "polar_materialized", "polar_streaming",
@@ -32,4 +34,5 @@ __all__ = [
     "store_kvcache_oracle",
     "squared_relu_gate_oracle", "softcap_logits_oracle", "linear_head_rms_oracle",
     "sigmoid_gate_mul_oracle", "rms_sigmoid_gate_oracle",
+    "block_oracle", "model_oracle", "lfm2_mix_oracle", "memory_readout_oracle", "polar_mix_oracle", "mlp_oracle",
 ]

@@ -153,6 +153,55 @@ def main(ref_root):
         y = blk(x)
     G["block"] = dict(x=x, y=y, state={k_: v_.detach().clone() for k_, v_ in blk.state_dict().items()})
 
+    # ---- seeded-weight cases: weights come from seeded_weights.py on both sides -------
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    import seeded_weights as sw
+    from model.config import AtmaConfig
+
+    # BASELINE config 1 at its own shape: one global block, hidden 1024, 8/2 heads of 128, T=2048
+    sd = sw.block_state(seed=0, dim=1024, head_dim=128, num_kv_heads=2)
+    blk = ref.Block(1024, attention=True, head_dim=128, num_kv_heads=2, attn_window=None,
+                    mem_enabled=True, mem_chunk=64, mem_kernel="torch")
+    blk.load_state_dict(sd, strict=True)
+    x = torch.randn(1, 2048, 1024, generator=torch.Generator().manual_seed(100))
+    with torch.no_grad():
+        y = blk(x)
+    rows = torch.cat([torch.arange(0, 8), torch.arange(60, 70), torch.arange(8, 2048, 29), torch.arange(2040, 2048)]).unique()
+    G["block_cfg1"] = dict(weight_seed=0, x_seed=100, rows=rows, y_rows=y[0, rows].clone(),
+                           y_absmax=y.abs().max(), y_sum=y.double().sum().float())
+
+    # local (LFM2 gated conv) mixing module and block, model/reference.py:31-49
+    sd = sw.block_state(seed=1, dim=96, head_dim=32, num_kv_heads=1, attention=False)
+    blk = ref.Block(96, attention=False)
+    blk.load_state_dict(sd, strict=True)
+    x = torch.randn(2, 21, 96, generator=torch.Generator().manual_seed(101))
+    with torch.no_grad():
+        G["lfm2"] = dict(weight_seed=1, x=x, mix=blk.attn(x), y=blk(x))
+
+    # memory branch with its read-out, model/blocks.py:463-490 (TitansMemory.forward, torch backend)
+    gen = torch.Generator().manual_seed(102)
+    dim, H, dk, T = 64, 2, 32, 150
+    sd = sw.attention_state(gen, dim, dk, 1, prefix="")
+    att = ref.PolarAttention(dim, head_dim=dk, num_kv_heads=1, mem_enabled=True, mem_chunk=64, mem_kernel="torch")
+    att.load_state_dict(sd, strict=True)
+    x = torch.randn(2, T, dim, generator=gen)
+    q_t, k_t, v_t = (torch.randn(2, H, T, dk, generator=gen) for _ in range(3))
+    with torch.no_grad():
+        out = att.mem(x, q_t, k_t, v_t)
+    G["mem_readout"] = dict(x=x, q=q_t, k=k_t, v=v_t, out=out,
+                            state={k_: v_.clone() for k_, v_ in sd.items() if k_.startswith("mem.")})
+
+    # a whole small model: 8 layers (2 global), model/reference.py:236-269
+    cfg = AtmaConfig(vocab_size=640, num_hidden_layers=8, hidden_size=256, head_dim=64, attn_window=None,
+                     mem_enabled=True, mem_chunk=64, mem_kernel="torch", attn_kernel="torch")
+    sd = sw.model_state(seed=7, vocab=640, layers=8, dim=256, head_dim=64, num_kv_heads=1)
+    model = ref.ReferenceModel(cfg)
+    model.load_state_dict(sd, strict=True)
+    ids = torch.randint(0, 640, (2, 90), generator=torch.Generator().manual_seed(103))
+    with torch.no_grad():
+        logits = model(ids)
+    G["model_small"] = dict(weight_seed=7, ids=ids, logits=logits)
+
     out = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden.pt")
     torch.save(G, out)
     print("wrote", out, os.path.getsize(out), "bytes;", len(G), "cases")

@@ -18,17 +18,6 @@ def test_global_block_matches_reference_fp32(golden):
     assert max_abs(y, g["y"]) < 1e-4
 
 
-def test_global_block_chunked_continuation(golden):
-    """Memory state carried across two calls == one call (the Polar part is checked elsewhere);
-    with the memory branch alone responsible for the difference this pins the state hand-over."""
-    g = golden["block"]
-    sd = {k: v.cuda() for k, v in g["state"].items()}
-    x = g["x"].cuda()
-    _, S_full = global_block_forward(x, sd, head_dim=32, num_kv_heads=2, return_state=True)
-    _, S_a = global_block_forward(x[:, :24], sd, head_dim=32, num_kv_heads=2, return_state=True)
-    assert S_full.shape == S_a.shape == (2, 4, 32, 32)
-
-
 @pytest.mark.gpu
 def test_host_fed_pipeline_matches_direct_calls():
     """Three steps through the three-stream pipeline (distinct inputs per step, result slots reused)
@@ -138,8 +127,8 @@ def test_packed_global_attention_prefill_matches_oracle_per_sequence():
                                           conv_states=conv_g, mem_state_table=mem_g, k_cache=kc, v_cache=vc,
                                           slot_mapping=sm.to(dev))
     torch.cuda.synchronize()
-    assert max_rel(out, out_ref) < 3e-2
-    assert max_rel(mem_g, mem_ref) < 3e-2
+    assert max_rel(out, out_ref) < 2e-2
+    assert max_rel(mem_g, mem_ref) < 2e-2
     assert torch.equal(mem_g[1].cpu(), mem0[1])                       # a row no sequence owns
     for a, b in zip(conv_g, conv_ref):
         assert max_rel(a, b) < 2e-2
