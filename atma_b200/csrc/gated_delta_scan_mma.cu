@@ -7,25 +7,19 @@
 // Kernel A (one CTA per chunk) forms K K^T and Q K^T with mma.sync, inverts the four 16x16
 // diagonal blocks of the unit lower triangular system in fp32 by substitution, and solves
 // (I + A) [-W | U0] = [-beta g K | beta V] block row by block row with mma.sync, feeding each
-// solved 16-row block back as an operand from registers; all factors go to scratch as 16-bit tiles.
-// Kernel B (one CTA per (recurrence, head, 32- or 64-column slice of S)) walks the chunks in order: the
-// fp32 state lives in the mma accumulators of its 4 warps for the whole sequence, a 16-bit copy
-// in shared memory serves as the B operand of the two state products, and the per-chunk factors
-// stream in through a 2-stage cp.async ring.  The recurrence is latency-bound, which is why it
-// uses warp-level mma (operands and results stay in the issuing warp's registers) rather than
-// the asynchronous tcgen05 path.
+// solved 16-row block back as an operand from registers; all factors go to scratch as 16-bit tiles
+// (U0 transposed, [v][s], the layout the recurrence kernel adds it in).
+// The recurrence over the chunks runs on the tcgen05 kernel of gated_delta_scan_sm100.cu.
 #include "common.cuh"
 #include "mma_sync.cuh"
+#include "gated_delta_scan.cuh"
 
 namespace atma {
 
 using namespace mma;
+using namespace scan;
 
 namespace {
-
-constexpr int kC = 64, kD = 128;
-constexpr int kRecW = 0, kRecQg = kC * kD * 2, kRecKt = 2 * kC * kD * 2, kRecU0 = 3 * kC * kD * 2,
-              kRecRq = 4 * kC * kD * 2, kRecBytes = 4 * kC * kD * 2 + kC * kC * 2;    // 73,728 B per chunk
 
 // ------------------------------------------------------------------------------------------------
 // Kernel A: chunk-local factors
@@ -35,23 +29,6 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
   asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
   return d;
 }
-
-// Packed ("varlen") batches: sequences of different lengths back to back in one token axis.  Chunks
-// never straddle sequences: sequence i owns chunk records cu_chunks[i] .. cu_chunks[i+1]-1.
-struct VarLen {
-  const int32_t* cu_seqlens;   // device [n_seqs + 1] token offsets; nullptr = dense (B, T) batch
-  const int32_t* cu_chunks;    // device [n_seqs + 1] chunk offsets (built by varlen_chunk_offsets_kernel)
-  int n_seqs;
-  const int64_t* slots;        // device [n_seqs] rows of state_table, or nullptr (dense state arrays)
-  const int32_t* has_initial;  // device [n_seqs] or nullptr (= every sequence starts from its table row)
-  float* state_table;          // [rows][H][dk][dv] fp32, or nullptr
-  int64_t slot_stride;         // elements between table rows
-  // state snapshots for prefix reuse: after every snap_chunks chunks that lie wholly inside the
-  // sequence, the fp32 state goes to snapshots[snap_offsets[seq] + j] ([...][H][dk][dv]); nullptr = none
-  float* snapshots;
-  const int32_t* snap_offsets; // device [n_seqs]
-  int snap_chunks;
-};
 
 __global__ void varlen_chunk_offsets_kernel(const int32_t* __restrict__ cu_seqlens, int32_t* __restrict__ cu_chunks, int n_seqs) {
   if (threadIdx.x == 0 && blockIdx.x == 0) {
@@ -330,233 +307,17 @@ scan_local_mma_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt) {
         const uint32_t lo = pack2<kBf16>(acc[nt][0], acc[nt][1]), hi = pack2<kBf16>(acc[nt][2], acc[nt][3]);
-        *reinterpret_cast<uint32_t*>(out + (16 * i + gq) * kD + cb + 8 * nt + 2 * tq) = lo;
-        *reinterpret_cast<uint32_t*>(out + (16 * i + gq + 8) * kD + cb + 8 * nt + 2 * tq) = hi;
-        if (i < 3) { xb[i][nt][0] = movmatrix_trans(lo); xb[i][nt][1] = movmatrix_trans(hi); }
-      }
-    }
-  }
-}
-
-// ------------------------------------------------------------------------------------------------
-// Kernel B: the recurrence over chunks
-// ------------------------------------------------------------------------------------------------
-struct RecMap {            // recurrence i walks the chunk records of batch entry rec[i];
-  int rec[16];             // zero_u0[i] != 0 replaces U0 by zero (the "v = 0" recurrence that
-  int zero_u0[16];         // yields a segment's state-transfer matrix)
-};
-
-template <int NCOL> struct SeqCfg {
-  static constexpr int kStage = 3 * kC * kD * 2 + kC * NCOL * 2 + kC * kC * 2;   // W, Qg, Kt, U0 slice, Rq
-  static constexpr int kSmem = 2 * kStage + kD * NCOL * 2 + kC * NCOL * 2;       // + S copy + U copy
-};
-
-template <bool kBf16, int NCOL>
-__global__ void __launch_bounds__(128)
-scan_seq_mma_kernel(const uint8_t* __restrict__ rec_base, const float* __restrict__ gc_base,
-                    const float* __restrict__ initial_state, uint16_t* __restrict__ o,
-                    float* __restrict__ final_state, int Tlen, int H, int NC, const RecMap map, const VarLen var) {
-  constexpr int NT = NCOL / 8, NP = NCOL / 16, CHN = NCOL / 8;
-  constexpr int kStage = SeqCfg<NCOL>::kStage;
-  extern __shared__ __align__(128) uint8_t sm[];
-  uint8_t* Sb = sm + 2 * kStage;                     // [128 k][NCOL v] 16-bit, swizzled
-  uint8_t* Ub = Sb + kD * NCOL * 2;                  // [64 s][NCOL v]
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int slice = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-  const bool packed = var.cu_seqlens != nullptr;
-  const int rb = packed ? 0 : map.rec[b];
-  const bool zero_u0 = packed ? false : map.zero_u0[b] != 0;
-  const int gq = lane >> 2, tq = lane & 3;
-  // chunk records [c_begin, c_end) and the tokens [tok_base, tok_end) they cover
-  const int c_begin = packed ? var.cu_chunks[b] : 0;
-  const int c_end = packed ? var.cu_chunks[b + 1] : NC;
-  const int64_t tok_base = packed ? (int64_t)var.cu_seqlens[b] : (int64_t)b * Tlen;
-  const int64_t tok_end = packed ? (int64_t)var.cu_seqlens[b + 1] : tok_base + Tlen;
-  const uint8_t* recs = rec_base + ((int64_t)rb * H + h) * NC * (int64_t)kRecBytes;
-  const float* gcs = gc_base + ((int64_t)rb * H + h) * NC;
-
-  auto stage_ptr = [&](int s) { return sm + s * kStage; };
-  auto load_stage = [&](int c, int s) {
-    const uint8_t* rec = recs + (int64_t)c * kRecBytes;
-    uint8_t* dst = stage_ptr(s);
-    for (int i = tid; i < 3 * kC * 16; i += 128) {             // W, Qg, Kt: three [64][128] tiles
-      const int tile = i / (kC * 16), r = (i >> 4) & 63, ch = i & 15;
-      cp_async16(smem_u32(dst) + tile * (kC * kD * 2) + tile_off(r, ch * 8, kD), rec + tile * (kC * kD * 2) + r * 256 + ch * 16, true);
-    }
-    for (int i = tid; i < kC * CHN; i += 128) {                // U0 columns [NCOL*slice, +NCOL)
-      const int r = i / CHN, ch = i % CHN;
-      cp_async16(smem_u32(dst) + 3 * kC * kD * 2 + tile_off(r, ch * 8, NCOL), rec + kRecU0 + r * 256 + slice * NCOL * 2 + ch * 16, !zero_u0);
-    }
-    for (int i = tid; i < kC * 8; i += 128) {                  // Rq
-      const int r = i >> 3, ch = i & 7;
-      cp_async16(smem_u32(dst) + 3 * kC * kD * 2 + kC * NCOL * 2 + tile_off(r, ch * 8, 64), rec + kRecRq + r * 128 + ch * 16, true);
-    }
-  };
-
-  // fp32 state: warp w owns rows k = 32w .. 32w+31 (two 16-row tiles) x NCOL columns
-  float S[2][NT][4];
-  const int64_t sbase = ((int64_t)b * H + h) * kD * kD + slice * NCOL;
-  // where the state comes from and goes to: dense (n, H, dk, dv) arrays, or rows of a slot-indexed table
-  const float* s_in = initial_state ? initial_state + sbase : nullptr;
-  float* s_out = final_state ? final_state + sbase : nullptr;
-  if (packed && var.state_table != nullptr) {
-    float* row = var.state_table + var.slots[b] * var.slot_stride + (int64_t)h * kD * kD + slice * NCOL;
-    s_in = (var.has_initial == nullptr || var.has_initial[b] != 0) ? row : nullptr;
-    s_out = row;
-  }
-#pragma unroll
-  for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
-        const int kr = 32 * warp + 16 * mt + gq + 8 * hh, col = 8 * nt + 2 * tq;
-        float2 v2 = make_float2(0.f, 0.f);
-        if (s_in) v2 = *reinterpret_cast<const float2*>(s_in + (int64_t)kr * kD + col);
-        S[mt][nt][2 * hh] = v2.x; S[mt][nt][2 * hh + 1] = v2.y;
-        *reinterpret_cast<uint32_t*>(Sb + tile_off(kr, col, NCOL)) = pack2<kBf16>(v2.x, v2.y);
-      }
-  if (c_begin < c_end) load_stage(c_begin, 0);
-  cp_async_commit();
-
-  int am, ak, bk, bn, tk, tm;
-  a_rowmajor_lane(lane, am, ak);
-  b_kn_lane(lane, bk, bn);
-  a_km_lane(lane, tk, tm);
-
-  for (int c = c_begin; c < c_end; ++c) {
-    const int s = (c - c_begin) & 1;
-    if (c + 1 < c_end) load_stage(c + 1, s ^ 1);
-    cp_async_commit();
-    cp_async_wait<1>();
-    __syncthreads();                                           // stage s landed; Sb from the previous chunk visible
-    const uint32_t Wsm = smem_u32(stage_ptr(s)), Qsm = Wsm + kC * kD * 2, Ksm = Qsm + kC * kD * 2;
-    const uint8_t* U0s = stage_ptr(s) + 3 * kC * kD * 2;
-    const uint32_t Rsm = Wsm + 3 * kC * kD * 2 + kC * NCOL * 2;
-    const float gC = gcs[c];
-
-    // U = U0 - W S ; O = Qg S   (rows 16w..16w+15 of the chunk)
-    float U[NT][4], O[NT][4];
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-#pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
-        const float2 u2 = unpack2<kBf16>(*reinterpret_cast<const uint32_t*>(U0s + tile_off(16 * warp + gq + 8 * hh, 8 * nt + 2 * tq, NCOL)));
-        U[nt][2 * hh] = u2.x; U[nt][2 * hh + 1] = u2.y;
-        O[nt][2 * hh] = 0.f; O[nt][2 * hh + 1] = 0.f;
-      }
-    }
-#pragma unroll
-    for (int ks = 0; ks < 8; ++ks) {
-      uint32_t aw[4], aq[4];
-      ldsm_x4(Wsm + tile_off(16 * warp + am, 16 * ks + ak, kD), aw);
-      ldsm_x4(Qsm + tile_off(16 * warp + am, 16 * ks + ak, kD), aq);
-#pragma unroll
-      for (int pr = 0; pr < NP; ++pr) {
-        uint32_t bf[4];
-        ldsm_x4_trans(smem_u32(Sb) + tile_off(16 * ks + bk, 16 * pr + bn, NCOL), bf);
-        mma16816<kBf16>(U[2 * pr], aw, bf[0], bf[1]);
-        mma16816<kBf16>(U[2 * pr + 1], aw, bf[2], bf[3]);
-        mma16816<kBf16>(O[2 * pr], aq, bf[0], bf[1]);
-        mma16816<kBf16>(O[2 * pr + 1], aq, bf[2], bf[3]);
-      }
-    }
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-      *reinterpret_cast<uint32_t*>(Ub + tile_off(16 * warp + gq, 8 * nt + 2 * tq, NCOL)) = pack2<kBf16>(U[nt][0], U[nt][1]);
-      *reinterpret_cast<uint32_t*>(Ub + tile_off(16 * warp + gq + 8, 8 * nt + 2 * tq, NCOL)) = pack2<kBf16>(U[nt][2], U[nt][3]);
-    }
-    __syncthreads();                                           // U of every warp visible; all reads of Sb done
-
-    // O += Rq U  (s <= 16w+15 -> k-steps 0..w) and store
-    if (o != nullptr) {
-#pragma unroll
-      for (int ks = 0; ks < 4; ++ks) {
-        if (ks <= warp) {
-          uint32_t ar[4];
-          ldsm_x4(Rsm + tile_off(16 * warp + am, 16 * ks + ak, 64), ar);
-#pragma unroll
-          for (int pr = 0; pr < NP; ++pr) {
-            uint32_t bf[4];
-            ldsm_x4_trans(smem_u32(Ub) + tile_off(16 * ks + bk, 16 * pr + bn, NCOL), bf);
-            mma16816<kBf16>(O[2 * pr], ar, bf[0], bf[1]);
-            mma16816<kBf16>(O[2 * pr + 1], ar, bf[2], bf[3]);
-          }
+        const uint32_t lo_t = movmatrix_trans(lo), hi_t = movmatrix_trans(hi);
+        if (which) {                                             // U0 goes out transposed, [v][s]
+          *reinterpret_cast<uint32_t*>(out + (cb + 8 * nt + gq) * kC + 16 * i + 2 * tq) = lo_t;
+          *reinterpret_cast<uint32_t*>(out + (cb + 8 * nt + gq) * kC + 16 * i + 8 + 2 * tq) = hi_t;
+        } else {
+          *reinterpret_cast<uint32_t*>(out + (16 * i + gq) * kD + cb + 8 * nt + 2 * tq) = lo;
+          *reinterpret_cast<uint32_t*>(out + (16 * i + gq + 8) * kD + cb + 8 * nt + 2 * tq) = hi;
         }
-      }
-#pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
-        const int64_t t = tok_base + (int64_t)(c - c_begin) * kC + 16 * warp + gq + 8 * hh;
-        if (t < tok_end) {
-          uint16_t* orow = o + (t * H + h) * kD + slice * NCOL;
-#pragma unroll
-          for (int nt = 0; nt < NT; ++nt)
-            *reinterpret_cast<uint32_t*>(orow + 8 * nt + 2 * tq) = pack2<kBf16>(O[nt][2 * hh], O[nt][2 * hh + 1]);
-        }
+        if (i < 3) { xb[i][nt][0] = lo_t; xb[i][nt][1] = hi_t; }
       }
     }
-
-    // S <- gC S + Kt^T U   (rows k = 32w.., A = Kt^T from the [s][k] tile with a transposing load)
-#pragma unroll
-    for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-      for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) S[mt][nt][e] *= gC;
-#pragma unroll
-    for (int ks = 0; ks < 4; ++ks) {
-      uint32_t bfr[NP][4];
-#pragma unroll
-      for (int pr = 0; pr < NP; ++pr) ldsm_x4_trans(smem_u32(Ub) + tile_off(16 * ks + bk, 16 * pr + bn, NCOL), bfr[pr]);
-#pragma unroll
-      for (int mt = 0; mt < 2; ++mt) {
-        uint32_t at[4];
-        ldsm_x4_trans(Ksm + tile_off(16 * ks + tk, 32 * warp + 16 * mt + tm, kD), at);
-#pragma unroll
-        for (int pr = 0; pr < NP; ++pr) {
-          mma16816<kBf16>(S[mt][2 * pr], at, bfr[pr][0], bfr[pr][1]);
-          mma16816<kBf16>(S[mt][2 * pr + 1], at, bfr[pr][2], bfr[pr][3]);
-        }
-      }
-    }
-#pragma unroll
-    for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-      for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-        for (int hh = 0; hh < 2; ++hh)
-          *reinterpret_cast<uint32_t*>(Sb + tile_off(32 * warp + 16 * mt + gq + 8 * hh, 8 * nt + 2 * tq, NCOL)) =
-              pack2<kBf16>(S[mt][nt][2 * hh], S[mt][nt][2 * hh + 1]);
-    __syncthreads();                                           // stage s and Ub free; new Sb complete
-    if (packed && var.snapshots != nullptr) {                  // state after a whole page of tokens
-      const int done = c - c_begin + 1;
-      if (done % var.snap_chunks == 0 && tok_base + (int64_t)done * kC <= tok_end) {
-        float* snap = var.snapshots + (((int64_t)var.snap_offsets[b] + done / var.snap_chunks - 1) * H + h) * kD * kD +
-                      slice * NCOL;
-#pragma unroll
-        for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-          for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-              const int kr = 32 * warp + 16 * mt + gq + 8 * hh, col = 8 * nt + 2 * tq;
-              *reinterpret_cast<float2*>(snap + (int64_t)kr * kD + col) = make_float2(S[mt][nt][2 * hh], S[mt][nt][2 * hh + 1]);
-            }
-      }
-    }
-  }
-  cp_async_wait<0>();
-  if (s_out) {
-#pragma unroll
-    for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-      for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-          const int kr = 32 * warp + 16 * mt + gq + 8 * hh, col = 8 * nt + 2 * tq;
-          *reinterpret_cast<float2*>(s_out + (int64_t)kr * kD + col) =
-              make_float2(S[mt][nt][2 * hh], S[mt][nt][2 * hh + 1]);
-        }
   }
 }
 
@@ -601,31 +362,19 @@ int gated_delta_scan_mma_recur(void* scratch, int dtype, int B, int T, int H, in
                                const int* zero_u0, const float* initial_state, void* o, float* final_state,
                                cudaStream_t st) {
   const int NC = (T + kC - 1) / kC;
-  if (n_rec < 1 || n_rec > 16) return fail(ATMA_ERR_INVALID, "gated_delta_scan_recur: n_rec=%d outside 1..16", n_rec);
+  if (n_rec < 1 || n_rec > kMaxRec) return fail(ATMA_ERR_INVALID, "gated_delta_scan_recur: n_rec=%d outside 1..%d", n_rec, kMaxRec);
   RecMap map{};
   for (int i = 0; i < n_rec; ++i) {
     map.rec[i] = rec_of ? rec_of[i] : i;
     map.zero_u0[i] = zero_u0 ? zero_u0[i] : 0;
+    map.o_row[i] = i;
     if (map.rec[i] < 0 || map.rec[i] >= B)
       return fail(ATMA_ERR_INVALID, "gated_delta_scan_recur: rec_of[%d]=%d outside the %d factor sets", i, map.rec[i], B);
   }
   const uint8_t* recs = static_cast<const uint8_t*>(scratch);
   const float* gcs = gc_array(scratch, B, H, NC);
-  const bool bf = dtype == ATMA_BF16;
-  // one CTA per SM: 32-column slices (4 CTAs per head) shorten the per-chunk critical path as long
-  // as the whole grid still fits one wave
-  const bool narrow = (int64_t)n_rec * H * 4 <= 148;
-#define ATMA_LAUNCH(BF, NCOL)                                                                                     \
-  do {                                                                                                            \
-    auto kern = scan_seq_mma_kernel<BF, NCOL>;                                                                    \
-    ATMA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SeqCfg<NCOL>::kSmem));   \
-    kern<<<dim3(kD / NCOL, H, n_rec), 128, SeqCfg<NCOL>::kSmem, st>>>(recs, gcs, initial_state, (uint16_t*)o,     \
-                                                                       final_state, T, H, NC, map, VarLen{});     \
-  } while (0)
-  if (bf) { if (narrow) ATMA_LAUNCH(true, 32); else ATMA_LAUNCH(true, 64); }
-  else { if (narrow) ATMA_LAUNCH(false, 32); else ATMA_LAUNCH(false, 64); }
-#undef ATMA_LAUNCH
-  return launch_status("gated_delta_scan (recurrence, mma)");
+  return gated_delta_recur_sm100(recs, gcs, dtype == ATMA_BF16, (int64_t)B * H * NC, initial_state, o, final_state, T, H, NC,
+                                 n_rec, map, VarLen{}, st);
 }
 
 // Packed batch: chunk offsets, factors of every chunk, one recurrence per sequence, all in one go.
@@ -660,19 +409,8 @@ int gated_delta_scan_mma_varlen(const void* q, const void* k, const void* v, int
   }
   int rc = launch_status("gated_delta_scan (packed, chunk-local, mma)");
   if (rc != ATMA_OK) return rc;
-  const bool narrow = (int64_t)n_seqs * H * 4 <= 148;
-  RecMap map{};
-#define ATMA_LAUNCH(BF, NCOL)                                                                                     \
-  do {                                                                                                            \
-    auto kern = scan_seq_mma_kernel<BF, NCOL>;                                                                    \
-    ATMA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SeqCfg<NCOL>::kSmem));   \
-    kern<<<dim3(kD / NCOL, H, n_seqs), 128, SeqCfg<NCOL>::kSmem, st>>>(recs, gcs, initial_state, (uint16_t*)o,    \
-                                                                        final_state, 0, H, NCu, map, var);        \
-  } while (0)
-  if (bf) { if (narrow) ATMA_LAUNCH(true, 32); else ATMA_LAUNCH(true, 64); }
-  else { if (narrow) ATMA_LAUNCH(false, 32); else ATMA_LAUNCH(false, 64); }
-#undef ATMA_LAUNCH
-  return launch_status("gated_delta_scan (packed, recurrence, mma)");
+  return gated_delta_recur_sm100(recs, gcs, bf, (int64_t)H * NCu, initial_state, o, final_state, 0, H, NCu, n_seqs, RecMap{}, var,
+                                 st);
 }
 
 int gated_delta_scan_mma(const void* q, const void* k, const void* v, int dtype, const float* g, const float* beta,
@@ -681,9 +419,9 @@ int gated_delta_scan_mma(const void* q, const void* k, const void* v, int dtype,
   int rc = gated_delta_scan_mma_factors(q, k, v, dtype, g, beta, scratch, B, T, H, Hkv, normalize_qk, scale, st);
   if (rc != ATMA_OK) return rc;
   int done = 0;
-  while (done < B) {                                  // at most 16 recurrences per launch
-    const int n = (B - done) < 16 ? (B - done) : 16;
-    int rec_of[16];
+  while (done < B) {                                  // at most kMaxRec recurrences per launch
+    const int n = (B - done) < kMaxRec ? (B - done) : kMaxRec;
+    int rec_of[kMaxRec];
     for (int i = 0; i < n; ++i) rec_of[i] = done + i;
     const int64_t so = (int64_t)done * H * kD * kD, oo = (int64_t)done * T * H * kD;
     rc = gated_delta_scan_mma_recur(scratch, dtype, B, T, H, n, rec_of, nullptr,

@@ -25,6 +25,7 @@
 // status word for the host.
 #include "polar_prefill.cuh"
 #include "sm100.cuh"
+#include "gated_delta_scan.cuh"
 
 namespace atma {
 
@@ -603,5 +604,9 @@ int sm100_status_fetch_and_clear(int* out) {
 // the device; clears the flag).
 extern "C" int atma_device_status(int* status) {
   ATMA_REQUIRE(status != nullptr, "device_status: null out pointer");
-  return atma::sm100_status_fetch_and_clear(status);
+  int a = 0, b = 0;
+  int rc = atma::sm100_status_fetch_and_clear(&a);
+  if (rc == ATMA_OK) rc = atma::scan_sm100_status_fetch_and_clear(&b);
+  *status = a | b;
+  return rc;
 }
