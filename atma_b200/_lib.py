@@ -71,6 +71,9 @@ _SIGNATURES = {
     "atma_gated_delta_scan": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                       c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                       c_int, c_float, c_void_p]),
+    "atma_gated_delta_scan_segmented": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                                c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                c_int, c_float, c_int, c_void_p]),
     "atma_gated_delta_scan_factors": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                               c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]),
     "atma_gated_delta_scan_recur": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,

@@ -221,7 +221,7 @@ bool gated_delta_scan_mma_supported(int dtype, int dk, int dv);
 int64_t gated_delta_scan_mma_scratch_bytes(int B, int T, int H);
 int gated_delta_scan_mma(const void* q, const void* k, const void* v, int dtype, const float* g, const float* beta,
                          const float* initial_state, void* o, float* final_state, void* scratch, int B, int T, int H,
-                         int Hkv, int normalize_qk, float scale, cudaStream_t st);
+                         int Hkv, int normalize_qk, float scale, int segments, cudaStream_t st);
 
 int gated_delta_scan_mma_factors(const void* q, const void* k, const void* v, int dtype, const float* g,
                                  const float* beta, void* scratch, int B, int T, int H, int Hkv, int normalize_qk,
@@ -329,6 +329,16 @@ extern "C" int atma_gated_delta_scan(const void* q, const void* k, const void* v
                                      void* o, float* final_state, void* scratch, int B, int T, int H,
                                      int Hkv, int dk, int dv, int normalize_qk, float scale,
                                      void* stream) {
+  return atma_gated_delta_scan_segmented(q, k, v, dtype, g, beta, initial_state, o, final_state, scratch, B, T, H, Hkv, dk, dv,
+                                         normalize_qk, scale, 0, stream);
+}
+
+extern "C" int atma_gated_delta_scan_segmented(const void* q, const void* k, const void* v, int dtype,
+                                               const float* g, const float* beta, const float* initial_state,
+                                               void* o, float* final_state, void* scratch, int B, int T, int H,
+                                               int Hkv, int dk, int dv, int normalize_qk, float scale,
+                                               int segments, void* stream) {
+  ATMA_REQUIRE(segments >= 0 && segments <= 16, "gated_delta_scan: segments=%d outside 0..16", segments);
   ATMA_REQUIRE(dtype_ok(dtype), "gated_delta_scan: unsupported dtype %d", dtype);
   ATMA_REQUIRE(dk >= 1 && dk <= 128 && dv >= 1 && dv <= 128, "gated_delta_scan: dk=%d dv=%d outside 1..128", dk, dv);
   ATMA_REQUIRE(B >= 0 && T >= 0 && H > 0, "gated_delta_scan: bad shape");
@@ -347,7 +357,7 @@ extern "C" int atma_gated_delta_scan(const void* q, const void* k, const void* v
   if (gated_delta_scan_mma_supported(dtype, dk, dv) && ((uintptr_t)q % 16 == 0) && ((uintptr_t)k % 16 == 0) &&
       ((uintptr_t)v % 16 == 0) && ((uintptr_t)scratch % 256 == 0))
     return gated_delta_scan_mma(q, k, v, dtype, g, beta, initial_state, o, final_state, scratch, B, T, H, Hkv,
-                                normalize_qk, scale, st);
+                                normalize_qk, scale, segments, st);
   const int NC = (T + kScanC - 1) / kScanC;
   const int ldq = (dk > dv ? dk : dv) + 1;
   const size_t smem1 = sizeof(float) * ((size_t)kScanC * (dk + 1) + (size_t)kScanC * ldq +

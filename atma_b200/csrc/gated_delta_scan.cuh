@@ -39,6 +39,7 @@ struct RecMap {                 // recurrence i walks the chunk records of batch
   int c_begin[kMaxRec];         // chunk range [c_begin, c_end) of the records that recurrence i walks
   int c_end[kMaxRec];           // (c_end = 0 means "all NC chunks")
   int o_row[kMaxRec];           // batch row of the output tensor that recurrence i writes
+  int state_row[kMaxRec];       // plane of initial_state / final_state that recurrence i reads / writes
 };
 
 }  // namespace scan
@@ -50,5 +51,13 @@ int gated_delta_recur_sm100(const uint8_t* recs, const float* gcs, int is_bf16, 
                             void* o, float* final_state, int Tlen, int H, int NC, int n_rec, const scan::RecMap& map,
                             const scan::VarLen& var, cudaStream_t st);
 int scan_sm100_status_fetch_and_clear(int* out);
+
+// Chunk-local factors on the 5th-generation tensor cores (gated_delta_local_sm100.cu): q (tokens, H, 128),
+// k, v (tokens, Hkv, 128) contiguous 16-bit; g, beta (tokens, H) fp32; records and g_C as laid out above.
+// Dense form: B sequences of Tlen tokens (NC chunks each); packed form: var.cu_seqlens / cu_chunks.
+int gated_delta_local_sm100(const void* q, const void* k, const void* v, int is_bf16, const float* g, const float* beta,
+                            uint8_t* recs, float* gcs, int B, int Tlen, int H, int Hkv, int NC, int normalize_qk, float scale,
+                            const scan::VarLen& var, int64_t total_tokens, cudaStream_t st);
+int scan_local_status_fetch_and_clear(int* out);
 
 }  // namespace atma

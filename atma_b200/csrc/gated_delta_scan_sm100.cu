@@ -229,7 +229,8 @@ scan_recur_sm100_kernel(const __grid_constant__ CUtensorMap tmap_rec, const __gr
     const uint32_t lane_base = tbase + (uint32_t(32 * quad) << 16);
 
     // where the state comes from and goes to: element (k, v) of the [dk][dv] plane, k = 64*half + j
-    const int64_t sbase = ((int64_t)b * p.H + h) * kD * kD + (int64_t)(64 * half) * kD + row;
+    const int srow = packed ? b : p.map.state_row[b];
+    const int64_t sbase = ((int64_t)srow * p.H + h) * kD * kD + (int64_t)(64 * half) * kD + row;
     const float* s_in = p.initial_state ? p.initial_state + sbase : nullptr;
     float* s_out = p.final_state ? p.final_state + sbase : nullptr;
     if (packed && p.var.state_table != nullptr) {

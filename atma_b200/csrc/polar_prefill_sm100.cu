@@ -604,9 +604,10 @@ int sm100_status_fetch_and_clear(int* out) {
 // the device; clears the flag).
 extern "C" int atma_device_status(int* status) {
   ATMA_REQUIRE(status != nullptr, "device_status: null out pointer");
-  int a = 0, b = 0;
+  int a = 0, b = 0, c = 0;
   int rc = atma::sm100_status_fetch_and_clear(&a);
   if (rc == ATMA_OK) rc = atma::scan_sm100_status_fetch_and_clear(&b);
-  *status = a | b;
+  if (rc == ATMA_OK) rc = atma::scan_local_status_fetch_and_clear(&c);
+  *status = a | b | c;
   return rc;
 }

@@ -171,7 +171,7 @@ def packed_gated_delta_prefill(q, k, v, g, beta, cu_seqlens, state_table, slots,
 @torch.no_grad()
 def chunk_gated_delta_rule(q=None, k=None, v=None, g=None, beta=None, scale=None,
                            initial_state=None, output_final_state=False,
-                           use_qk_l2norm_in_kernel=False, cu_seqlens=None, **unused):
+                           use_qk_l2norm_in_kernel=False, cu_seqlens=None, segments=None, **unused):
     """Chunked gated-delta scan.  q (B,T,H,dk); k (B,T,H or Hkv,dk), v (B,T,H or Hkv,dv) - the
     un-expanded KV heads are accepted, head h then reads KV head h // (H // Hkv); g (B,T,H) log-decay (<= 0);
     beta (B,T,H); initial_state (B,H,dk,dv) fp32 or None.  Returns (o (B,T,H,dv) in q's dtype,
@@ -179,7 +179,11 @@ def chunk_gated_delta_rule(q=None, k=None, v=None, g=None, beta=None, scale=None
     flash-linear-attention; the reference always passes 1.0.
 
     ``cu_seqlens`` (n+1,) as in flash-linear-attention: the batch axis must be 1 and the token
-    axis holds n sequences back to back; initial_state / final_state are then (n,H,dk,dv)."""
+    axis holds n sequences back to back; initial_state / final_state are then (n,H,dk,dv).
+
+    ``segments`` (not in the reference's call): how many pieces each sequence is cut into along T so
+    that a batch of few sequences still fills the GPU (None = chosen from the shapes, 1 = single pass,
+    which is the least total work and what a caller running the scan beside other kernels wants)."""
     _lib.require_cuda(q, "chunk_gated_delta_rule")
     lib = _lib.load()
     B, T, H, dk = q.shape
@@ -217,10 +221,11 @@ def chunk_gated_delta_rule(q=None, k=None, v=None, g=None, beta=None, scale=None
     o = torch.empty((B, T, H, dv), device=q.device, dtype=q.dtype)
     final = torch.empty((B, H, dk, dv), device=q.device, dtype=torch.float32) if output_final_state else None
     scratch = _scan_scratch(q.device, max(16, lib.atma_gated_delta_scan_scratch_bytes(B, T, H, dk, dv)))
-    _lib.check(lib.atma_gated_delta_scan(
+    _lib.check(lib.atma_gated_delta_scan_segmented(
         _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.dtype_code(q), _lib.ptr(g), _lib.ptr(beta),
         _lib.ptr(initial_state), _lib.ptr(o), _lib.ptr(final), _lib.ptr(scratch),
-        B, T, H, Hkv, dk, dv, 1 if use_qk_l2norm_in_kernel else 0, float(scale), _lib.stream_ptr()))
+        B, T, H, Hkv, dk, dv, 1 if use_qk_l2norm_in_kernel else 0, float(scale),
+        0 if segments is None else int(segments), _lib.stream_ptr()))
     return o, final
 
 
@@ -251,7 +256,7 @@ def scan_factors(q, k, v, g, beta, scale=1.0, use_qk_l2norm_in_kernel=True):
 
 @torch.no_grad()
 def scan_recur(factors, rec_of, initial_state=None, zero_value=None, want_output=True):
-    """Second half: run ``len(rec_of)`` (<= 16) recurrences over ``factors``.  Recurrence i walks
+    """Second half: run ``len(rec_of)`` (<= 64) recurrences over ``factors``.  Recurrence i walks
     the factors of sequence ``rec_of[i]`` from ``initial_state[i]`` ((n,H,dk,dv) fp32 or None).
     ``zero_value[i]`` true runs it with v = 0 (started from the identity it yields the
     state-transfer matrix of the segment).  Returns (o (n,T,H,dv) or None, final_state (n,H,dk,dv))."""

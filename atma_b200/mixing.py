@@ -3,8 +3,8 @@
 In the reference the Polar core and the gated-delta memory read the same post-conv q, k, v
 and do not depend on each other (model/reference.py:174-194; inference/models/atma.py:422-426
 runs them back to back on one stream).  The memory recurrence is latency-bound and occupies
-only a few dozen SMs, so this helper puts it on a side stream: the tensor-core attention kernel
-fills the remaining SMs while the recurrence walks its chunks.
+one SM per (sequence, head), so this helper puts it on a side stream: the tensor-core attention
+kernel fills the remaining SMs while the recurrence walks its chunks.
 """
 
 import torch
@@ -46,8 +46,11 @@ def global_layer_mixing(q, k, v, g, beta, n_keys, polar_params, *, window=None, 
     with torch.cuda.stream(side):
         if events:
             events[2].record(side)
+        # beside the attention kernel the single-pass recurrence is the right one: it takes the fewest SM-seconds,
+        # and its latency hides under the attention anyway; alone, the library cuts the sequence into segments
         o, S = chunk_gated_delta_rule(q=q, k=k, v=v, g=g, beta=beta, scale=1.0, initial_state=initial_state,
-                                      output_final_state=True, use_qk_l2norm_in_kernel=True)
+                                      output_final_state=True, use_qk_l2norm_in_kernel=True,
+                                      segments=1 if overlap else None)
         if events:
             events[3].record(side)
     if events:

@@ -174,6 +174,20 @@ int atma_gated_delta_scan(const void* q, const void* k, const void* v, int dtype
                           const float* initial_state, void* o, float* final_state,
                           void* scratch, int B, int T, int H, int Hkv, int dk, int dv,
                           int normalize_qk, float scale, void* stream);
+/* The same call with the cut of each sequence along T stated (16-bit inputs, dk = dv = 128;
+ * ignored otherwise).  A batch of few sequences and heads leaves most SMs idle in the recurrence
+ * over the chunks, so the sequence is cut into `segments` pieces that are walked side by side:
+ * a first pass gives every later segment's affine map on the state (segment 0 runs for real), the
+ * maps are chained into the state at the start of each segment, a second pass runs the later
+ * segments from those states.  Results are those of the single pass within rounding (the same
+ * hand-over the reference does between prefill chunks, inference/models/atma.py:509-544).
+ * segments = 1: single pass (least total work - for a scan that runs beside other kernels);
+ * 2..16: that many segments; 0: chosen from B, H and T (what atma_gated_delta_scan does). */
+int atma_gated_delta_scan_segmented(const void* q, const void* k, const void* v, int dtype,
+                                    const float* g, const float* beta,
+                                    const float* initial_state, void* o, float* final_state,
+                                    void* scratch, int B, int T, int H, int Hkv, int dk, int dv,
+                                    int normalize_qk, float scale, int segments, void* stream);
 
 /* ------------------------------------------------------------------------------------
  * The two halves of atma_gated_delta_scan, for a sequence that is split across GPUs.
@@ -181,7 +195,7 @@ int atma_gated_delta_scan(const void* q, const void* k, const void* v, int dtype
  * the chunked-prefill state carry of inference/models/atma.py:262-301.)
  * _factors builds the state-independent per-chunk factors of B sequences into `scratch`
  * (16-bit inputs, dk = dv = 128 only; arguments as atma_gated_delta_scan).
- * _recur runs n_rec (<= 16) recurrences over those factors: recurrence i uses the factors of
+ * _recur runs n_rec (<= 64) recurrences over those factors: recurrence i uses the factors of
  * sequence rec_of[i] (host array, NULL = identity), starts from initial_state[i] (fp32
  * [n_rec][H][dk][dv], NULL = zeros), writes o[i] ([n_rec][T][H][dv], NULL = no outputs) and
  * final_state[i].  zero_u0[i] != 0 (host array, NULL = all 0) runs the recurrence with v = 0:

@@ -231,3 +231,25 @@ def test_packed_prefill_state_snapshots_give_exact_prefix_reuse():
                                                   torch.tensor([0, lens[0] - 2 * page], dtype=torch.int32), table2,
                                                   torch.tensor([2]))
     assert torch.equal(o_tail, o[tail]) and torch.equal(table2[2], table[3])
+
+
+@pytest.mark.parametrize("B,T,segments", [(1, 8192, 4), (1, 4500, 0), (2, 4096 + 37, 3), (1, 16384, 8)])
+def test_scan_cut_into_segments_equals_the_single_pass(B, T, segments):
+    """A long sequence of a small batch is walked as several segments side by side (transfer maps,
+    chained states, second pass): outputs and final state agree with the single pass and with the
+    oracle; `segments=0` lets the library choose, 1 forces the single pass."""
+    H, Hkv, d = 8, 2, 128
+    g = torch.Generator().manual_seed(T)
+    q = torch.randn(B, T, H, d, generator=g).bfloat16()
+    k = torch.randn(B, T, Hkv, d, generator=g).bfloat16()
+    v = torch.randn(B, T, Hkv, d, generator=g).bfloat16()
+    glog = F.logsigmoid(torch.randn(B, T, H, generator=g) + 3.9)
+    beta = torch.sigmoid(torch.randn(B, T, H, generator=g))
+    S0 = torch.randn(B, H, d, d, generator=g) * 0.3
+    kw = dict(q=q.cuda(), k=k.cuda(), v=v.cuda(), g=glog.cuda(), beta=beta.cuda(), scale=1.0, initial_state=S0.cuda(),
+              output_final_state=True, use_qk_l2norm_in_kernel=True)
+    o1, S1 = atma_b200.chunk_gated_delta_rule(segments=1, **kw)
+    o2, S2 = atma_b200.chunk_gated_delta_rule(segments=segments, **kw)
+    assert max_rel(o2, o1) < 1e-2 and max_rel(S2, S1) < 1e-2
+    o_ref, S_ref = oracle.chunk_gated_delta_rule_oracle(q, k, v, glog, beta, initial_state=S0)
+    assert max_rel(o2, o_ref) < 2e-2 and max_rel(S2, S_ref) < 2e-2
