@@ -51,6 +51,7 @@ class PolarDecodeArgs(Structure):
         ("B", c_int), ("H", c_int), ("Hkv", c_int), ("dk", c_int), ("block_size", c_int),
         ("max_blocks", c_int), ("num_blocks", c_int), ("n_splits", c_int), ("dtype", c_int),
         ("window", c_int), ("eps", c_float),
+        ("gate", c_void_p), ("gate_sb", c_int64), ("gate_sh", c_int64), ("c_sb", c_int64), ("mag_sb", c_int64),
     ]
 
 
@@ -71,6 +72,16 @@ _SIGNATURES = {
     "atma_gated_delta_scan": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                       c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                       c_int, c_float, c_void_p]),
+    "atma_gated_delta_decode_step_fused": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
+                                                   c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+                                                   c_float, c_float, c_void_p, c_int64, c_int64, c_void_p, c_void_p,
+                                                   c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int,
+                                                   c_float, c_float, c_void_p]),
+    "atma_qkv_prep_decode": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p,
+                                     c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p,
+                                     c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                     c_float, c_int, c_void_p]),
+    "atma_add_rms_norm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p]),
     "atma_gated_delta_scan_segmented": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                                 c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                                 c_int, c_float, c_int, c_void_p]),

@@ -145,13 +145,14 @@ def ring_polar_prefill(q_parts, k_parts, v_parts, positions, params, *, backend=
 
 @torch.no_grad()
 def gathered_polar_prefill(q_parts, k_parts, v_parts, positions, params, *, backend=None, group=None,
-                           eps=1e-6, window=None):
+                           eps=1e-6, window=None, events=None):
     """Same contract as ``ring_polar_prefill``, for sequences whose K/V fit every GPU: one
     all-gather brings the un-expanded K/V of the whole sequence into local HBM (token order),
     then each query segment is ONE kernel launch over the keys it can see (absolute key counts
     do the masking).  Two launches per rank instead of 2N+1 and no statistics carried through
     memory; the launch of the later (longer) segment is issued first and the other one runs
-    beside it on a second stream."""
+    beside it on a second stream.  ``events`` = two CUDA timing events recorded on the current
+    stream before the first and after the last Polar launch (the all-gather lies before them)."""
     backend = backend or CudaBackend()
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
@@ -177,11 +178,17 @@ def gathered_polar_prefill(q_parts, k_parts, v_parts, positions, params, *, back
         return [run(0), run(1)]
     cur = torch.cuda.current_stream(dev)
     second = _second_stream(dev)
+    kv_ready = torch.cuda.Event()
+    kv_ready.record(cur)                                             # k_all, v_all (and the queries) are ready here
+    if events:
+        events[0].record(cur)
     out_hi = run(1)                                                  # long rows first
-    second.wait_stream(cur)                                          # k_all, v_all are ready
+    second.wait_event(kv_ready)                                      # ... and the short segment beside them
     with torch.cuda.stream(second):
         out_lo = run(0)
     cur.wait_stream(second)
+    if events:
+        events[1].record(cur)
     for t in out_lo:
         t.record_stream(cur)
     k_all.record_stream(second)
@@ -323,6 +330,13 @@ def _side_resources(device, group):
 GATHER_LIMIT_BYTES = 8 << 30
 
 
+def default_polar_mode(shard, world):
+    """"gather" while the K/V of the whole sequence (what every rank then holds) stay below
+    ``GATHER_LIMIT_BYTES``, else "ring" (memory per GPU stays O(T/N))."""
+    kv_bytes = world * sum(x.numel() * x.element_size() for x in (*shard.k, *shard.v))
+    return "gather" if kv_bytes <= GATHER_LIMIT_BYTES else "ring"
+
+
 @torch.no_grad()
 def cp_global_layer_prefill(shard, params, *, backend=None, group=None, overlap=None, polar_mode=None, window=None):
     """Polar pass + gated-delta prefix scan for one rank's shard.  Returns
@@ -344,9 +358,7 @@ def cp_global_layer_prefill(shard, params, *, backend=None, group=None, overlap=
             o, S = cp_gated_delta_scan(shard.q, shard.k, shard.v, shard.g, shard.beta, backend=backend,
                                        group=scan_group)
     if polar_mode is None:
-        world = dist.get_world_size(group)
-        kv_bytes = 2 * world * sum(x.numel() * x.element_size() for x in (*shard.k, *shard.v))
-        polar_mode = "gather" if kv_bytes <= GATHER_LIMIT_BYTES else "ring"
+        polar_mode = default_polar_mode(shard, dist.get_world_size(group))
     if polar_mode not in ("gather", "ring"):
         raise ValueError(f"polar_mode must be 'gather' or 'ring', not {polar_mode!r}")
     polar_fn = gathered_polar_prefill if polar_mode == "gather" else ring_polar_prefill
@@ -374,14 +386,19 @@ class CapturedPrefill:
     overwritten by the next replay.
     """
 
-    def __init__(self, shard, params, *, group=None, warmup=3, polar_mode=None, window=None):
+    def __init__(self, shard, params, *, group=None, warmup=3, polar_mode=None, window=None, static=None):
         dev = shard.q[0].device
         self.group = group
         self.polar_mode = polar_mode
         self.window = window
-        self.static = GlobalLayerShard(positions=list(shard.positions),
-                                       **{f: [x.clone() for x in getattr(shard, f)]
-                                          for f in ("q", "k", "v", "g", "beta")})
+        if static is None:
+            static = GlobalLayerShard(positions=list(shard.positions),
+                                      **{f: [x.clone() for x in getattr(shard, f)] for f in ("q", "k", "v", "g", "beta")})
+        else:                                              # caller-owned input tensors (e.g. views of one packed buffer)
+            for f in ("q", "k", "v", "g", "beta"):
+                for dst, src in zip(getattr(static, f), getattr(shard, f)):
+                    dst.copy_(src)
+        self.static = static
         self.params = params
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream(dev))
@@ -433,27 +450,68 @@ class CapturedPrefill:
                                        window=self.window)
 
 
+def _packed_views(buf, templates):
+    """Views of one byte buffer with the shapes and dtypes of ``templates`` (256-byte aligned offsets)."""
+    views, off = [], 0
+    for t in templates:
+        n = t.numel() * t.element_size()
+        views.append(buf[off:off + n].view(t.dtype).view(t.shape))
+        off += (n + 255) // 256 * 256
+    return views
+
+
+def _packed_bytes(templates):
+    return sum((t.numel() * t.element_size() + 255) // 256 * 256 for t in templates)
+
+
 class HostFedCapturedPrefill:
     """Context-parallel steps fed from pinned host memory: ``depth`` captured steps with their own
     input buffers on a three-stream pipeline (copy-in | graph replay | copy-out), so that the PCIe
     copies of neighbouring steps hide behind the replay.  Every rank must construct it, call
     ``submit`` the same number of times and ``close`` it before the process group goes away.
 
-    ``submit(host_shard)`` takes a ``GlobalLayerShard`` of pinned tensors and returns a ticket;
-    ``results(ticket)`` waits for that step's copies and returns the pinned outputs
-    [c_lo, mag_lo, c_hi, mag_hi, o_lo, o_hi, S] (reused ``depth`` submits later)."""
+    A step moves ONE buffer in each direction: the inputs of a step are views of one device buffer
+    and ``host_shard(slot)`` hands out matching views of one pinned buffer for the producer of the
+    activations to fill, the seven results are packed on the device and leave in one copy.  (Ten
+    copies in and seven out per step, as separate tensors need, cost more in per-copy latency than
+    in bytes once eight ranks share the host.)  The copy-in stream runs up to ``depth`` - 1 steps
+    ahead of the replays, so a late copy on one rank does not stall the collectives of all ranks.
+
+    ``submit(host_shard)`` takes a ``GlobalLayerShard`` of pinned tensors - one of ``host_shard(i)``
+    for the single-copy path, any other pinned shard is copied tensor by tensor - and returns a
+    ticket; ``results(ticket)`` waits for that step's copy and returns the pinned outputs
+    [c_lo, mag_lo, c_hi, mag_hi, o_lo, o_hi, S] (reused ``depth`` submits later).  ``copy_only``
+    skips the replays: what is left is the host <-> device traffic of the pipeline alone."""
 
     FIELDS = ("q", "k", "v", "g", "beta")
 
-    def __init__(self, shard, params, *, group=None, polar_mode=None, depth=2, window=None):
+    def __init__(self, shard, params, *, group=None, polar_mode=None, depth=3, window=None, copy_only=False):
         dev = shard.q[0].device
-        self.device, self.depth = dev, depth
-        self.caps = [CapturedPrefill(shard, params, group=group, polar_mode=polar_mode, window=window) for _ in range(depth)]
+        torch.cuda.set_device(dev)                       # pinned allocations below belong to this rank's device
+        self.device, self.depth, self.copy_only = dev, depth, copy_only
+        templates = [x for f in self.FIELDS for x in getattr(shard, f)]
+        nbytes = _packed_bytes(templates)
+        self.in_dev = [torch.empty(nbytes, dtype=torch.uint8, device=dev) for _ in range(depth)]
+        self.in_host = [torch.empty(nbytes, dtype=torch.uint8, pin_memory=True) for _ in range(depth)]
+        self._host_shards = [self._as_shard(b, shard) for b in self.in_host]
+        self.caps = [CapturedPrefill(shard, params, group=group, polar_mode=polar_mode, window=window,
+                                     static=self._as_shard(self.in_dev[i], shard)) for i in range(depth)]
         self.copy_in, self.compute, self.copy_out = (torch.cuda.Stream(device=dev) for _ in range(3))
         self.in_free = [None] * depth
         self.out_done = [None] * depth
+        self.out_dev = [None] * depth
         self.out_host = [None] * depth
+        self.out_views = [None] * depth
         self.step = 0
+
+    def _as_shard(self, buf, like):
+        views = _packed_views(buf, [x for f in self.FIELDS for x in getattr(like, f)])
+        it = iter(views)
+        return GlobalLayerShard(positions=list(like.positions), **{f: [next(it) for _ in getattr(like, f)] for f in self.FIELDS})
+
+    def host_shard(self, slot):
+        """Pinned views (one packed buffer) for the inputs of a step; fill them, then ``submit`` them."""
+        return self._host_shards[slot % self.depth]
 
     @staticmethod
     def _flat(outputs):
@@ -464,28 +522,36 @@ class HostFedCapturedPrefill:
         slot = self.step % self.depth
         self.step += 1
         cap = self.caps[slot]
+        packed_src = next((i for i, h in enumerate(self._host_shards) if h is host_shard), None)
         with torch.cuda.stream(self.copy_in):
             if self.in_free[slot] is not None:
                 self.copy_in.wait_event(self.in_free[slot])
-            for f in self.FIELDS:
-                for dst, src in zip(getattr(cap.static, f), getattr(host_shard, f)):
-                    dst.copy_(src, non_blocking=True)
+            if packed_src is not None:
+                self.in_dev[slot].copy_(self.in_host[packed_src], non_blocking=True)
+            else:
+                for f in self.FIELDS:
+                    for dst, src in zip(getattr(cap.static, f), getattr(host_shard, f)):
+                        dst.copy_(src, non_blocking=True)
             arrived = torch.cuda.Event()
             arrived.record(self.copy_in)
         with torch.cuda.stream(self.compute):
             self.compute.wait_event(arrived)
-            if self.out_done[slot] is not None:                 # the step's output buffers were read out
+            if self.out_done[slot] is not None:                 # the slot's packed results were read out
                 self.compute.wait_event(self.out_done[slot])
-            outs = self._flat(cap.replay())
+            outs = self._flat(cap.outputs if self.copy_only and cap.outputs is not None else cap.replay())
+            if self.out_dev[slot] is None:
+                nb = _packed_bytes(outs)
+                self.out_dev[slot] = torch.empty(nb, dtype=torch.uint8, device=self.device)
+                self.out_host[slot] = torch.empty(nb, dtype=torch.uint8, pin_memory=True)
+                self.out_views[slot] = (_packed_views(self.out_dev[slot], outs), _packed_views(self.out_host[slot], outs))
+            for dst, src in zip(self.out_views[slot][0], outs):  # pack on the device: seven small device copies
+                dst.copy_(src, non_blocking=True)
             computed = torch.cuda.Event()
             computed.record(self.compute)
         self.in_free[slot] = computed
-        if self.out_host[slot] is None:
-            self.out_host[slot] = [torch.empty(x.shape, dtype=x.dtype, pin_memory=True) for x in outs]
         with torch.cuda.stream(self.copy_out):
             self.copy_out.wait_event(computed)
-            for h, d in zip(self.out_host[slot], outs):
-                h.copy_(d, non_blocking=True)
+            self.out_host[slot].copy_(self.out_dev[slot], non_blocking=True)
             done = torch.cuda.Event()
             done.record(self.copy_out)
         self.out_done[slot] = done
@@ -495,7 +561,7 @@ class HostFedCapturedPrefill:
         if ticket < self.step - self.depth or ticket >= self.step:
             raise ValueError("that step's result slot has been reused (or the step was never submitted)")
         self.out_done[ticket % self.depth].synchronize()
-        return self.out_host[ticket % self.depth]
+        return self.out_views[ticket % self.depth][1]
 
     def drain(self, stream=None):
         stream = stream or torch.cuda.current_stream(self.device)

@@ -245,7 +245,8 @@ __global__ void polar_decode_merge_kernel(const float* __restrict__ scratch,
                                           const float* __restrict__ sps,
                                           const float* __restrict__ beta, T* __restrict__ c,
                                           T* __restrict__ mag, int B, int H, int dk, int n_splits,
-                                          int window, int max_ctx, float eps) {
+                                          int window, int max_ctx, float eps, const T* __restrict__ gate,
+                                          int64_t gate_sb, int64_t gate_sh, int64_t c_sb, int64_t mag_sb) {
   const int bh = blockIdx.x, b = bh / H, h = bh % H;
   const int tid = threadIdx.x;
   const float* stats = scratch + (int64_t)bh * n_splits * 4;
@@ -292,11 +293,17 @@ __global__ void polar_decode_merge_kernel(const float* __restrict__ scratch,
   __syncthreads();
   const float inv = s_bc;
   cnt = 0;
-  for (int d = tid; d < dk; d += blockDim.x, ++cnt) c[(int64_t)bh * dk + d] = from_f32<T>(sv[cnt] * inv);
+  T* crow = c + (c_sb ? (int64_t)b * c_sb + (int64_t)h * dk : (int64_t)bh * dk);
+  for (int d = tid; d < dk; d += blockDim.x, ++cnt) {
+    float o = sv[cnt] * inv;
+    if (gate != nullptr)                                   // c * sigmoid(gate), rounded where the separate ops round
+      o = round_through<T>(o) * round_through<T>(1.0f / (1.0f + __expf(-to_f32(gate[b * gate_sb + h * gate_sh + d]))));
+    crow[d] = from_f32<T>(o);
+  }
   if (tid == 0) {
     const float n_eff = L * L / fmaxf(Q2, 1e-30f);
     const float m_eff = n_eff * (L / fmaxf(Z, eps));
-    mag[bh] = from_f32<T>(tanhf(beta[h] * log1pf(m_eff)));
+    mag[mag_sb ? (int64_t)b * mag_sb + h : (int64_t)bh] = from_f32<T>(tanhf(beta[h] * log1pf(m_eff)));
   }
 }
 
@@ -313,7 +320,8 @@ int launch_decode(const atma_polar_decode_args& a, cudaStream_t st) {
     if (rc != ATMA_OK) return rc;
     polar_decode_merge_kernel<T><<<a.B * a.H, 64, 0, st>>>(
         a.scratch, a.context_lens, a.v_null, a.spg, a.null_base, a.sps, a.beta, (T*)a.c, (T*)a.mag,
-        a.B, a.H, a.dk, a.n_splits, a.window, a.max_blocks * a.block_size, a.eps);
+        a.B, a.H, a.dk, a.n_splits, a.window, a.max_blocks * a.block_size, a.eps, (const T*)a.gate, a.gate_sb, a.gate_sh,
+        a.c_sb, a.mag_sb);
     return launch_status("polar_decode (merge)");
   }
 #define ATMA_LAUNCH(DKK, GM)                                                                    \
@@ -336,7 +344,8 @@ int launch_decode(const atma_polar_decode_args& a, cudaStream_t st) {
   if (rc != ATMA_OK) return rc;
   polar_decode_merge_kernel<T><<<a.B * a.H, 64, 0, st>>>(
       a.scratch, a.context_lens, a.v_null, a.spg, a.null_base, a.sps, a.beta, (T*)a.c, (T*)a.mag,
-      a.B, a.H, a.dk, a.n_splits, a.window, a.max_blocks * a.block_size, a.eps);
+      a.B, a.H, a.dk, a.n_splits, a.window, a.max_blocks * a.block_size, a.eps, (const T*)a.gate, a.gate_sb, a.gate_sh,
+      a.c_sb, a.mag_sb);
   return launch_status("polar_decode (merge)");
 }
 

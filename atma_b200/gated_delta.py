@@ -48,13 +48,64 @@ def gated_delta_decode_step(q, k, v, gamma, beta, state_table, slots, eps=1e-12,
     return r
 
 
+@torch.no_grad()
+def gated_delta_decode_step_fused(q, k, v, state_table, slots, *, gamma=None, beta=None, gate_logits=None,
+                                  gamma_bias=3.9, beta_bias=0.0, gate=None, out=None, eps=1e-12):
+    """The decode step of the memory with the ops around it folded in (dk = dv = 128): q (B,H,dk); k, v
+    (B,Hkv,d) UN-expanded KV heads; gamma/beta (B,H) fp32, or ``gate_logits`` = (g_logit, b_logit), the
+    (B,H) outputs of the two gate projections in q's dtype (gamma = sigmoid(g + gamma_bias), ...);
+    ``gate`` (B,H*dv) with ``out`` (B,H*dv) view -> out = RMSNorm(r) * sigmoid(gate) in q's dtype (the
+    operand of mem.proj, inference/models/atma.py:373-375) and ``out`` is returned; else r (B,H,dv) fp32."""
+    _lib.require_cuda(q, "gated_delta_decode_step_fused")
+    lib = _lib.load()
+    B, H, dk = q.shape
+    Hkv, dv = k.shape[1], state_table.shape[3]
+    if state_table.dtype != torch.float32 or state_table.stride(3) != 1 or state_table.stride(2) != dv:
+        raise ValueError("state_table must be float32 with dense [dk, dv] planes")
+    q, k, v = _inner_contiguous(q), _inner_contiguous(k).to(q.dtype), _inner_contiguous(v).to(q.dtype)
+    slots = slots.to(torch.int64).contiguous()
+    g_l = b_l = None
+    logit_sb = 0
+    if gate_logits is not None:
+        g_l, b_l = gate_logits
+        if g_l.dtype != q.dtype or b_l.dtype != q.dtype or g_l.stride(1) != 1 or b_l.stride(1) != 1 or g_l.stride(0) != b_l.stride(0):
+            raise ValueError("gate_logits must be two (B,H) tensors in q's dtype with equal row strides")
+        logit_sb = g_l.stride(0)
+    else:
+        gamma, beta = gamma.float().contiguous(), beta.float().contiguous()
+    r = None
+    if gate is None:
+        r = torch.empty((B, H, dv), device=q.device, dtype=torch.float32)
+    else:
+        if out is None:
+            out = torch.empty((B, H * dv), device=q.device, dtype=q.dtype)
+        if gate.dtype != q.dtype or gate.stride(1) != 1 or out.dtype != q.dtype or out.stride(1) != 1:
+            raise ValueError("gate and out must be (B,H*dv) in q's dtype with contiguous rows")
+    _lib.check(lib.atma_gated_delta_decode_step_fused(
+        _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), q.stride(0), q.stride(1), k.stride(0), k.stride(1), v.stride(0), v.stride(1),
+        _lib.dtype_code(q), Hkv, _lib.ptr(gamma) if g_l is None else None, _lib.ptr(beta) if g_l is None else None,
+        _lib.ptr(g_l), _lib.ptr(b_l), logit_sb, float(gamma_bias), float(beta_bias),
+        _lib.ptr(state_table), state_table.stride(0), state_table.stride(1), _lib.ptr(slots), _lib.ptr(r),
+        _lib.ptr(gate), 0 if gate is None else gate.stride(0), _lib.ptr(out), 0 if out is None else out.stride(0),
+        B, H, dk, dv, float(eps), float(torch.finfo(torch.float32).eps), _lib.stream_ptr()))
+    return r if gate is None else out
+
+
 _scratch_cache = {}
+_scratch_retired = []
 
 
 def _scan_scratch(device, nbytes):
-    key = (device.type, device.index)
+    """Scratch for the chunk records: one buffer per (device, stream), grown on demand; an outgrown
+    buffer is kept alive (a CUDA graph captured earlier may still point at it), and while a capture
+    is in progress the buffer comes from the graph's own pool."""
+    if torch.cuda.is_current_stream_capturing():
+        return torch.empty(int(nbytes), device=device, dtype=torch.uint8)
+    key = (device.type, device.index, torch.cuda.current_stream(device).cuda_stream)
     buf = _scratch_cache.get(key)
     if buf is None or buf.numel() < nbytes:
+        if buf is not None:
+            _scratch_retired.append(buf)
         buf = torch.empty(int(nbytes), device=device, dtype=torch.uint8)
         _scratch_cache[key] = buf
     return buf

@@ -242,3 +242,70 @@ def lfm2_conv_packed(projected, weight, state_table, token_seq_starts, token_seq
                                          _lib.ptr(s0), _lib.ptr(e0), _lib.ptr(sl), total, D, K,
                                          _lib.dtype_code(projected), _lib.stream_ptr()))
     return out
+
+
+@torch.no_grad()
+def qkv_prep_decode(q_gate, k, v, w_q, w_k, w_v, state_q, state_k, state_v, slots, k_cache=None, v_cache=None,
+                    slot_mapping=None, eps=None):
+    """One launch for the decode-side glue of a global layer (inference/models/atma.py:557-572): per-head
+    RMSNorm of q and k, the three Canon conv steps in residual form on the slot-indexed state tables
+    (updated IN PLACE), and the scatter of the new K/V row into the paged cache.
+
+    q_gate (B, H, 2*dk) as the q projection produces it, any (row, head) strides (the gate half is left
+    alone); k, v (B, Hkv, dk), any row stride; w_* (C, K); state_* (rows, C, K-1); slots (B,) int64
+    (negative = padded row); k_cache / v_cache (..., Hkv, dk) contiguous with slot_mapping (B,) int32
+    (-1 = skip).  Returns q (B, H, dk), k, v (B, Hkv, dk)."""
+    _lib.require_cuda(q_gate, "qkv_prep_decode")
+    lib = _lib.load()
+    B, H, two_dk = q_gate.shape
+    dk, Hkv, K, dt = two_dk // 2, k.shape[1], w_q.shape[1], q_gate.dtype
+    if q_gate.stride(2) != 1:
+        q_gate = q_gate.contiguous()
+    if k.stride(2) != 1 or k.stride(1) != dk or k.dtype != dt:
+        k = k.to(dt).contiguous()
+    if v.stride(2) != 1 or v.stride(1) != dk or v.dtype != dt:
+        v = v.to(dt).contiguous()
+    w_q, w_k, w_v = (w.to(dt).contiguous() for w in (w_q, w_k, w_v))
+    for st in (state_q, state_k, state_v):
+        _check_conv_state(st, dt, K)
+    if eps is None:
+        eps = torch.finfo(torch.float32).eps
+    slots = slots.to(torch.int64).contiguous()
+    if k_cache is not None:
+        if k_cache.dtype != dt or not k_cache.is_contiguous() or not v_cache.is_contiguous():
+            raise ValueError("the caches must be contiguous and in the activation dtype")
+        slot_mapping = slot_mapping.to(torch.int32).contiguous()
+    q_out = torch.empty((B, H, dk), device=q_gate.device, dtype=dt)
+    k_out = torch.empty((B, Hkv, dk), device=q_gate.device, dtype=dt)
+    v_out = torch.empty((B, Hkv, dk), device=q_gate.device, dtype=dt)
+    _lib.check(lib.atma_qkv_prep_decode(
+        _lib.ptr(q_gate), q_gate.stride(0), q_gate.stride(1), _lib.ptr(k), k.stride(0), _lib.ptr(v), v.stride(0),
+        _lib.ptr(w_q), _lib.ptr(w_k), _lib.ptr(w_v), _lib.ptr(state_q), _lib.ptr(state_k), _lib.ptr(state_v),
+        state_q.stride(0), state_k.stride(0), state_v.stride(0), _lib.ptr(slots), _lib.ptr(q_out), _lib.ptr(k_out),
+        _lib.ptr(v_out), _lib.ptr(k_cache), _lib.ptr(v_cache), _lib.ptr(slot_mapping) if k_cache is not None else None,
+        B, H, Hkv, dk, K, float(eps), _lib.dtype_code(q_gate), _lib.stream_ptr()))
+    return q_out, k_out, v_out
+
+
+@torch.no_grad()
+def add_rms_norm(x, y, weight, eps=1e-6):
+    """(x + y, RMSNorm(x + y) * weight) in one pass over rows of up to 4096 values; y None = no add
+    (then the first result is x itself).  The residual add of one sub-layer fused with the norm in
+    front of the next (inference/models/atma.py:709-712)."""
+    _lib.require_cuda(x, "add_rms_norm")
+    lib = _lib.load()
+    D = x.shape[-1]
+    x2 = x.reshape(-1, D)
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    y2 = None
+    if y is not None:
+        y2 = y.reshape(-1, D).to(x.dtype)
+        if not y2.is_contiguous():
+            y2 = y2.contiguous()
+    w = None if weight is None else weight.to(x.dtype).contiguous()
+    x_out = torch.empty_like(x2) if y is not None else None
+    h = torch.empty_like(x2)
+    _lib.check(lib.atma_add_rms_norm(_lib.ptr(x2), _lib.ptr(y2), _lib.ptr(w), _lib.ptr(x_out), _lib.ptr(h), x2.shape[0], D,
+                                     float(eps), _lib.dtype_code(x), _lib.stream_ptr()))
+    return (x if y is None else x_out.view(x.shape)), h.view(x.shape)

@@ -22,7 +22,7 @@ import torch.nn.functional as F
 from .gated_delta import packed_gated_delta_prefill
 from .inference_ops import qkv_prep_prefill, rms_sigmoid_gate, sigmoid_gate_mul
 from .mixing import _side_stream
-from .polar import polar_attention_packed_fwd
+from .polar import polar_attention_fwd, polar_attention_packed_fwd
 
 
 class PackedMaps:
@@ -53,13 +53,15 @@ def _linear(x, sd, name):
 @torch.no_grad()
 def global_attention_prefill_packed(x, sd, maps, *, num_heads, num_kv_heads, head_dim, conv_states, mem_state_table,
                                     k_cache=None, v_cache=None, slot_mapping=None, window=None, mem_gamma_bias=3.9,
-                                    mem_beta_bias=0.0, prefix="attn.", overlap=True):
+                                    mem_beta_bias=0.0, prefix="attn.", overlap=True, has_initial=None):
     """x (tokens, D) packed fresh prompts; ``sd`` the attention module's tensors (reference names
     under ``prefix``: q, k, v, proj, mu_proj, canon_q/k/v, the five Polar parameters, and mem.*
     when the layer has a memory); ``maps`` a ``PackedMaps``; ``conv_states`` = (q, k, v) conv-state
     tables and ``mem_state_table`` (rows, H, dk, dk) fp32, all updated IN PLACE at the sequences'
     slots; ``k_cache``/``v_cache`` with ``slot_mapping`` receive the post-conv K/V rows.
-    Returns the layer's mixing output (tokens, D)."""
+    ``has_initial``: per sequence, whether its memory continues from its state row (None = all do;
+    False = fresh prompts: every memory starts from zero, as the reference's fresh prefill does,
+    inference/models/atma.py:272-279).  Returns the layer's mixing output (tokens, D)."""
     P = prefix
     H, Hkv, dk = num_heads, num_kv_heads, head_dim
     total = x.shape[0]
@@ -80,13 +82,26 @@ def global_attention_prefill_packed(x, sd, maps, *, num_heads, num_kv_heads, hea
         with torch.cuda.stream(side):
             g = F.logsigmoid(_linear(x, sd, P + "mem.w_gamma").float() + mem_gamma_bias)
             beta = torch.sigmoid(_linear(x, sd, P + "mem.w_beta").float() + mem_beta_bias)
-            r = packed_gated_delta_prefill(q, k, v, g, beta, maps.cu_seqlens, mem_state_table, maps.seq_slots)
+            if has_initial is False:
+                has_initial = torch.zeros(maps.seq_slots.numel(), dtype=torch.int32, device=x.device)
+            r = packed_gated_delta_prefill(q, k, v, g, beta, maps.cu_seqlens, mem_state_table, maps.seq_slots, has_initial)
             mem_out = _linear(rms_sigmoid_gate(r, _linear(x, sd, P + "mem.gate")), sd, P + "mem.proj")
 
-    c, mag = polar_attention_packed_fwd(q, k, v, maps.tile_seq_starts, maps.tile_q_starts, maps.tile_seq_lens,
-                                        window=window, v_null=sd[P + "v_null"], null_base=sd[P + "null_base"],
-                                        null_slope_raw=sd[P + "null_slope_raw"], len_gain_raw=sd[P + "len_gain_raw"],
-                                        mag_beta_raw=sd[P + "mag_beta_raw"])
+    pp = dict(v_null=sd[P + "v_null"], null_base=sd[P + "null_base"], null_slope_raw=sd[P + "null_slope_raw"],
+              len_gain_raw=sd[P + "len_gain_raw"], mag_beta_raw=sd[P + "mag_beta_raw"])
+    if q.dtype in (torch.bfloat16, torch.float16):
+        c, mag = polar_attention_packed_fwd(q, k, v, maps.tile_seq_starts, maps.tile_q_starts, maps.tile_seq_lens,
+                                            window=window, **pp)
+    else:                                   # fp32: sequence by sequence, as the reference's own fallback route does
+        c = torch.empty_like(q)
+        mag = torch.empty((total, H), device=q.device, dtype=q.dtype)
+        cu = maps.cu_seqlens.tolist()
+        for a, b in zip(cu[:-1], cu[1:]):
+            if b > a:
+                n = torch.arange(1, b - a + 1, device=q.device, dtype=torch.float32)
+                ci, mi = polar_attention_fwd(q[a:b].transpose(0, 1)[None], k[a:b].transpose(0, 1)[None],
+                                             v[a:b].transpose(0, 1)[None], n, window=window, **pp)
+                c[a:b], mag[a:b] = ci[0].transpose(0, 1), mi[0].transpose(0, 1)
     gated = sigmoid_gate_mul(c, q_gate[..., dk:]).view(total, H * dk)       # the gate half is read in place
     out = _linear(gated, sd, P + "proj") + _linear(mag, sd, P + "mu_proj")
     if has_mem:

@@ -25,10 +25,18 @@ HAS_CUDA_EXT = HAS_TRITON
 _param_cache = {}
 
 
+def invalidate_param_cache():
+    """Forget the prepared Polar parameters.  The cache is keyed on each raw tensor's storage address and
+    version counter; a write that bypasses the counter (``param.data.copy_``, ``set_``, a loader that
+    assigns ``.data``) leaves a stale entry behind - call this after such a write."""
+    _param_cache.clear()
+
+
 def _params(v_null, null_base, null_slope_raw, len_gain_raw, mag_beta_raw, device):
     """softplus on the host, as kernel/polar_triton.py:540-544 does.  The five small tensors are
     prepared once per (storage, version) of the raw parameters and reused, so a decode step
-    launches nothing but its own kernels."""
+    launches nothing but its own kernels.  Writes through ``.data`` do not bump the version:
+    see ``invalidate_param_cache``."""
     raw = (v_null, null_base, null_slope_raw, len_gain_raw, mag_beta_raw)
     key = tuple((t.data_ptr(), t._version, t.dtype, str(t.device)) for t in raw) + (str(device),)
     hit = _param_cache.get(key)
@@ -178,11 +186,23 @@ def polar_attention_packed_fwd(q, k, v, tile_seq_starts, tile_q_starts, tile_seq
     return c, mag
 
 
-def decode_num_splits(B, Hkv, max_context, sm_count=148, ctas_per_sm=2):
+_sm_counts = {}
+
+
+def _sm_count(device=None):
+    idx = torch.cuda.current_device() if device is None or device.index is None else device.index
+    if idx not in _sm_counts:
+        _sm_counts[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return _sm_counts[idx]
+
+
+def decode_num_splits(B, Hkv, max_context, sm_count=None, ctas_per_sm=2):
     """Key ranges per (sequence, KV head).  The split kernel keeps ``ctas_per_sm`` CTAs resident
     per SM, so the grid B*Hkv*n runs in ceil(B*Hkv*n / (sm_count*ctas_per_sm)) waves; pick the n
     (at least 1024 keys per range, at most 64 ranges) whose last wave is fullest, preferring
     more ranges on a tie-ish.  Depends only on launch-time shapes (CUDA-graph safe)."""
+    if sm_count is None:
+        sm_count = _sm_count() if torch.cuda.is_available() else 148
     slots = sm_count * ctas_per_sm
     n_max = int(max(1, min(64, max_context // 1024)))
     best_n, best_eff = 1, -1.0
@@ -198,14 +218,21 @@ def decode_num_splits(B, Hkv, max_context, sm_count=148, ctas_per_sm=2):
 
 
 _scratch_cache = {}
+_scratch_retired = []
 
 
 def _decode_scratch(device, nfloats):
-    """Per-device scratch for the split partials, grown on demand and reused across calls
-    (stable address once warm, which is what CUDA-graph replay needs)."""
-    key = (device.type, device.index)
+    """Scratch for the split partials: one buffer per (device, stream), so calls on different streams
+    never share it; grown on demand and reused across calls (stable address once warm).  A buffer
+    that is outgrown is kept alive, not freed: a CUDA graph captured earlier may still point at it.
+    While a capture is in progress the buffer comes from the graph's own pool instead."""
+    if torch.cuda.is_current_stream_capturing():
+        return torch.empty(int(nfloats), device=device, dtype=torch.float32)     # owned by the graph being captured
+    key = (device.type, device.index, torch.cuda.current_stream(device).cuda_stream)
     buf = _scratch_cache.get(key)
     if buf is None or buf.numel() < nfloats:
+        if buf is not None:
+            _scratch_retired.append(buf)
         buf = torch.empty(int(nfloats), device=device, dtype=torch.float32)
         _scratch_cache[key] = buf
     return buf
@@ -215,11 +242,17 @@ def _decode_scratch(device, nfloats):
 def polar_attention_decode(q, k_cache, v_cache, block_tables, context_lens, *,
                            v_null, null_base, null_slope_raw, len_gain_raw, mag_beta_raw,
                            eps=1e-6, block_n=None, num_warps=None, num_stages=None, window=None,
-                           num_splits=None):
+                           num_splits=None, gate=None, out=None):
     """Paged Polar decode.  q (B,H,dk); caches (num_blocks, block_size, Hkv, dk) contiguous;
     block_tables (B,max_blocks) int32; context_lens (B,) int32 including the current token.
     Returns c (B,H,dk), mag (B,H) in q's dtype.  ``block_n``, ``num_warps``, ``num_stages``
-    are the reference's Triton launch knobs, accepted and ignored."""
+    are the reference's Triton launch knobs, accepted and ignored.
+
+    Two extensions that are not in the reference's signature: ``gate`` (B,H,dk), any (row, head)
+    strides - c comes back as c * sigmoid(gate), the operand of the output projection
+    (inference/models/atma.py:246-252), from the merge kernel itself; ``out`` = (c_view, mag_view),
+    preallocated views with a dense last dimension (e.g. two column ranges of one activation
+    buffer) that receive the results instead of fresh tensors."""
     _lib.require_cuda(q, "polar_attention_decode")
     lib = _lib.load()
     B, H, dk = q.shape
@@ -237,9 +270,20 @@ def polar_attention_decode(q, k_cache, v_cache, block_tables, context_lens, *,
     params = _params(v_null, null_base, null_slope_raw, len_gain_raw, mag_beta_raw, q.device)
     n_splits = num_splits or decode_num_splits(B, Hkv, max_blocks * block_size)
     scratch = _decode_scratch(q.device, lib.atma_polar_decode_scratch_floats(B, H, dk, n_splits))
-    c = torch.empty((B, H, dk), device=q.device, dtype=q.dtype)
-    mag = torch.empty((B, H), device=q.device, dtype=q.dtype)
     a = _lib.PolarDecodeArgs()
+    if out is None:
+        c = torch.empty((B, H, dk), device=q.device, dtype=q.dtype)
+        mag = torch.empty((B, H), device=q.device, dtype=q.dtype)
+    else:
+        c, mag = out
+        if c.shape != (B, H, dk) or mag.shape != (B, H) or c.dtype != q.dtype or mag.dtype != q.dtype or \
+                c.stride(2) != 1 or c.stride(1) != dk or mag.stride(1) != 1:
+            raise ValueError("out = (c (B,H,dk), mag (B,H)) views in q's dtype with dense rows")
+        a.c_sb, a.mag_sb = c.stride(0), mag.stride(0)
+    if gate is not None:
+        if gate.shape != (B, H, dk) or gate.dtype != q.dtype or gate.stride(2) != 1:
+            raise ValueError("gate must be (B,H,dk) in q's dtype with a contiguous last dimension")
+        a.gate, a.gate_sb, a.gate_sh = _lib.ptr(gate), gate.stride(0), gate.stride(1)
     a.q, a.k_cache, a.v_cache = _lib.ptr(q), _lib.ptr(k_cache), _lib.ptr(v_cache)
     a.block_tables, a.bt_stride, a.context_lens = _lib.ptr(block_tables), block_tables.stride(0), _lib.ptr(context_lens)
     a.v_null, a.spg, a.null_base = _lib.ptr(params["v_null"]), _lib.ptr(params["spg"]), _lib.ptr(params["null_base"])

@@ -23,9 +23,7 @@ import argparse
 import json
 import os
 import statistics
-import subprocess
 import sys
-import tempfile
 import time
 
 import torch
@@ -38,11 +36,12 @@ H, HKV, DK, CHUNK = 8, 2, 128, 64
 T_PREFILL = 65536
 DEC_B, DEC_CTX, DEC_BLOCK = 64, 32768, 256
 METRIC = "global_layer_prefill_tok_s_at_64k"
-# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) from the committed ncu captures
-# (profiles/polar_prefill_sm100_T16384.md and profiles/polar_decode_b16_ctx16384.md: the two DRAM counters
-# captured on the bench launches themselves).
-PREFILL_TRAFFIC_64K = 336.0e6      # read 231 MB + write 105 MB, captured on the 64K launch itself
-DECODE_TRAFFIC_RATIO = 2155.3 / 2147.5   # read 2147.8 MB + write 5.8-9.3 MB on the 64 x 32K launch itself
+# roofline.traffic is not measured by the run that prints it (that needs a profiler): it is the DRAM
+# traffic (dram__bytes_read.sum + dram__bytes_write.sum, one ncu pass) of the same launch at the same
+# shape, scaled by the token count / cache bytes where the run uses another size.
+PREFILL_TRAFFIC_64K = 336.0e6      # read 231 MB + write 105 MB for the 65,536-token launch
+DECODE_TRAFFIC_RATIO = 2155.3 / 2147.5   # read 2147.8 MB + write 5.8-9.3 MB for 2147.5 MB of cache rows (64 x 32K)
+REF_SAMPLE_TOKENS = 4096           # what one step of the reference arm times, whatever N, K and W are
 
 
 def measured_peaks():
@@ -63,27 +62,46 @@ def scan_flops(T):
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons, sampled every 20 ms.  The sampler is started before the
-    warm-up steps (nvidia-smi needs a moment to come up) and the samples are then cut to the timed
-    region by their timestamps; if the timed region was too short to catch one, the samples of the
-    warm-up steps (the same load, directly before) are used and ``window`` says so."""
-    Q = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """SM clock and throttle reasons during the timed region, read through NVML every millisecond
+    on a background thread (read-only queries), so that a timed region of a few tens of
+    milliseconds still holds samples.  ``mark_begin`` / ``mark_end`` cut the samples to the region."""
+    NAMES = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20), ("sw_power_cap", 0x4))
 
     def __init__(self, gpu_index):
-        self.gpu, self.proc, self.path = gpu_index, None, None
+        self.gpu, self.rows, self.thread, self.stop_flag = gpu_index, [], None, False
         self.t_begin = self.t_end = None
 
+    def _index(self):
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            try:
+                return int(vis.split(",")[self.gpu])
+            except (ValueError, IndexError):
+                pass
+        return self.gpu
+
     def start(self):
+        import threading
         try:
-            fd, self.path = tempfile.mkstemp(suffix=".csv")
-            os.close(fd)
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "20"],
-                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
-        except Exception:
-            self.proc = None
+            import pynvml
+            pynvml.nvmlInit()
+            h = pynvml.nvmlDeviceGetHandleByIndex(self._index())
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+        except Exception:                                   # noqa: BLE001 - no NVML: no samples
+            return
+
+        def loop():
+            while not self.stop_flag:
+                try:
+                    mhz = float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM))
+                    reasons = int(pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h))
+                    self.rows.append((time.time(), mhz, reasons))
+                except Exception:                           # noqa: BLE001
+                    pass
+                time.sleep(0.001)
+
+        self.thread = threading.Thread(target=loop, daemon=True)
+        self.thread.start()
 
     def mark_begin(self):
         self.t_begin = time.time()
@@ -92,38 +110,20 @@ class ClockSampler:
         self.t_end = time.time()
 
     def stop(self):
-        import datetime
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        if self.proc is None:
+        if self.thread is None:
             return out
         if self.t_end is None:
             self.t_end = time.time()
-        time.sleep(0.05)
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except Exception:
-            self.proc.kill()
-        rows = []
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in open(self.path):
-            f = [x.strip() for x in line.split(",")]
-            if len(f) < 9:
-                continue
-            try:
-                ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
-                rows.append((ts, float(f[1]), float(f[2]), [n for n, val in zip(names, f[5:9]) if val.lower().startswith("active")]))
-            except ValueError:
-                continue
-        os.unlink(self.path)
-        inside = [r for r in rows if self.t_begin is not None and self.t_begin - 0.01 <= r[0] <= self.t_end + 0.03]
-        window = "timed region"
-        if not inside:
-            inside = [r for r in rows if r[0] <= self.t_end + 0.03][-10:]
-            window = "warm-up steps directly before the timed region (it was shorter than the sampling period)"
+        self.stop_flag = True
+        self.thread.join(timeout=2)
+        inside = [r for r in self.rows if self.t_begin is not None and self.t_begin <= r[0] <= self.t_end]
         if inside:
-            out.update(sm_mhz=statistics.median(r[1] for r in inside), sm_max_mhz=max(r[2] for r in inside),
-                       reasons=sorted({n for r in inside for n in r[3]}), samples=len(inside), window=window)
+            bits = 0
+            for r in inside:
+                bits |= r[2]
+            out.update(sm_mhz=statistics.median(r[1] for r in inside), sm_max_mhz=self.max_mhz,
+                       reasons=[n for n, bit in self.NAMES if bits & bit], samples=len(inside), window="timed region")
         return out
 
 
@@ -270,15 +270,13 @@ def cpu_baseline(sample_T, threads):
 
 
 def run_reference(args, rank):
+    """The reference arm: the CPU oracle (a restatement of the reference's pure-PyTorch path - the reference
+    itself is Python that cannot travel to this box) on all host cores.  Each step times the SAME bounded
+    sample of the workload, REF_SAMPLE_TOKENS tokens, whatever N, K and W are."""
     if rank != 0:
         return
     threads = os.cpu_count() or 1
-    t_probe = cpu_baseline(512, threads)
-    budget = 150.0 / max(1, args.steps + args.warmup)
-    sample_T = 512
-    for cand in (1024, 2048, 4096, 8192, 16384):
-        if t_probe * (cand / 512.0) ** 2 < budget:      # materialised Polar is quadratic
-            sample_T = cand
+    sample_T = REF_SAMPLE_TOKENS
     for _ in range(args.warmup):
         cpu_baseline(sample_T, threads)
     t0 = time.perf_counter()
@@ -416,8 +414,9 @@ def profile_case(which):
         for _ in range(5):
             ab.chunk_gated_delta_rule(q=q, k=k, v=v, g=gl, beta=be, scale=1.0, output_final_state=True,
                                       use_qk_l2norm_in_kernel=True)
-        info = {"kernel": "scan_local_mma_kernel + scan_seq_mma_kernel", "B": B, "T": T,
-                "flops_per_launch": scan_flops(T) * B}
+        info = {"kernel": "scan_local_sm100_kernel + scan_recur_sm100_kernel", "B": B, "T": T,
+                "flops_per_launch": scan_flops(T) * B,
+                "algorithmic_bytes": 4.0 * B * T * H * DK * 2 - 2.0 * B * T * (H - HKV) * DK * 2 + 2.0 * B * T * H * 4}
     torch.cuda.synchronize()
     emit({"profile": which, **info})
 
@@ -457,17 +456,23 @@ def run_context_parallel(args, ab, rank, local_rank, world, device, peaks):
         return cp.GlobalLayerShard(positions=sh.positions,
                                    **{f: [x.to(device, non_blocking=True) for x in host[f]] for f in fields})
 
+    mode = cp.default_polar_mode(sh, world)
+    polar_fn = cp.gathered_polar_prefill if mode == "gather" else cp.ring_polar_prefill
+
     def step(shard, ev=None):
         tr = lambda x: x.transpose(1, 2)
-        if ev:
+        kw = {"events": ev[0:2]} if (ev and mode == "gather") else {}
+        if ev and mode != "gather":
             ev[0].record()
-        polar = cp.ring_polar_prefill([tr(x) for x in shard.q], [tr(x) for x in shard.k], [tr(x) for x in shard.v],
-                                      shard.positions, params)
-        if ev:
+        polar = polar_fn([tr(x) for x in shard.q], [tr(x) for x in shard.k], [tr(x) for x in shard.v],
+                         shard.positions, params, **kw)
+        if ev and mode != "gather":
             ev[1].record()
-        o, S = cp.cp_gated_delta_scan(shard.q, shard.k, shard.v, shard.g, shard.beta)
         if ev:
             ev[2].record()
+        o, S = cp.cp_gated_delta_scan(shard.q, shard.k, shard.v, shard.g, shard.beta)
+        if ev:
+            ev[3].record()
         return polar, o, S
 
     def barrier():
@@ -475,20 +480,21 @@ def run_context_parallel(args, ab, rank, local_rank, world, device, peaks):
         torch.cuda.synchronize()
 
     dev_shard = to_dev()
-    # (1) un-overlapped eager pass: the ring and the memory branch one after the other, for the
-    #     per-branch durations the roofline entry quotes
+    # (1) the two branches one after the other, launch by launch, in the mode the timed step uses, for the
+    #     per-branch durations: in gather mode the events bracket the two Polar launches (the K/V all-gather
+    #     lies before them); in ring mode the whole ring pass
     for _ in range(args.warmup):
         step(dev_shard)
     barrier()
     n_eager = max(3, min(args.steps, 10))
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(n_eager)]
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(n_eager)]
     h0 = time.perf_counter()
     for i in range(n_eager):
         step(dev_shard, ev[i])
     host_enqueue_ms = (time.perf_counter() - h0) * 1e3 / n_eager
     barrier()
-    polar_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / n_eager
-    scan_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / n_eager
+    polar_ms = statistics.median(e[0].elapsed_time(e[1]) for e in ev)
+    scan_ms = statistics.median(e[2].elapsed_time(e[3]) for e in ev)
 
     # (2) the timed step: the public entry (memory branch beside the ring), replayed from a CUDA
     #     graph unless --no-graph
@@ -502,7 +508,7 @@ def run_context_parallel(args, ab, rank, local_rank, world, device, peaks):
             print(f"[bench] graph capture failed, running eagerly: {getattr(cap, 'error', None)!r}", file=sys.stderr)
     sampler = ClockSampler(local_rank)
     sampler.start()
-    for _ in range(max(args.warmup, 50)):                       # also gives the clock sampler time to come up
+    for _ in range(max(args.warmup, 20)):
         run_step()
     barrier()
     sampler.mark_begin()
@@ -519,23 +525,44 @@ def run_context_parallel(args, ab, rank, local_rank, world, device, peaks):
     # (3) end to end: every step copies its pinned host shard in and all results back out.  With the graph:
     #     two captured steps on a three-stream pipeline (copy-in | replay | copy-out); without: one stream.
     host_shard = cp.GlobalLayerShard(positions=sh.positions, **{f: host[f] for f in fields})
+    copy_only_ms = None
     if graph_used:
         pipe = cp.HostFedCapturedPrefill(dev_shard, params)
-        for _ in range(3):
-            pipe.submit(host_shard)
+        # the producer of the activations fills the pipeline's own pinned views (one packed buffer per step slot)
+        packed = []
+        for i in range(pipe.depth):
+            hs = pipe.host_shard(i)
+            for f in fields:
+                for dst, src in zip(getattr(hs, f), host[f]):
+                    dst.copy_(src)
+            packed.append(hs)
+
+        def run_pipe(n):
+            s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s0.record()
+            for s_ in (pipe.copy_in, pipe.compute, pipe.copy_out):
+                s_.wait_event(s0)
+            tk = None
+            for i in range(n):
+                tk = pipe.submit(packed[i % pipe.depth])
+            pipe.drain()
+            s1.record()
+            barrier()
+            return s0.elapsed_time(s1) / n, tk
+
+        for i in range(3):
+            pipe.submit(packed[i % pipe.depth])
         pipe.drain()
         barrier()
-        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s0.record()
-        for s_ in (pipe.copy_in, pipe.compute, pipe.copy_out):
-            s_.wait_event(s0)
-        for _ in range(args.steps):
-            ticket = pipe.submit(host_shard)
-        pipe.drain()
-        s1.record()
-        barrier()
+        e2e_ms_local, ticket = run_pipe(args.steps)
         out_host = pipe.results(ticket)
-        e2e_api = "atma_b200.context_parallel.HostFedCapturedPrefill.submit"
+        # the same pipeline with the replays left out: what the host <-> device copies alone cost per step
+        pipe.copy_only = True
+        run_pipe(3)
+        copy_only_ms, _ = run_pipe(args.steps)
+        pipe.copy_only = False
+        e2e_api = ("atma_b200.context_parallel.HostFedCapturedPrefill.submit (one packed pinned buffer per direction, "
+                   f"{pipe.depth} steps in flight)")
     else:
         out_host = None
 
@@ -561,12 +588,13 @@ def run_context_parallel(args, ab, rank, local_rank, world, device, peaks):
         s1.record()
         barrier()
         e2e_api = "atma_b200.context_parallel.cp_global_layer_prefill"
-    e2e_ms = s0.elapsed_time(s1) / args.steps
+        e2e_ms_local = s0.elapsed_time(s1) / args.steps
+    e2e_ms = e2e_ms_local
     h2d = sum(x.numel() * x.element_size() for f in fields for x in host[f])
     d2h = sum(x.numel() * x.element_size() for x in out_host)
-    t = torch.tensor([ms, e2e_ms, polar_ms, scan_ms], device=device, dtype=torch.float64)
+    t = torch.tensor([ms, e2e_ms, polar_ms, scan_ms, copy_only_ms or 0.0], device=device, dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, e2e_ms, polar_ms, scan_ms = t.tolist()
+    ms, e2e_ms, polar_ms, scan_ms, copy_only_ms = t.tolist()
     bytes_t = torch.tensor([h2d, d2h], device=device, dtype=torch.float64)
     dist.all_reduce(bytes_t)
     h2d, d2h = bytes_t.tolist()
@@ -579,6 +607,9 @@ def run_context_parallel(args, ab, rank, local_rank, world, device, peaks):
         del cap
     torch.cuda.empty_cache()
     decode = None if args.skip_decode else bench_decode_sharded(ab, device, max(args.steps, 10), args.warmup, peaks, world, dist)
+    long_leg = None
+    if not args.skip_long and T_PREFILL != 262144:
+        long_leg = cp_long_prefill(cp, dist, rank, world, device, params, 262144, peaks)
     dist.barrier()
     dist.destroy_process_group()
     if rank != 0:
@@ -592,25 +623,128 @@ def run_context_parallel(args, ab, rank, local_rank, world, device, peaks):
                                "context-parallel over the GPUs (zig-zag segments, K/V all-gathered over NVLink, one Polar launch per "
                                "query segment, gated-delta state handed over as an affine-map prefix)",
                    "tokens": T_PREFILL, "heads": H, "kv_heads": HKV, "head_dim": DK, "chunk": CHUNK, "window": None,
-                   "l2": "per-GPU inputs shrink with N; at N=8 they are 34 MB, below L2", "polar_kernel": "tcgen05"},
+                   "l2": "per-GPU inputs shrink with N; at N=8 they are 34 MB, below L2", "polar_kernel": "tcgen05",
+                   "polar_mode": mode},
         "e2e": {"value": T_PREFILL / (e2e_ms * 1e-3), "unit": "tok/s", "ms_per_step": e2e_ms, "api": e2e_api,
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                # the pipeline with the replays left out (copies only), max over ranks, and what that is in GB/s over all ranks
+                "copies_only_ms_per_step": copy_only_ms or None,
+                "copies_only_gbs_all_ranks": ((h2d + d2h) / (copy_only_ms * 1e-3) / 1e9) if copy_only_ms else None},
         # per rank and step: 2 Polar launches (one per query segment), the chunk-factor kernel and
         # 2 recurrence launches of this library; NCCL and torch's small copy kernels are not counted
         "gpu_launches": args.steps * 5 * world,
         "clocks": clocks,
-        "roofline": {"kernel": "polar_prefill (ring pass, all ranks)", "bound": "tensor", "achieved": achieved_tf,
+        "roofline": {"kernel": f"polar_prefill ({mode} mode, all ranks)", "bound": "tensor", "achieved": achieved_tf,
                      "peak": peaks["tf_burst"] * world, "unit": "TFLOP/s", "frac": achieved_tf / (peaks["tf_burst"] * world),
                      "traffic": None, "algorithmic_flops": polar_flops(T_PREFILL), "kernel_ms": polar_ms,
-                     "note": "kernel_ms = the whole ring pass (all block launches and the hops between them) of an "
-                             "un-overlapped eager run, max over ranks",
+                     "note": ("kernel_ms = first Polar launch to the end of the last one (two launches per rank on two "
+                              "streams, after the K/V all-gather)" if mode == "gather" else
+                              "kernel_ms = the whole ring pass (all block launches and the hops between them)") +
+                             ", launch by launch with nothing beside it, median over steps, max over ranks",
                      "peak_source": peaks["source"] + f" burst x {world} GPUs"},
         "scan": {"kernel_ms": scan_ms, "algorithmic_flops": scan_flops(T_PREFILL)},
         "host_enqueue_ms_eager": host_enqueue_ms, "cuda_graph": graph_used,
         "cpu_baseline": None,
         "decode": decode,
+        "prefill_256k": long_leg,
     }
     emit(line)
+
+
+def cp_long_prefill(cp, dist, rank, world, device, params, tokens, peaks, steps=5, warm=3):
+    """The long context-parallel case (BASELINE config 5's length, one global layer's mixing): the captured
+    step on a 262,144-token sequence, device-timed, max over ranks."""
+    global T_PREFILL
+    keep, T_PREFILL = T_PREFILL, tokens
+    try:
+        full = make_prefill_inputs(seed=5)
+    finally:
+        T_PREFILL = keep
+    sh = cp.shard_sequence(full, rank, world)
+    del full
+    shard = cp.GlobalLayerShard(positions=sh.positions,
+                                **{f: [x.to(device) for x in getattr(sh, f)] for f in ("q", "k", "v", "g", "beta")})
+    cap = cp.CapturedPrefill(shard, params)
+    for _ in range(warm):
+        cap.replay()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        cap.replay()
+    e1.record()
+    dist.barrier()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / steps], device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    graph = cap.captured
+    cap.close()
+    del cap, shard
+    torch.cuda.empty_cache()
+    tf = polar_flops(tokens) / (ms * 1e-3) / 1e12
+    return {"tokens": tokens, "ms_per_step": ms, "value": tokens / (ms * 1e-3), "unit": "tok/s", "steps": steps, "cuda_graph": graph,
+            "polar_mode": cp.default_polar_mode(sh, world), "step_tflops": tf, "frac_of_tensor_peak": tf / (peaks["tf_burst"] * world),
+            "note": "whole step (K/V all-gather, Polar, memory branch beside it) against the Polar FLOPs alone"}
+
+
+def timed(fn, iters, warm=3, flush=None):
+    """Median CUDA-event duration (ms) of fn(); ``flush``: a buffer larger than L2 rewritten before every call."""
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    out = []
+    for _ in range(iters):
+        if flush is not None:
+            flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        out.append(a.elapsed_time(b))
+    return statistics.median(out)
+
+
+def bench_config2(ab, device, peaks):
+    """BASELINE config 2: Polar prefill alone, q [4,8192,8,128], k/v [4,8192,2,128], bf16, seed 1, full causal context."""
+    torch.manual_seed(1)
+    B, T = 4, 8192
+    q = torch.randn(B, T, H, DK).bfloat16().to(device)
+    k = torch.randn(B, T, HKV, DK).bfloat16().to(device)
+    v = torch.randn(B, T, HKV, DK).bfloat16().to(device)
+    n = torch.arange(1, T + 1, dtype=torch.float32, device=device)
+    P = default_polar_params(device)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)       # the inputs (101 MB) fit L2: flush it
+    ms = timed(lambda: ab.polar_attention_fwd(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), n, **P), 10, flush=flush)
+    fl = B * polar_flops(T)
+    tf = fl / (ms * 1e-3) / 1e12
+    return {"workload": "BASELINE config 2: Polar prefill B=4 x 8192, H=8, Hkv=2, dk=128, bf16", "ms": ms,
+            "value": B * T / (ms * 1e-3), "unit": "tok/s", "algorithmic_flops": fl,
+            "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["tf_burst"], "unit": "TFLOP/s", "frac": tf / peaks["tf_burst"]},
+            "l2": "L2 flushed (256 MB written) before every timed launch"}
+
+
+def bench_config3(ab, device, peaks):
+    """BASELINE config 3: gated-delta scan alone, B=8, T=16384, H=8, d=128, chunk 64, bf16 inputs, fp32 state, seed 2."""
+    torch.manual_seed(2)
+    B, T = 8, 16384
+    q = F.normalize(torch.randn(B, T, H, DK), dim=-1).bfloat16().to(device)
+    k = F.normalize(torch.randn(B, T, H, DK), dim=-1).bfloat16().to(device)
+    v = torch.randn(B, T, H, DK).bfloat16().to(device)
+    beta = torch.sigmoid(torch.randn(B, T, H)).to(device)
+    g = (-F.softplus(torch.randn(B, T, H))).to(device)
+    ms = timed(lambda: ab.chunk_gated_delta_rule(q=q, k=k, v=v, g=g, beta=beta, scale=1.0, output_final_state=True,
+                                                 use_qk_l2norm_in_kernel=True), 10)
+    fl = scan_flops(T) * B
+    nbytes = 4.0 * B * T * H * DK * 2 + 2.0 * B * T * H * 4 + B * H * DK * DK * 4.0     # q, k, v, o + g, beta + final state
+    tf, gbs = fl / (ms * 1e-3) / 1e12, nbytes / (ms * 1e-3) / 1e9
+    return {"workload": "BASELINE config 3: gated-delta scan B=8 x 16384, H=8, d=128, chunk 64", "ms": ms,
+            "value": B * T / (ms * 1e-3), "unit": "tok/s", "algorithmic_flops": fl, "algorithmic_bytes": nbytes,
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s", "frac": gbs / peaks["hbm"],
+                         "tensor_tflops": tf, "tensor_frac": tf / peaks["tf_burst"]},
+            "l2": "inputs (805 MB) larger than L2"}
 
 
 _REAL_STDOUT = None
@@ -643,6 +777,8 @@ def main():
                     help="N > 1: issue the context-parallel step launch by launch instead of replaying a CUDA graph")
     ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline leg (profiling runs)")
     ap.add_argument("--skip-decode", action="store_true", help="omit the decode leg (profiling runs)")
+    ap.add_argument("--skip-long", action="store_true", help="N > 1: omit the 262,144-token leg")
+    ap.add_argument("--skip-configs", action="store_true", help="N = 1: omit the BASELINE config 2 / config 3 legs")
     ap.add_argument("--profile", default=None, choices=["prefill", "decode", "scan", "prep", "epilogue"],
                     help="run a few launches of ONE kernel on a small case (a few hundred MB, larger than L2) "
                          "and exit; meant to be wrapped in ncu")
@@ -704,11 +840,12 @@ def main():
     scan_ms = sum(e[2].elapsed_time(e[3]) for e in ev) / args.steps
     # the same kernels one after the other on one stream, for the isolated kernel durations
     from atma_b200.mixing import global_layer_mixing
-    iso = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(7)]
+    iso = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(9)]
     for e in iso:
         global_layer_mixing(dev_in["q"], dev_in["k"], dev_in["v"], dev_in["g"], dev_in["beta"], n_keys, params,
                             overlap=False, events=e)
-    torch.cuda.synchronize()
+        torch.cuda.synchronize()                                # one step at a time: nothing queued beside the kernel
+    iso = iso[2:]                                               # the first two calls warm the single-stream path up
     polar_iso_all = sorted(e[0].elapsed_time(e[1]) for e in iso)
     polar_iso_ms = polar_iso_all[len(iso) // 2]                     # median
     scan_iso_ms = sorted(e[2].elapsed_time(e[3]) for e in iso)[len(iso) // 2]
@@ -743,10 +880,17 @@ def main():
     ms, e2e_ms, polar_ms, scan_ms = times.tolist()
 
     decode = None
+    del dev_in
+    torch.cuda.empty_cache()
     if rank == 0 and not args.skip_decode:
-        del dev_in
-        torch.cuda.empty_cache()
         decode = bench_decode(ab, device, max(args.steps, 10), args.warmup, peaks)
+        torch.cuda.empty_cache()
+    config2 = config3 = None
+    if rank == 0 and not args.skip_configs and T_PREFILL == 65536:
+        config2 = bench_config2(ab, device, peaks)
+        torch.cuda.empty_cache()
+        config3 = bench_config3(ab, device, peaks)
+        torch.cuda.empty_cache()
     cpu = None
     if rank == 0 and world == 1 and not args.skip_cpu:
         threads = os.cpu_count() or 1
@@ -789,7 +933,7 @@ def main():
                      # 336 MB = the algorithmic input and output bytes; other lengths scale by the token count.
                      "traffic": PREFILL_TRAFFIC_64K * (T_PREFILL / 65536),
                      "algorithmic_flops": polar_flops(T_PREFILL), "kernel_ms": polar_ms,
-                     "kernel_ms_alone": polar_iso_ms, "kernel_ms_alone_all": polar_iso_all,
+                     "kernel_ms_alone": polar_iso_ms, "kernel_ms_alone_min_max": [polar_iso_all[0], polar_iso_all[-1]],
                      # the timed region runs under the power cap (see clocks); against the seconds-long cuBLAS figure:
                      "frac_of_sustained_peak": achieved_tf / peaks["tf_sustained"],
                      "frac_alone": polar_flops(T_PREFILL) / (polar_iso_ms * 1e-3) / 1e12 / peak_tf,
@@ -799,9 +943,14 @@ def main():
                      "peak_source": peaks["source"] + (" sustained" if ms > 1000 else " burst")},
         "scan": {"kernel_ms": scan_ms, "kernel_ms_alone": scan_iso_ms,
                  "tflops": scan_flops(T_PREFILL) / (scan_iso_ms * 1e-3) / 1e12,
-                 "algorithmic_flops": scan_flops(T_PREFILL)},
+                 "algorithmic_flops": scan_flops(T_PREFILL),
+                 "note": "kernel_ms: the single-pass scan (chunk-local kernel + one recurrence CTA per head) beside the "
+                         "attention kernel; kernel_ms_alone: the library's own choice with nothing beside it "
+                         "(the sequence cut into segments that are walked side by side)"},
         "cpu_baseline": cpu,
         "decode": decode,
+        "config2": config2,
+        "config3": config3,
     }
     emit(line)
 

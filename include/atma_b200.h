@@ -112,6 +112,13 @@ typedef struct {
   int dtype;
   int window;
   float eps;
+  /* Optional fused epilogue and output placement (all zero / NULL = plain dense c and mag).
+   * gate [B][H][dk] with element strides (gate_sb, gate_sh): c is written as c * sigmoid(gate),
+   * the operand of the output projection (inference/models/atma.py:246-252), with the roundings
+   * of the separate eager ops.  c_sb / mag_sb: element stride between the rows of c and of mag
+   * (0 = dense), so that both can land in one row of a wider activation buffer. */
+  const void* gate; int64_t gate_sb, gate_sh;
+  int64_t c_sb, mag_sb;
 } atma_polar_decode_args;
 
 int64_t atma_polar_decode_scratch_floats(int B, int H, int dk, int n_splits);
@@ -154,6 +161,51 @@ int atma_gated_delta_decode_step(const void* q, const void* k, const void* v,
                                  float* state, int64_t state_ss, int64_t state_sh,
                                  const int64_t* slots, float* r,
                                  int B, int H, int dk, int dv, float eps, void* stream);
+
+/* The same step with the work around it folded in (16-bit or fp32 inputs, dk = dv = 128), one CTA per
+ * (sequence, head) holding the whole 64 KiB state between its read and its write:
+ *  - k, v carry Hkv un-expanded heads (head h reads KV head h / (H / Hkv)); the reference expands
+ *    them first (inference/models/atma.py:609-611);
+ *  - gamma / beta either as fp32 [B][H] (g_logit == NULL) or as the logits of the two gate
+ *    projections in `dtype` with row stride logit_sb: gamma = sigmoid(g_logit + gamma_bias),
+ *    beta = sigmoid(b_logit + beta_bias) (:352-355);
+ *  - with gate != NULL the read-out is written as RMSNorm(r) * sigmoid(gate) in `dtype` to
+ *    out [B][H*dv] (row strides gate_sb, out_sb), the operand of mem.proj (:373-375); else r goes
+ *    out as fp32 [B][H][dv]. */
+int atma_gated_delta_decode_step_fused(const void* q, const void* k, const void* v,
+                                       int64_t q_sb, int64_t q_sh, int64_t k_sb, int64_t k_sh,
+                                       int64_t v_sb, int64_t v_sh, int dtype, int Hkv,
+                                       const float* gamma, const float* beta,
+                                       const void* g_logit, const void* b_logit, int64_t logit_sb,
+                                       float gamma_bias, float beta_bias,
+                                       float* state, int64_t state_ss, int64_t state_sh,
+                                       const int64_t* slots, float* r,
+                                       const void* gate, int64_t gate_sb, void* out, int64_t out_sb,
+                                       int B, int H, int dk, int dv, float eps, float rms_eps, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * Decode-side glue of a global layer in one launch (no single counterpart in the reference:
+ * it is the run of ops at inference/models/atma.py:557-572 - F.rms_norm of q and k per head,
+ * three _gpu_conv_step calls in residual form on the slot-indexed conv-state tables, and
+ * store_kvcache of the new K/V row).  q_gate [B][H][2*dk] with element strides (qg_row, qg_head),
+ * only the q half is read; k, v [B][Hkv][dk] with row strides; w_* [C][K]; state_* [rows][C][K-1]
+ * with row strides ss_*, UPDATED IN PLACE at rows slots[b] (negative = padded batch row: the
+ * conv sees a zero state and nothing is written); outputs dense; k_cache / v_cache rows
+ * [slot][Hkv][dk] receive the post-conv K/V at slot_mapping[b] (-1 = skip), may be NULL.
+ * ---------------------------------------------------------------------------------- */
+int atma_qkv_prep_decode(const void* q_gate, int64_t qg_row, int64_t qg_head, const void* k, int64_t k_row,
+                         const void* v, int64_t v_row, const void* w_q, const void* w_k, const void* w_v,
+                         void* state_q, void* state_k, void* state_v, int64_t ss_q, int64_t ss_k, int64_t ss_v,
+                         const int64_t* slots, void* q_out, void* k_out, void* v_out, void* k_cache,
+                         void* v_cache, const int32_t* slot_mapping, int B, int H, int Hkv, int dk, int K,
+                         float eps, int dtype, void* stream);
+
+/* Residual add followed by the next RMSNorm: x_out = x + y (y may be NULL), h_out =
+ * x_out * rsqrt(mean(x_out^2) + eps) * weight (weight may be NULL); rows of D <= 4096 values,
+ * dense.  The block structure x + mix(norm1(x)), x + mlp(norm2(x)) of
+ * inference/models/atma.py:709-712 (model/layers.py:14-17) is two of these per layer. */
+int atma_add_rms_norm(const void* x, const void* y, const void* weight, void* x_out, void* h_out, int rows, int D,
+                      float eps, int dtype, void* stream);
 
 /* ------------------------------------------------------------------------------------
  * Gated-delta chunked scan.  Replaces the third-party flash-linear-attention call

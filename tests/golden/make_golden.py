@@ -192,9 +192,9 @@ def main(ref_root):
                             state={k_: v_.clone() for k_, v_ in sd.items() if k_.startswith("mem.")})
 
     # a whole small model: 8 layers (2 global), model/reference.py:236-269
-    cfg = AtmaConfig(vocab_size=640, num_hidden_layers=8, hidden_size=256, head_dim=64, attn_window=None,
+    cfg = AtmaConfig(vocab_size=640, num_hidden_layers=8, hidden_size=512, head_dim=128, attn_window=None,
                      mem_enabled=True, mem_chunk=64, mem_kernel="torch", attn_kernel="torch")
-    sd = sw.model_state(seed=7, vocab=640, layers=8, dim=256, head_dim=64, num_kv_heads=1)
+    sd = sw.model_state(seed=7, vocab=640, layers=8, dim=512, head_dim=128, num_kv_heads=1)
     model = ref.ReferenceModel(cfg)
     model.load_state_dict(sd, strict=True)
     ids = torch.randint(0, 640, (2, 90), generator=torch.Generator().manual_seed(103))

@@ -67,7 +67,7 @@ def _worker(rank, world, port, ret):
         cap.close()
         torch.cuda.synchronize()
         ret[f"stage{rank}"] = "graph released"
-        # the host-fed pipeline: three steps from pinned host memory through two captured steps
+        # the host-fed pipeline: steps from pinned host memory through the captured steps
         host_shard = cp.GlobalLayerShard(positions=shard.positions,
                                          **{f: [x.cpu().pin_memory() for x in getattr(shard, f)] for f in ("q", "k", "v", "g", "beta")})
         pipe = cp.HostFedCapturedPrefill(shard, pg, polar_mode="gather")
@@ -76,6 +76,13 @@ def _worker(rank, world, port, ret):
         for step in range(3):
             ticket = pipe.submit(host_shard)
             got = pipe.results(ticket)
+            fed = fed and all(torch.equal(a, b.cpu()) for a, b in zip(got, want))
+        packed = pipe.host_shard(0)                       # the single-copy path: views of one pinned buffer
+        for f in ("q", "k", "v", "g", "beta"):
+            for dst, src in zip(getattr(packed, f), getattr(shard, f)):
+                dst.copy_(src.cpu())
+        for step in range(2):
+            got = pipe.results(pipe.submit(packed))
             fed = fed and all(torch.equal(a, b.cpu()) for a, b in zip(got, want))
         ret[f"fed{rank}"] = bool(fed)
         pipe.close()

@@ -63,8 +63,8 @@ def test_memory_readout_matches_reference(golden):
 
 def test_small_model_logits_match_reference(golden):
     g = golden["model_small"]
-    sd = sw.model_state(seed=int(g["weight_seed"]), vocab=640, layers=8, dim=256, head_dim=64, num_kv_heads=1)
-    logits = oracle.model_oracle(g["ids"], sd, layers=8, head_dim=64, num_kv_heads=1)
+    sd = sw.model_state(seed=int(g["weight_seed"]), vocab=640, layers=8, dim=512, head_dim=128, num_kv_heads=1)
+    logits = oracle.model_oracle(g["ids"], sd, layers=8, head_dim=128, num_kv_heads=1)
     assert max_abs(logits, g["logits"]) < 1e-4
 
 
