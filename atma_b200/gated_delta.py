@@ -160,6 +160,37 @@ def _scan_varlen(q, k, v, g, beta, cu_seqlens, scale, use_qk_l2norm_in_kernel, *
     return o, final
 
 
+def _packed_prefill_snapshots_by_page(q, k, v, g, beta, seqlens, state_table, slots, has_initial, scale, l2norm, page):
+    """fp32 inputs / other head sizes: every sequence is scanned page by page through the dense entry, the state
+    after each full page is kept.  Same return value as the one-pass form."""
+    counts = [int(n) // page for n in seqlens]
+    offsets = [0]
+    for c in counts:
+        offsets.append(offsets[-1] + c)
+    H, dk, dv = q.shape[1], q.shape[-1], v.shape[-1]
+    snaps = torch.empty((max(offsets[-1], 1), H, dk, dv), device=q.device, dtype=torch.float32)
+    o = torch.empty((q.shape[0], H, dv), device=q.device, dtype=q.dtype)
+    slot_l = slots.tolist()
+    init_l = None if has_initial is None else has_initial.tolist()
+    pos = 0
+    for i, n in enumerate(seqlens):
+        n = int(n)
+        S = state_table[slot_l[i]].unsqueeze(0).clone() if (init_l is None or init_l[i]) else None
+        for j, a in enumerate(range(0, n, page)):
+            b = min(a + page, n)
+            sl = slice(pos + a, pos + b)
+            oi, S = chunk_gated_delta_rule(q=q[sl].unsqueeze(0), k=k[sl].unsqueeze(0), v=v[sl].unsqueeze(0), g=g[sl].unsqueeze(0),
+                                           beta=beta[sl].unsqueeze(0), scale=scale, initial_state=S, output_final_state=True,
+                                           use_qk_l2norm_in_kernel=l2norm)
+            o[sl] = oi[0]
+            if b - a == page:
+                snaps[offsets[i] + j] = S[0]
+        if n > 0:
+            state_table[slot_l[i]] = S[0]
+        pos += n
+    return o, snaps[:offsets[-1]], offsets[:-1]
+
+
 @torch.no_grad()
 def packed_gated_delta_prefill(q, k, v, g, beta, cu_seqlens, state_table, slots, has_initial=None, scale=1.0,
                                use_qk_l2norm_in_kernel=True, snapshot_every=None, seqlens=None):
@@ -180,13 +211,15 @@ def packed_gated_delta_prefill(q, k, v, g, beta, cu_seqlens, state_table, slots,
     sequence: (o, snapshots (n_pages_total, H, dk, dv) fp32, page_offsets list) where sequence
     i's j-th page boundary is row page_offsets[i] + j.  With these a request that reuses cached
     K/V pages can start its memory from the matching state instead of from zero
-    (16-bit inputs with dk = dv = 128 only)."""
+    (one kernel pass for 16-bit inputs with dk = dv = 128; other inputs are scanned page by page)."""
     _lib.require_cuda(q, "packed_gated_delta_prefill")
     dk, dv = q.shape[-1], v.shape[-1]
     if snapshot_every is not None:
-        if not _varlen_supported(q, dk, dv) or seqlens is None or snapshot_every % 64 != 0:
-            raise ValueError("state snapshots need 16-bit inputs with dk = dv = 128, the host-side seqlens and a "
-                             "spacing that is a multiple of 64 tokens")
+        if seqlens is None or snapshot_every % 64 != 0:
+            raise ValueError("state snapshots need the host-side seqlens and a spacing that is a multiple of 64 tokens")
+        if not _varlen_supported(q, dk, dv):
+            return _packed_prefill_snapshots_by_page(q, k, v, g, beta, seqlens, state_table, slots, has_initial, scale,
+                                                     use_qk_l2norm_in_kernel, snapshot_every)
         counts = [int(n) // snapshot_every for n in seqlens]
         offsets = [0]
         for cnt in counts:

@@ -30,7 +30,11 @@ from dataclasses import dataclass, field
 import torch
 import torch.nn.functional as F
 
-from .gated_delta import gated_delta_decode_step, gated_delta_decode_step_fused
+import hashlib
+
+from .gated_delta import gated_delta_decode_step, gated_delta_decode_step_fused, packed_gated_delta_prefill
+from .inference_ops import qkv_prep_prefill, sigmoid_gate_mul
+from .polar import polar_attention_fwd
 from .inference_ops import (add_rms_norm, lfm2_conv_decode_step, lfm2_conv_packed, qkv_prep_decode, rms_sigmoid_gate,
                             softcap_logits, squared_relu_gate)
 from .layer import PackedMaps, global_attention_prefill_packed
@@ -117,13 +121,26 @@ class AtmaModel:
 
     # ---- packed prefill of fresh prompts ----------------------------------------------------------------------
     @torch.no_grad()
-    def prefill(self, ids, seqlens, slots, state, slot_mapping):
+    def prefill(self, ids, seqlens, slots, state, slot_mapping, maps=None, snapshot_every=None):
         """ids (tokens,) packed prompts; seqlens / slots per sequence (host lists); slot_mapping (tokens,) cache rows.
-        Conv states, memory states and K/V pages of ``state`` are written at the sequences' slots.
-        Returns the final-norm hidden states of all tokens (tokens, D)."""
+        Conv states, memory states and K/V pages of ``state`` are written at the sequences' slots.  ``maps``: the
+        batch's ``PackedMaps`` if the caller has built them already.
+        Returns the final-norm hidden states of all tokens (tokens, D).
+
+        ``snapshot_every`` (tokens; the K/V page size, a multiple of 64): also returns a ``PrefixSnapshots`` with the
+        recurrent state of every layer after each full page of each sequence - the fp32 memory state and the last
+        K-1 conv inputs - so that a later request whose prompt shares those pages can continue from them
+        (``prefill_from_prefix``) instead of inheriting K/V without state, which the reference documents as a
+        source of drift (docs/inference.md:72-75; inference/models/atma.py:477-479)."""
         sd = self.sd
-        maps = PackedMaps(seqlens, slots, self.device)
+        if maps is None:
+            maps = PackedMaps(seqlens, slots, self.device)
         sm = slot_mapping.to(self.device, torch.int64)
+        snaps = None
+        if snapshot_every is not None:
+            if snapshot_every % 64 != 0:
+                raise ValueError("snapshot_every must be a multiple of 64 tokens")
+            snaps = PrefixSnapshots(seqlens, snapshot_every, maps.cu_seqlens.tolist(), self.device)
         x = sd["embed.weight"][ids.to(self.device)]
         x, h = add_rms_norm(x, None, sd["blocks.0.norm1.weight"], self.eps)
         for i in range(self.L):
@@ -134,11 +151,78 @@ class AtmaModel:
                     conv_states=[state.conv[f"attn_{i}_{n}"] for n in ("q", "k", "v")], mem_state_table=state.mem[i],
                     k_cache=state.k_cache[i].view(-1, self.Hkv, self.dk), v_cache=state.v_cache[i].view(-1, self.Hkv, self.dk),
                     slot_mapping=sm, window=self.window, mem_gamma_bias=self.gamma_bias, mem_beta_bias=self.beta_bias,
-                    prefix=P + "attn.", has_initial=False)
+                    prefix=P + "attn.", has_initial=False, snapshots=None if snaps is None else (snaps, i, seqlens))
             else:
                 proj = self._lin(h, P + "attn.in_proj")
                 y = lfm2_conv_packed(proj, sd[P + "attn.conv.weight"].squeeze(1), state.conv[f"conv_{i}"],
                                      maps.token_seq_starts, maps.token_seq_ends, maps.token_seq_slots)
+                if snaps is not None:                   # the conv's inputs B * x' at the rows before each page boundary
+                    rows = snaps.rows(self.conv_k - 1)
+                    gated = proj[rows, :self.D] * proj[rows, 2 * self.D:]
+                    snaps.conv[f"conv_{i}"] = gated.view(-1, self.conv_k - 1, self.D).transpose(1, 2).contiguous()
+                mix = self._lin(y, P + "attn.out_proj")
+            x, h = add_rms_norm(x, mix, sd[P + "norm2.weight"], self.eps)
+            nxt = sd[f"blocks.{i + 1}.norm1.weight"] if i + 1 < self.L else sd["norm.weight"]
+            x, h = add_rms_norm(x, self._mlp(h, i), nxt, self.eps)
+        return h if snaps is None else (h, snaps)
+
+    @torch.no_grad()
+    def prefill_from_prefix(self, ids_tail, prefix_len, slot, state, slot_mapping_tail, block_table_row, snapshots, index):
+        """The rest of ONE prompt whose first ``prefix_len`` tokens (whole pages) are already in the K/V pages that
+        ``block_table_row`` points to - cached by an earlier request - with the recurrent state of that prefix taken
+        from ``snapshots[index]`` (``PrefixSnapshots``; ``index`` = the page-boundary row, e.g. from
+        ``PrefixStateCache.lookup``).  The sequence's rows in the state tables are set from the snapshot, the tail's
+        K/V rows go to ``slot_mapping_tail``, attention sees prefix + tail keys (what the reference's chunked-prefill
+        continuation does, inference/models/atma.py:509-538).  Returns the tail's final-norm hidden states (T, D)."""
+        sd, H, Hkv, dk = self.sd, self.H, self.Hkv, self.dk
+        dev = self.device
+        T = ids_tail.shape[0]
+        maps = PackedMaps([T], [slot], dev)
+        sm = slot_mapping_tail.to(dev, torch.int64)
+        bs = next(iter(state.k_cache.values())).shape[1]
+        if prefix_len % bs != 0:
+            raise ValueError("a reused prefix must end at a page boundary")
+        pages = block_table_row[:prefix_len // bs].to(dev, torch.long)
+        n_keys = torch.arange(prefix_len + 1, prefix_len + T + 1, device=dev, dtype=torch.float32)
+        one = torch.ones(1, dtype=torch.int32, device=dev)
+        x = sd["embed.weight"][ids_tail.to(dev)]
+        x, h = add_rms_norm(x, None, sd["blocks.0.norm1.weight"], self.eps)
+        for i in range(self.L):
+            P = f"blocks.{i}."
+            if i in self.global_layers:
+                A = P + "attn."
+                tabs = [state.conv[f"attn_{i}_{n}"] for n in ("q", "k", "v")]
+                inits = []
+                for n, tab in zip(("q", "k", "v"), tabs):                # the prefix's conv state: left context of the tail
+                    init = torch.zeros_like(tab)
+                    init[slot] = snapshots.conv[f"attn_{i}_{n}"][index]
+                    inits.append(init)
+                state.mem[i][slot] = snapshots.mem[i][index]
+                q_gate = self._lin(h, A + "q").view(T, H, 2 * dk)
+                k = self._lin(h, A + "k").view(T, Hkv, dk)
+                v = self._lin(h, A + "v").view(T, Hkv, dk)
+                q, k, v = qkv_prep_prefill(q_gate, k, v, *(sd[A + f"canon_{n}.weight"].squeeze(1) for n in ("q", "k", "v")), *tabs,
+                                           maps.token_seq_starts, maps.token_seq_ends, maps.token_seq_slots,
+                                           state.k_cache[i].view(-1, Hkv, dk), state.v_cache[i].view(-1, Hkv, dk), sm,
+                                           initial_states=inits)
+                k_all = torch.cat([state.k_cache[i][pages].reshape(-1, Hkv, dk), k])     # cached prefix rows + the tail's
+                v_all = torch.cat([state.v_cache[i][pages].reshape(-1, Hkv, dk), v])
+                c, mag = polar_attention_fwd(q.transpose(0, 1)[None], k_all.transpose(0, 1)[None], v_all.transpose(0, 1)[None],
+                                             n_keys, is_causal=False, window=self.window,
+                                             **{n: sd[A + n] for n in POLAR_NAMES})
+                gated = sigmoid_gate_mul(c[0].transpose(0, 1), q_gate[..., dk:]).view(T, H * dk)
+                mix = self._lin(gated, A + "proj") + self._lin(mag[0].transpose(0, 1), A + "mu_proj")
+                g = F.logsigmoid(self._lin(h, A + "mem.w_gamma").float() + self.gamma_bias)
+                beta = torch.sigmoid(self._lin(h, A + "mem.w_beta").float() + self.beta_bias)
+                r = packed_gated_delta_prefill(q, k, v, g, beta, maps.cu_seqlens, state.mem[i], maps.seq_slots, one)
+                mix = mix + self._lin(rms_sigmoid_gate(r, self._lin(h, A + "mem.gate")), A + "mem.proj")
+            else:
+                tab = state.conv[f"conv_{i}"]
+                init = torch.zeros_like(tab)
+                init[slot] = snapshots.conv[f"conv_{i}"][index]
+                proj = self._lin(h, P + "attn.in_proj")
+                y = lfm2_conv_packed(proj, sd[P + "attn.conv.weight"].squeeze(1), tab, maps.token_seq_starts,
+                                     maps.token_seq_ends, maps.token_seq_slots, initial_state=init)
                 mix = self._lin(y, P + "attn.out_proj")
             x, h = add_rms_norm(x, mix, sd[P + "norm2.weight"], self.eps)
             nxt = sd[f"blocks.{i + 1}.norm1.weight"] if i + 1 < self.L else sd["norm.weight"]
@@ -204,6 +288,112 @@ class AtmaModel:
                         (self.L - len(self.global_layers)) * self.D * (self.conv_k - 1))
         act = 2 * self.D * 2
         return n_w + batch * (kv + mem + conv + act)
+
+
+class PrefixSnapshots:
+    """Recurrent state of every layer at the page boundaries of a packed prefill.  Row r of every tensor belongs
+    to one (sequence, page boundary): sequence i's j-th full page is row ``offsets[i] + j`` (j = 0 is the state
+    after the first ``page`` tokens).  ``mem[layer]`` (rows, H, dk, dk) fp32; ``conv[name]`` (rows, C, K-1) in the
+    conv-state tables' layout (oldest input first)."""
+
+    def __init__(self, seqlens, page, cu_seqlens, device):
+        self.page = page
+        counts = [int(n) // page for n in seqlens]
+        self.offsets = [0]
+        for c in counts:
+            self.offsets.append(self.offsets[-1] + c)
+        self.n_rows = self.offsets.pop()
+        self.ends = [cu_seqlens[i] + (j + 1) * page for i, c in enumerate(counts) for j in range(c)]   # packed token index after each page
+        self.device = device
+        self.mem, self.conv = {}, {}
+
+    def rows(self, k_minus_1):
+        """Packed token indices of the last K-1 inputs before every page boundary, oldest first (rows * (K-1),)."""
+        ends = torch.tensor(self.ends, dtype=torch.long, device=self.device)
+        return (ends[:, None] + torch.arange(-k_minus_1, 0, device=self.device)[None, :]).reshape(-1)
+
+
+class PrefixStateCache:
+    """Which snapshot goes with which cached page: the bookkeeping an engine keeps beside its block manager's
+    hash table.  A page is named by the chained hash of the token ids up to and including it (the scheme of the
+    reference's block manager, inference/engine/block_manager.py:42-57); ``register`` files the snapshot rows of a
+    finished prefill under those names, ``lookup`` returns the longest run of leading pages of a new prompt that
+    has both K/V pages and state on record."""
+
+    def __init__(self, page):
+        self.page = page
+        self.table = {}                       # chained page hash -> (snapshots, row, physical page id)
+
+    @staticmethod
+    def _chain(prev, token_ids):
+        h = hashlib.blake2b(digest_size=8)
+        h.update(prev.to_bytes(8, "little"))
+        h.update(torch.as_tensor(token_ids, dtype=torch.int64).numpy().tobytes())
+        return int.from_bytes(h.digest(), "little")
+
+    def page_hashes(self, token_ids):
+        out, prev = [], 0
+        for j in range(len(token_ids) // self.page):
+            prev = self._chain(prev, token_ids[j * self.page:(j + 1) * self.page])
+            out.append(prev)
+        return out
+
+    def register(self, token_ids, snapshots, seq_index, block_table_row):
+        for j, hsh in enumerate(self.page_hashes(token_ids)):
+            self.table.setdefault(hsh, (snapshots, snapshots.offsets[seq_index] + j, int(block_table_row[j])))
+
+    def lookup(self, token_ids):
+        """(n_pages, physical page ids, snapshots, row of the last shared page) or (0, [], None, None).  At least one
+        token of the prompt is left for the tail."""
+        hit = []
+        for hsh in self.page_hashes(token_ids[:max(len(token_ids) - 1, 0)]):
+            if hsh not in self.table:
+                break
+            hit.append(self.table[hsh])
+        if not hit:
+            return 0, [], None, None
+        return len(hit), [p for _, _, p in hit], hit[-1][0], hit[-1][1]
+
+
+def random_state_dict(*, layers, hidden, head_dim, num_kv_heads, vocab, seed, device, dtype=torch.bfloat16, kernel_attn=4,
+                      kernel_conv=3):
+    """Random weights in the reference's key layout (model/reference.py:236-262), drawn on the device: the default
+    initialisation's distributions (uniform +-1/sqrt(fan_in) for linears and convs, ones for norms, the Polar
+    constants of model/reference.py:17-20), except that ``mem.proj`` is random instead of zero so that the memory
+    branch contributes.  For benchmarks - checkpoints load through ``AtmaModel(state_dict, ...)`` directly."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    H, dk, Hkv, D = hidden // head_dim, head_dim, num_kv_heads, hidden
+    sd = {}
+
+    def uni(shape, fan):
+        return ((torch.rand(*shape, device=device, generator=g) * 2 - 1) * fan ** -0.5).to(dtype)
+
+    def lin(name, out_f, in_f):
+        sd[name + ".weight"], sd[name + ".bias"] = uni((out_f, in_f), in_f), uni((out_f,), in_f)
+
+    sd["embed.weight"] = torch.randn(vocab, D, device=device, generator=g).to(dtype)
+    for i in range(layers):
+        P = f"blocks.{i}."
+        if i % 4 == 2:
+            lin(P + "attn.q", 2 * H * dk, D); lin(P + "attn.k", Hkv * dk, D); lin(P + "attn.v", Hkv * dk, D)
+            for n, C in (("q", H * dk), ("k", Hkv * dk), ("v", Hkv * dk)):
+                sd[P + f"attn.canon_{n}.weight"] = uni((C, 1, kernel_attn), kernel_attn)
+            lin(P + "attn.proj", D, H * dk); lin(P + "attn.mu_proj", D, H)
+            sd[P + "attn.v_null"] = torch.zeros(H, dk, device=device)
+            for n, val in (("null_base", 2.0), ("null_slope_raw", 0.5), ("len_gain_raw", -1.0), ("mag_beta_raw", -1.5)):
+                sd[P + "attn." + n] = torch.full((H,), val, device=device)
+            lin(P + "attn.mem.w_gamma", H, D); lin(P + "attn.mem.w_beta", H, D); lin(P + "attn.mem.gate", H * dk, D)
+            lin(P + "attn.mem.proj", D, H * dk)
+        else:
+            lin(P + "attn.in_proj", 3 * D, D)
+            sd[P + "attn.conv.weight"] = uni((D, 1, kernel_conv), kernel_conv)
+            lin(P + "attn.out_proj", D, D)
+        lin(P + "mlp.fc", 8 * D, D); lin(P + "mlp.proj", D, 4 * D)
+        sd[P + "norm1.weight"] = torch.ones(D, device=device, dtype=dtype)
+        sd[P + "norm2.weight"] = torch.ones(D, device=device, dtype=dtype)
+    lin("proj", vocab, D)
+    sd["norm.weight"] = torch.ones(D, device=device, dtype=dtype)
+    return sd
 
 
 class CapturedDecode:

@@ -186,28 +186,28 @@ def bench_decode(ab, device, steps, warmup, peaks):
     def step():
         ab.store_kvcache(kn, vn, k_cache, v_cache, slot_map)
         c, mag = ab.polar_attention_decode(q, k_cache, v_cache, bt, cl, **params)
-        ke = kn.repeat_interleave(H // HKV, dim=1)
-        ve = vn.repeat_interleave(H // HKV, dim=1)
-        r = ab.gated_delta_decode_step(q, ke, ve, gamma, beta, state, slots)
+        r = ab.gated_delta_decode_step_fused(q, kn, vn, state, slots, gamma=gamma, beta=beta)   # un-expanded KV heads
         return c, mag, r
 
     for _ in range(warmup):
         step()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    pe = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    pe = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(steps)]
     e0.record()
     for i in range(steps):
         ab.store_kvcache(kn, vn, k_cache, v_cache, slot_map)
         pe[i][0].record()
         ab.polar_attention_decode(q, k_cache, v_cache, bt, cl, **params)
         pe[i][1].record()
-        ab.gated_delta_decode_step(q, kn.repeat_interleave(H // HKV, dim=1), vn.repeat_interleave(H // HKV, dim=1),
-                                   gamma, beta, state, slots)
+        pe[i][2].record()
+        ab.gated_delta_decode_step_fused(q, kn, vn, state, slots, gamma=gamma, beta=beta)
+        pe[i][3].record()
     e1.record()
     torch.cuda.synchronize()
     eager_ms = e0.elapsed_time(e1) / steps
-    polar_ms = sum(a.elapsed_time(b) for a, b in pe) / steps
+    polar_ms = sum(e[0].elapsed_time(e[1]) for e in pe) / steps
+    mem_step_ms = sum(e[2].elapsed_time(e[3]) for e in pe) / steps
     # the step as the engine runs it: captured once, replayed (inference/engine/model_runner.py:254-310)
     ms, graphed = eager_ms, False
     try:
@@ -244,6 +244,9 @@ def bench_decode(ab, device, steps, warmup, peaks):
                      # algorithmic; a sharded batch scales it by its cache bytes.
                      "traffic": kv_bytes * DECODE_TRAFFIC_RATIO,
                      "algorithmic_bytes": kv_bytes, "kernel_ms": polar_ms, "peak_source": peaks["source"]},
+        "memory_step": {"kernel": "gated_delta_step_wide_kernel", "kernel_ms": mem_step_ms, "algorithmic_bytes": state_bytes,
+                        "achieved": state_bytes / (mem_step_ms * 1e-3) / 1e9, "unit": "GB/s",
+                        "frac": state_bytes / (mem_step_ms * 1e-3) / 1e9 / peaks["hbm"]},
         "step_bytes": kv_bytes + state_bytes,
         "step_hbm_frac": (kv_bytes + state_bytes) / (ms * 1e-3) / 1e9 / peaks["hbm"],
     }
@@ -747,6 +750,93 @@ def bench_config3(ab, device, peaks):
             "l2": "inputs (805 MB) larger than L2"}
 
 
+MODEL = dict(layers=16, hidden=1024, head_dim=128, num_kv_heads=2)
+VOCAB = 50304
+
+
+def bench_model_decode(device, peaks, steps=20):
+    """BASELINE config 4 on one GPU: the whole 16-layer model (12 LFM2 conv + 4 Polar/gated-delta layers, 378M
+    random-init bf16 weights, seed 3), one decode step for 64 sequences with 32,768 tokens of context each in the
+    paged cache (256-token pages in shuffled order), replayed from one CUDA graph."""
+    from atma_b200.model import AtmaModel, CapturedDecode, random_state_dict
+    sd = random_state_dict(vocab=VOCAB, seed=3, device=device, **MODEL)
+    model = AtmaModel(sd, device=device, **MODEL)
+    del sd
+    B, ctx, bs = DEC_B, DEC_CTX, DEC_BLOCK
+    pages = ctx // bs
+    state = model.new_state(max_seqs=B, num_blocks=B * pages, block_size=bs)
+    g = torch.Generator(device=device).manual_seed(3)
+    for i in model.global_layers:
+        state.k_cache[i].normal_(generator=g)
+        state.v_cache[i].normal_(generator=g)
+        state.mem[i].normal_(generator=g).mul_(0.1)
+    bt = torch.randperm(B * pages, generator=torch.Generator().manual_seed(3)).int().view(B, pages).to(device)
+    cap = CapturedDecode(model, state, batch=B, max_blocks=pages)
+    cap.ids.copy_(torch.randint(0, VOCAB, (B,), generator=torch.Generator().manual_seed(3)).to(device))
+    cap.block_tables.copy_(bt)
+    cap.context_lens.fill_(ctx)
+    cap.slot_mapping.copy_((bt[:, -1].long() * bs + bs - 1).int())
+    cap.capture()
+    for _ in range(3):
+        cap.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        cap.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    nbytes = float(model.decode_bytes(B, ctx))
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    finite = bool(torch.isfinite(cap.logits.float()).all())
+    return {"workload": f"BASELINE config 4: full model (16 layers, 4 global), decode of {B} sequences x {ctx} tokens of context, "
+                        f"pages of {bs}", "ms_per_step": ms, "value": B / (ms * 1e-3), "unit": "tok/s", "steps": steps,
+            "cuda_graph": True, "logits_finite": finite, "algorithmic_bytes": nbytes,
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s", "frac": gbs / peaks["hbm"]},
+            "projections": "cuBLAS (F.linear); everything between them this library"}
+
+
+def bench_model_prefill(device, peaks, tokens=262144, steps=2):
+    """BASELINE config 5 on one GPU: the whole model, one prompt of 262,144 uniform token ids, prefilled in one pass
+    (packed-prefill path with a single sequence); last-token logits computed."""
+    from atma_b200.layer import PackedMaps
+    from atma_b200.model import AtmaModel, random_state_dict
+    sd = random_state_dict(vocab=VOCAB, seed=4, device=device, **MODEL)
+    model = AtmaModel(sd, device=device, **MODEL)
+    del sd
+    bs = DEC_BLOCK
+    pages = tokens // bs
+    state = model.new_state(max_seqs=1, num_blocks=pages, block_size=bs)
+    ids = torch.randint(0, VOCAB, (tokens,), generator=torch.Generator().manual_seed(4)).to(device)
+    bt = torch.randperm(pages, generator=torch.Generator().manual_seed(4))
+    pos = torch.arange(tokens)
+    sm = (bt[pos // bs] * bs + pos % bs).to(device)
+    maps = PackedMaps([tokens], [0], device)
+
+    def step():
+        h = model.prefill(ids, [tokens], [0], state, sm, maps=maps)
+        return model.logits(h[-1:])
+
+    logits = step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        logits = step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    n_body = sum(t.numel() for n, t in model.sd.items() if n not in ("embed.weight", "proj.weight", "proj.bias"))
+    fl = len(model.global_layers) * polar_flops(tokens) + 2.0 * n_body * tokens + len(model.global_layers) * scan_flops(tokens)
+    tf = fl / (ms * 1e-3) / 1e12
+    return {"workload": f"BASELINE config 5 on one GPU: full model, one {tokens}-token prompt", "ms_per_step": ms,
+            "value": tokens / (ms * 1e-3), "unit": "tok/s", "steps": steps, "algorithmic_flops": fl,
+            "logits_finite": bool(torch.isfinite(logits.float()).all()),
+            "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["tf_sustained"], "unit": "TFLOP/s",
+                         "frac": tf / peaks["tf_sustained"], "peak_source": peaks["source"] + " sustained (a step is ~0.7 s long)"}}
+
+
 _REAL_STDOUT = None
 
 
@@ -779,6 +869,7 @@ def main():
     ap.add_argument("--skip-decode", action="store_true", help="omit the decode leg (profiling runs)")
     ap.add_argument("--skip-long", action="store_true", help="N > 1: omit the 262,144-token leg")
     ap.add_argument("--skip-configs", action="store_true", help="N = 1: omit the BASELINE config 2 / config 3 legs")
+    ap.add_argument("--skip-model", action="store_true", help="N = 1: omit the full-model legs (BASELINE configs 4 and 5)")
     ap.add_argument("--profile", default=None, choices=["prefill", "decode", "scan", "prep", "epilogue"],
                     help="run a few launches of ONE kernel on a small case (a few hundred MB, larger than L2) "
                          "and exit; meant to be wrapped in ncu")
@@ -891,6 +982,12 @@ def main():
         torch.cuda.empty_cache()
         config3 = bench_config3(ab, device, peaks)
         torch.cuda.empty_cache()
+    config4 = config5 = None
+    if rank == 0 and not args.skip_model and T_PREFILL == 65536:
+        config4 = bench_model_decode(device, peaks)
+        torch.cuda.empty_cache()
+        config5 = bench_model_prefill(device, peaks)
+        torch.cuda.empty_cache()
     cpu = None
     if rank == 0 and world == 1 and not args.skip_cpu:
         threads = os.cpu_count() or 1
@@ -951,6 +1048,8 @@ def main():
         "decode": decode,
         "config2": config2,
         "config3": config3,
+        "config4_model_decode": config4,
+        "config5_model_prefill_1gpu": config5,
     }
     emit(line)
 

@@ -218,3 +218,49 @@ def test_add_rms_norm(dtype, D):
     assert max_rel(h, h_ref) < (1e-2 if dtype != torch.float32 else 1e-6)
     x2, h2 = atma_b200.add_rms_norm(x, None, None, 1e-6)
     assert x2 is x and max_rel(h2, F.rms_norm(x.float(), (D,), eps=1e-6)) < (1e-2 if dtype != torch.float32 else 1e-6)
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-4), (torch.bfloat16, 2e-2)])
+def test_prefix_hit_from_another_request_equals_full_recompute(golden, dtype, tol):
+    """Request A is prefilled with state snapshots at every page boundary and registered in the prefix cache.
+    Request B shares A's first two pages and then differs.  B served from the cache - A's K/V pages in its block
+    table, conv and memory state from the page-2 snapshot, only the tail prefilled - gives the logits and final
+    states of B prefilled from scratch (the reference inherits the K/V but not the state there, docs/inference.md:72-75)."""
+    from atma_b200.model import PrefixStateCache
+    model, ids, _ = _model(golden, dtype)
+    page = 64
+    gen = torch.Generator().manual_seed(11)
+    a_ids = torch.randint(0, 640, (200,), generator=gen)
+    b_ids = torch.cat([a_ids[:2 * page], torch.randint(0, 640, (75,), generator=gen)])
+    n_a, n_b = a_ids.numel(), b_ids.numel()
+    state = model.new_state(max_seqs=4, num_blocks=16, block_size=page)
+    rows_of = lambda table, n: (table[torch.arange(n) // page].long() * page + torch.arange(n) % page)
+    bt_a = torch.tensor([5, 2, 9, 0])
+    _, snaps = model.prefill(a_ids, [n_a], [0], state, rows_of(bt_a, n_a), snapshot_every=page)
+    cache = PrefixStateCache(page)
+    cache.register(a_ids.tolist(), snaps, 0, bt_a)
+    # B from scratch, in its own pages and slot
+    bt_full = torch.tensor([11, 12, 13, 14, 15])
+    h_full = model.prefill(b_ids, [n_b], [1], state, rows_of(bt_full, n_b))
+    logits_full = model.logits(h_full)
+    # B through the cache
+    n_pages, phys, hit_snaps, row = cache.lookup(b_ids.tolist())
+    assert n_pages == 2 and phys == [5, 2] and hit_snaps is snaps
+    bt_b = torch.tensor(phys + [7, 8, 3])
+    tail = torch.arange(n_pages * page, n_b)
+    sm_tail = bt_b[tail // page].long() * page + tail % page
+    h_tail = model.prefill_from_prefix(b_ids[n_pages * page:], n_pages * page, 2, state, sm_tail, bt_b, hit_snaps, row)
+    logits_tail = model.logits(h_tail)
+    err = max_abs if dtype == torch.float32 else max_rel
+    assert err(logits_tail, logits_full[n_pages * page:]) < tol
+    for name, tab in state.conv.items():
+        assert err(tab[2], tab[1]) < tol, name
+    for i, tab in state.mem.items():
+        assert err(tab[2], tab[1]) < tol, i
+    # and the snapshot itself is the state of a prefill that stops at the page boundary
+    st2 = model.new_state(max_seqs=1, num_blocks=4, block_size=page)
+    model.prefill(a_ids[:2 * page], [2 * page], [0], st2, torch.arange(2 * page))
+    for name, tab in st2.conv.items():
+        assert err(snaps.conv[name][1], tab[0]) < tol, name
+    for i, tab in st2.mem.items():
+        assert err(snaps.mem[i][1], tab[0]) < tol, i
