@@ -87,6 +87,14 @@ class CudaBackend:
         from .polar import _params
         return _params(device=device, **params)
 
+    def decode_partials(self, q, k_cache, v_cache, block_tables, local_lens, total_lens, params, eps):
+        from .polar import polar_decode_partials
+        return polar_decode_partials(q, k_cache, v_cache, block_tables, local_lens, total_lens, params, eps=eps)
+
+    def decode_merge(self, stats, sums, total_lens, params, dtype, eps):
+        from .polar import polar_decode_merge
+        return polar_decode_merge(stats, sums, total_lens, params, dtype, eps=eps)
+
 
 def _exchange(send_buf, recv_buf, rank, world, group):
     """Post the ring hop: my current K/V block goes to rank+1 while rank-1's arrives."""
@@ -259,6 +267,28 @@ def cp_gated_delta_scan(q_parts, k_parts, v_parts, g_parts, beta_parts, *, backe
     my_states = torch.stack([S_in[rank], S_in[2 * world - 1 - rank]]).contiguous()
     o, _ = backend.scan_recur(factors, [0, 1], my_states, None, want_output=True)
     return [o[0:1], o[1:2]], S_final
+
+
+@torch.no_grad()
+def cp_polar_decode(q, k_cache, v_cache, block_tables, local_lens, total_lens, params, *, backend=None, group=None, eps=1e-6):
+    """One decode step of Polar attention for sequences whose K/V were prefilled context-parallel: every rank
+    holds the pages of its own segments and the same query q (B,H,dk).  Each rank reduces the keys of ITS cache
+    (``local_lens`` (B,) of them, reached through ``block_tables``) to partial statistics (m, L, sum p^2, sum p v),
+    one small all-gather shares them, and every rank merges all partials with the rule of the single-GPU kernel
+    (L and the sums scale by e^(m_i - m), the squares by its square; the null sink is folded once, for the whole
+    context of ``total_lens`` keys).  The single-device statement of the same computation is the reference's
+    paged decode, kernel/polar_triton.py:796-858.  Full-context attention only (no window).
+    Returns c (B,H,dk), mag (B,H) on every rank."""
+    backend = backend or CudaBackend()
+    world = dist.get_world_size(group)
+    prepared = backend.prepare_params(params, q.device)
+    stats, sums = backend.decode_partials(q, k_cache, v_cache, block_tables, local_lens, total_lens, prepared, eps)
+    B, H, P, dk = sums.shape
+    mine = torch.cat([stats, sums], dim=-1).contiguous()                        # (B, H, P, 4 + dk)
+    gathered = torch.empty((world * B, H, P, 4 + dk), dtype=mine.dtype, device=mine.device)
+    dist.all_gather_into_tensor(gathered, mine, group=group)
+    allp = gathered.view(world, B, H, P, 4 + dk).permute(1, 2, 0, 3, 4).reshape(B, H, world * P, 4 + dk)     # every rank's partials side by side
+    return backend.decode_merge(allp[..., :4].contiguous(), allp[..., 4:].contiguous(), total_lens, prepared, q.dtype, eps)
 
 
 @torch.no_grad()

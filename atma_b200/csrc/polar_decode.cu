@@ -58,7 +58,7 @@ template <typename T, int DK, int GMAX>
 __global__ void __launch_bounds__(kDecWarps * 32)
 polar_decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
                           const T* __restrict__ v_cache, const int32_t* __restrict__ block_tables,
-                          int64_t bt_stride, const int32_t* __restrict__ context_lens,
+                          int64_t bt_stride, const int32_t* __restrict__ context_lens, const int32_t* __restrict__ temp_lens,
                           const float* __restrict__ spg, float* __restrict__ scratch, int B, int H,
                           int Hkv, int block_size, int max_blocks, int num_blocks, int n_splits,
                           int window) {
@@ -95,7 +95,8 @@ polar_decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache
     return;
   }
 
-  const float nf = fmaxf(window > 0 ? fminf((float)n, (float)window) : (float)n, 1.0f);
+  const int nt = temp_lens != nullptr ? temp_lens[b] : n;      // the whole context sets the temperature
+  const float nf = fmaxf(window > 0 ? fminf((float)nt, (float)window) : (float)nt, 1.0f);
   const float logn = logf(nf);
   const float inv_sqrt_dk = rsqrtf((float)DK);
 
@@ -317,7 +318,7 @@ int launch_decode(const atma_polar_decode_args& a, cudaStream_t st) {
   const int G = a.H / a.Hkv;
   if (polar_decode_mma_supported(a)) {
     int rc = polar_decode_split_mma(a, st);
-    if (rc != ATMA_OK) return rc;
+    if (rc != ATMA_OK || a.skip_merge) return rc;
     polar_decode_merge_kernel<T><<<a.B * a.H, 64, 0, st>>>(
         a.scratch, a.context_lens, a.v_null, a.spg, a.null_base, a.sps, a.beta, (T*)a.c, (T*)a.mag,
         a.B, a.H, a.dk, a.n_splits, a.window, a.max_blocks * a.block_size, a.eps, (const T*)a.gate, a.gate_sb, a.gate_sh,
@@ -327,7 +328,7 @@ int launch_decode(const atma_polar_decode_args& a, cudaStream_t st) {
 #define ATMA_LAUNCH(DKK, GM)                                                                    \
   polar_decode_split_kernel<T, DKK, GM><<<grid, block, 0, st>>>(                                \
       (const T*)a.q, (const T*)a.k_cache, (const T*)a.v_cache, a.block_tables, a.bt_stride,     \
-      a.context_lens, a.spg, a.scratch, a.B, a.H, a.Hkv, a.block_size, a.max_blocks,            \
+      a.context_lens, a.temp_lens, a.spg, a.scratch, a.B, a.H, a.Hkv, a.block_size, a.max_blocks,            \
       a.num_blocks, a.n_splits, a.window)
 #define ATMA_CASE(DKK)                                                                          \
   case DKK:                                                                                     \
@@ -341,7 +342,7 @@ int launch_decode(const atma_polar_decode_args& a, cudaStream_t st) {
 #undef ATMA_CASE
 #undef ATMA_LAUNCH
   int rc = launch_status("polar_decode (split)");
-  if (rc != ATMA_OK) return rc;
+  if (rc != ATMA_OK || a.skip_merge) return rc;
   polar_decode_merge_kernel<T><<<a.B * a.H, 64, 0, st>>>(
       a.scratch, a.context_lens, a.v_null, a.spg, a.null_base, a.sps, a.beta, (T*)a.c, (T*)a.mag,
       a.B, a.H, a.dk, a.n_splits, a.window, a.max_blocks * a.block_size, a.eps, (const T*)a.gate, a.gate_sb, a.gate_sh,
@@ -374,6 +375,22 @@ extern "C" int atma_polar_decode(const atma_polar_decode_args* args, void* strea
   int rc = ATMA_OK;
   ATMA_DISPATCH_DTYPE(a.dtype, T, { rc = launch_decode<T>(a, (cudaStream_t)stream); });
   return rc;
+}
+
+extern "C" int atma_polar_decode_merge(const atma_polar_decode_args* args, void* stream) {
+  ATMA_REQUIRE(args != nullptr, "polar_decode_merge: null args");
+  const atma_polar_decode_args& a = *args;
+  ATMA_REQUIRE(dtype_ok(a.dtype), "polar_decode_merge: unsupported dtype %d", a.dtype);
+  ATMA_REQUIRE(a.n_splits >= 1 && a.n_splits <= 4096, "polar_decode_merge: n_splits=%d", a.n_splits);
+  ATMA_REQUIRE(a.scratch != nullptr && a.context_lens != nullptr && a.c != nullptr && a.mag != nullptr, "polar_decode_merge: missing buffers");
+  ATMA_REQUIRE(a.dk >= 1 && a.dk <= 256, "polar_decode_merge: head_dim %d", a.dk);
+  if (a.B <= 0) return ATMA_OK;
+  ATMA_DISPATCH_DTYPE(a.dtype, T, {
+    polar_decode_merge_kernel<T><<<a.B * a.H, 64, 0, (cudaStream_t)stream>>>(
+        a.scratch, a.context_lens, a.v_null, a.spg, a.null_base, a.sps, a.beta, (T*)a.c, (T*)a.mag, a.B, a.H, a.dk, a.n_splits,
+        a.window, 0x7fffffff, a.eps, (const T*)a.gate, a.gate_sb, a.gate_sh, a.c_sb, a.mag_sb);
+  });
+  return launch_status("polar_decode (merge)");
 }
 
 // ---- decode without caller scratch ---------------------------------------------------------

@@ -38,7 +38,7 @@ template <bool kBf16, int DK, int STAGES>
 __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2)
 polar_decode_split_mma_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ k_cache,
                               const uint16_t* __restrict__ v_cache, const int32_t* __restrict__ block_tables,
-                              int64_t bt_stride, const int32_t* __restrict__ context_lens,
+                              int64_t bt_stride, const int32_t* __restrict__ context_lens, const int32_t* __restrict__ temp_lens,
                               const float* __restrict__ spg, float* __restrict__ scratch, int B, int H, int Hkv,
                               int block_size, int max_blocks, int num_blocks, int n_splits, int window) {
   constexpr int KS = DK / 16;                 // k-steps of K Q^T
@@ -132,7 +132,8 @@ polar_decode_split_mma_kernel(const uint16_t* __restrict__ q, const uint16_t* __
     }
   }
   // this thread's two heads: g0 + 2 tq + e
-  const float nf = fmaxf(window > 0 ? fminf((float)n, (float)window) : (float)n, 1.0f);
+  const int nt = temp_lens != nullptr ? temp_lens[b] : n;      // the whole context sets the temperature
+  const float nf = fmaxf(window > 0 ? fminf((float)nt, (float)window) : (float)nt, 1.0f);
   const float logn = logf(nf);
   float sc[2];                                 // log2-domain score scale
 #pragma unroll
@@ -268,7 +269,7 @@ int polar_decode_split_mma(const atma_polar_decode_args& a, cudaStream_t st) {
     auto kern = polar_decode_split_mma_kernel<BF, DKK, kStages>;                                                \
     ATMA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));                \
     kern<<<grid, 128, smem, st>>>((const uint16_t*)a.q, (const uint16_t*)a.k_cache, (const uint16_t*)a.v_cache, \
-                                  a.block_tables, a.bt_stride, a.context_lens, a.spg, a.scratch, a.B, a.H,      \
+                                  a.block_tables, a.bt_stride, a.context_lens, a.temp_lens, a.spg, a.scratch, a.B, a.H,      \
                                   a.Hkv, a.block_size, a.max_blocks, a.num_blocks, a.n_splits, a.window);       \
   } while (0)
   if (a.dtype == ATMA_BF16) { if (a.dk == 128) ATMA_LAUNCH(true, 128); else ATMA_LAUNCH(true, 64); }

@@ -294,3 +294,55 @@ def polar_attention_decode(q, k_cache, v_cache, block_tables, context_lens, *,
     a.dtype, a.window, a.eps = _lib.dtype_code(q), (0 if window is None else int(window)), float(eps)
     _lib.check(lib.atma_polar_decode(byref(a), _lib.stream_ptr()))
     return c, mag
+
+
+@torch.no_grad()
+def polar_decode_partials(q, k_cache, v_cache, block_tables, local_lens, total_lens, params, *, eps=1e-6, num_splits=None):
+    """Key-range pass of the paged decode over the keys of THIS cache only, for a context whose keys are spread
+    over several caches (a sequence prefilled context-parallel over several GPUs).  ``local_lens`` (B,) int32 =
+    keys in this cache, ``total_lens`` (B,) int32 = the whole context (it sets the temperature); ``params`` as
+    returned by ``_params``.  Returns the un-merged statistics (stats (B,H,n,4) = {m, L, Q2, 0}, sums (B,H,n,dk)),
+    fp32; ``polar_decode_merge`` folds any number of them."""
+    _lib.require_cuda(q, "polar_decode_partials")
+    lib = _lib.load()
+    B, H, dk = q.shape
+    num_blocks, block_size, Hkv, _ = k_cache.shape
+    q = q.contiguous()
+    block_tables = block_tables.to(torch.int32).contiguous()
+    local_lens = local_lens.to(torch.int32).contiguous()
+    total_lens = total_lens.to(torch.int32).contiguous()
+    n = num_splits or decode_num_splits(B, Hkv, block_tables.shape[1] * block_size)
+    scratch = torch.empty(int(lib.atma_polar_decode_scratch_floats(B, H, dk, n)), device=q.device, dtype=torch.float32)
+    a = _lib.PolarDecodeArgs()
+    a.q, a.k_cache, a.v_cache = _lib.ptr(q), _lib.ptr(k_cache), _lib.ptr(v_cache)
+    a.block_tables, a.bt_stride, a.context_lens = _lib.ptr(block_tables), block_tables.stride(0), _lib.ptr(local_lens)
+    a.temp_lens, a.skip_merge = _lib.ptr(total_lens), 1
+    a.v_null, a.spg, a.null_base = _lib.ptr(params["v_null"]), _lib.ptr(params["spg"]), _lib.ptr(params["null_base"])
+    a.sps, a.beta, a.scratch = _lib.ptr(params["sps"]), _lib.ptr(params["beta"]), _lib.ptr(scratch)
+    a.B, a.H, a.Hkv, a.dk, a.block_size = B, H, Hkv, dk, block_size
+    a.max_blocks, a.num_blocks, a.n_splits = block_tables.shape[1], num_blocks, n
+    a.dtype, a.window, a.eps = _lib.dtype_code(q), 0, float(eps)
+    _lib.check(lib.atma_polar_decode(byref(a), _lib.stream_ptr()))
+    cut = B * H * n * 4
+    return scratch[:cut].view(B, H, n, 4), scratch[cut:].view(B, H, n, dk)
+
+
+@torch.no_grad()
+def polar_decode_merge(stats, sums, total_lens, params, dtype, *, eps=1e-6):
+    """Merge partial statistics (stats (B,H,P,4), sums (B,H,P,dk)) of one context from any number of caches, fold
+    the null sink for a context of ``total_lens`` keys and emit c (B,H,dk), mag (B,H) in ``dtype``."""
+    lib = _lib.load()
+    B, H, P, dk = sums.shape
+    scratch = torch.cat([stats.reshape(-1), sums.reshape(-1)]).contiguous()
+    total_lens = total_lens.to(torch.int32).contiguous()
+    c = torch.empty((B, H, dk), device=sums.device, dtype=dtype)
+    mag = torch.empty((B, H), device=sums.device, dtype=dtype)
+    a = _lib.PolarDecodeArgs()
+    a.context_lens, a.scratch = _lib.ptr(total_lens), _lib.ptr(scratch)
+    a.v_null, a.spg, a.null_base = _lib.ptr(params["v_null"]), _lib.ptr(params["spg"]), _lib.ptr(params["null_base"])
+    a.sps, a.beta = _lib.ptr(params["sps"]), _lib.ptr(params["beta"])
+    a.c, a.mag = _lib.ptr(c), _lib.ptr(mag)
+    a.B, a.H, a.dk, a.n_splits = B, H, dk, P
+    a.dtype, a.window, a.eps = _lib.DTYPE_CODE[dtype], 0, float(eps)
+    _lib.check(lib.atma_polar_decode_merge(byref(a), _lib.stream_ptr()))
+    return c, mag

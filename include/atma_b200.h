@@ -119,10 +119,22 @@ typedef struct {
    * (0 = dense), so that both can land in one row of a wider activation buffer. */
   const void* gate; int64_t gate_sb, gate_sh;
   int64_t c_sb, mag_sb;
+  /* A context whose keys are spread over several caches (a sequence prefilled context-parallel
+   * over several GPUs): context_lens then counts the keys of THIS cache, temp_lens int32 [B] the
+   * whole context, which sets the per-query temperature (NULL = context_lens); skip_merge != 0
+   * stops after the key-range pass and leaves the partial statistics in `scratch`:
+   * [B*H][n_splits]{m, L, Q2, 0} followed by [B*H][n_splits][dk] sums.  atma_polar_decode_merge
+   * then merges any number of such partials (this cache's and the peers', laid out the same way
+   * with n_splits = their total count) with context_lens = the whole context; it reads scratch,
+   * context_lens, the five parameter arrays, B, H, dk, n_splits, window, dtype, eps and the output
+   * fields.  Windowed attention is not available in this form. */
+  const int32_t* temp_lens;
+  int skip_merge;
 } atma_polar_decode_args;
 
 int64_t atma_polar_decode_scratch_floats(int B, int H, int dk, int n_splits);
 int atma_polar_decode(const atma_polar_decode_args* args, void* stream);
+int atma_polar_decode_merge(const atma_polar_decode_args* args, void* stream);
 
 /* ------------------------------------------------------------------------------------
  * Paged Polar decode for callers that cannot allocate device memory.  (No counterpart in

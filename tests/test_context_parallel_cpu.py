@@ -26,6 +26,35 @@ class OracleBackend:
             return stats
         return polar_finalize(stats, n_keys, eps=eps, window=window, **params)
 
+    def decode_partials(self, q, k_cache, v_cache, block_tables, local_lens, total_lens, params, eps):
+        B, H, dk = q.shape
+        bs = k_cache.shape[1]
+        stats, sums = torch.zeros(B, H, 1, 4), torch.zeros(B, H, 1, dk)
+        for b in range(B):
+            n = int(local_lens[b])
+            pages = block_tables[b, :(n + bs - 1) // bs].long()
+            kk = k_cache[pages].reshape(-1, k_cache.shape[2], dk)[:n].permute(1, 0, 2)[None]
+            vv = v_cache[pages].reshape(-1, k_cache.shape[2], dk)[:n].permute(1, 0, 2)[None]
+            m, L, Q2, S = polar_streaming_stats(q[b][None, :, None, :], kk, vv, torch.tensor([float(total_lens[b])]),
+                                                len_gain_raw=params["len_gain_raw"], tile=8)
+            stats[b, :, 0, 0], stats[b, :, 0, 1], stats[b, :, 0, 2] = m[0, :, 0], L[0, :, 0], Q2[0, :, 0]
+            sums[b, :, 0] = S[0, :, 0]
+        return stats, sums
+
+    def decode_merge(self, stats, sums, total_lens, params, dtype, eps):
+        m = stats[..., 0].amax(-1)                                          # the merge rule of the device kernel
+        w = torch.exp(stats[..., 0] - m[..., None])
+        L = (stats[..., 1] * w).sum(-1)
+        Q2 = (stats[..., 2] * w * w).sum(-1)
+        S = (sums * w[..., None]).sum(-2)
+        cs, ms = [], []
+        for b in range(m.shape[0]):                                         # the null sink depends on each sequence's length
+            c, mag = polar_finalize((m[b:b + 1, :, None], L[b:b + 1, :, None], Q2[b:b + 1, :, None], S[b:b + 1, :, None]),
+                                    total_lens[b:b + 1].float(), eps=eps, **params)
+            cs.append(c[:, :, 0])
+            ms.append(mag[:, :, 0])
+        return torch.cat(cs).to(dtype), torch.cat(ms).to(dtype)
+
     def scan_factors(self, q, k, v, g, beta):
         return (q, k, v, g, beta)
 
@@ -133,3 +162,59 @@ def test_state_prefix_composition():
         assert torch.allclose(states[i], S)
         S = P[i] @ S + Q[i]
     assert torch.allclose(final, S)
+
+
+def _decode_worker(rank, world, port, ret):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.set_num_threads(1)
+        B, H, Hkv, dk, bs, T = 3, 4, 2, 16, 8, 48
+        g = torch.Generator().manual_seed(5)
+        k = torch.randn(B, T, Hkv, dk, generator=g)
+        v = torch.randn(B, T, Hkv, dk, generator=g)
+        q = torch.randn(B, H, dk, generator=g)
+        lens = torch.tensor([48, 31, 17])
+        params = dict(v_null=torch.randn(H, dk, generator=g) * 0.3, null_base=torch.full((H,), 2.0),
+                      null_slope_raw=torch.full((H,), 0.5), len_gain_raw=torch.full((H,), -1.0),
+                      mag_beta_raw=torch.full((H,), -1.5))
+        # this rank's share of every sequence: the zig-zag segments it owns, packed into its own pages
+        segs = cp.zigzag_segments(T, world)[rank]
+        pages_per = T // bs
+        kc, vc = torch.zeros(B * pages_per, bs, Hkv, dk), torch.zeros(B * pages_per, bs, Hkv, dk)
+        bt = torch.arange(B * pages_per).view(B, pages_per).int()
+        local = torch.zeros(B, dtype=torch.int32)
+        for b in range(B):
+            idx = torch.cat([torch.arange(a, min(e, int(lens[b]))) for a, e in segs if a < int(lens[b])] or [torch.zeros(0, dtype=torch.long)])
+            local[b] = idx.numel()
+            flat_k, flat_v = kc.view(-1, Hkv, dk), vc.view(-1, Hkv, dk)
+            base = int(bt[b, 0]) * bs
+            flat_k[base:base + idx.numel()] = k[b, idx]
+            flat_v[base:base + idx.numel()] = v[b, idx]
+        c, mag = cp.cp_polar_decode(q, kc, vc, bt, local, lens.int(), params, backend=OracleBackend())
+        ret[rank] = (c, mag)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_decode_over_a_context_parallel_cache_matches_single_process(world):
+    """Every rank holds the K/V of its own segments; partial statistics are all-gathered and merged: the result is
+    the decode over the whole cache, on every rank (ragged lengths, one sequence shorter than a segment)."""
+    B, H, Hkv, dk, bs, T = 3, 4, 2, 16, 8, 48
+    g = torch.Generator().manual_seed(5)
+    k = torch.randn(B, T, Hkv, dk, generator=g)
+    v = torch.randn(B, T, Hkv, dk, generator=g)
+    q = torch.randn(B, H, dk, generator=g)
+    lens = torch.tensor([48, 31, 17], dtype=torch.int32)
+    params = dict(v_null=torch.randn(H, dk, generator=g) * 0.3, null_base=torch.full((H,), 2.0),
+                  null_slope_raw=torch.full((H,), 0.5), len_gain_raw=torch.full((H,), -1.0),
+                  mag_beta_raw=torch.full((H,), -1.5))
+    kc, vc = k.reshape(B * T // bs, bs, Hkv, dk), v.reshape(B * T // bs, bs, Hkv, dk)
+    bt = torch.arange(B * T // bs).view(B, T // bs).int()
+    c_ref, m_ref = oracle.polar_decode_oracle(q, kc, vc, bt, lens, params)
+    ret = mp.Manager().dict()
+    mp.spawn(_decode_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
+    for rank in range(world):
+        c, mag = ret[rank]
+        assert (c - c_ref).abs().max() < 1e-5 and (mag - m_ref).abs().max() < 1e-5

@@ -86,6 +86,20 @@ def _worker(rank, world, port, ret):
             fed = fed and all(torch.equal(a, b.cpu()) for a, b in zip(got, want))
         ret[f"fed{rank}"] = bool(fed)
         pipe.close()
+        # decode over the context-parallel cache: this rank's K/V rows (its two segments) in its own pages
+        Hkv, dk, bs = shard.k[0].shape[2], shard.k[0].shape[3], 64
+        rows_k = torch.cat([x[0] for x in shard.k])
+        rows_v = torch.cat([x[0] for x in shard.v])
+        n_local = rows_k.shape[0]
+        pages = (n_local + bs - 1) // bs
+        kc = torch.zeros(pages, bs, Hkv, dk, dtype=rows_k.dtype, device=dev)
+        vc = torch.zeros_like(kc)
+        kc.view(-1, Hkv, dk)[:n_local], vc.view(-1, Hkv, dk)[:n_local] = rows_k, rows_v
+        qd = torch.randn(1, shard.q[0].shape[2], dk, generator=torch.Generator().manual_seed(3)).to(dev, rows_k.dtype)
+        cd, md = cp.cp_polar_decode(qd, kc, vc, torch.arange(pages, dtype=torch.int32, device=dev)[None],
+                                    torch.tensor([n_local], dtype=torch.int32, device=dev),
+                                    torch.tensor([n_local * world], dtype=torch.int32, device=dev), pg)
+        ret[f"dec{rank}"] = (cd.float().cpu(), md.float().cpu())
         ret[f"stage{rank}"] = "pipeline released"
     finally:
         dist.destroy_process_group()
@@ -125,3 +139,13 @@ def test_two_rank_context_parallel_matches_one_gpu():
         assert rel(r["S"], S_ref[0]) < 2e-2
         assert ret[f"graph{rank}"], "graph replay differs from the launch-by-launch step (or capture failed)"
         assert ret[f"fed{rank}"], "the host-fed pipeline differs from the launch-by-launch step"
+    # one decode step over the distributed cache == single-GPU paged decode over the whole sequence's K/V
+    qd = torch.randn(1, tg["q"].shape[2], tg["q"].shape[3], generator=torch.Generator().manual_seed(3)).to("cuda", tg["q"].dtype)
+    bs = 64
+    kc = tg["k"][0].reshape(T // bs, bs, *tg["k"].shape[2:]).contiguous()
+    vc = tg["v"][0].reshape(T // bs, bs, *tg["v"].shape[2:]).contiguous()
+    c1, m1 = atma_b200.polar_attention_decode(qd, kc, vc, torch.arange(T // bs, dtype=torch.int32, device="cuda")[None],
+                                              torch.tensor([T], dtype=torch.int32, device="cuda"), **pg)
+    for rank in range(world):
+        cd, md = ret[f"dec{rank}"]
+        assert rel(cd, c1.float().cpu()) < 2e-2 and rel(md, m1.float().cpu()) < 2e-2

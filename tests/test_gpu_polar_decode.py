@@ -154,3 +154,42 @@ def test_decode_step_is_graph_capturable():
     for a, b in zip(got, want):
         assert torch.equal(a, b)
     assert torch.equal(st_g, st_e)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_partials_of_two_caches_merge_to_the_decode_of_the_whole_context(dtype):
+    """A context whose keys lie in two caches (as after a context-parallel prefill): the key-range pass over each
+    cache with the whole length setting the temperature, then one merge of all partials == decode over one cache
+    that holds every key, and == the oracle."""
+    from atma_b200.polar import _params, polar_decode_merge, polar_decode_partials
+    B, H, Hkv, dk, bs = 3, 8, 2, 128, 16
+    lens = [300, 17, 129]
+    k_cache, v_cache, bt, cl = make_paged(B, Hkv, dk, bs, lens, dtype, seed=9)
+    q = rand((B, H, dk), 3, dtype)
+    pc, pg = polar_params(H, dk, 4)
+    c_ref, m_ref = oracle.polar_decode_oracle(q, k_cache, v_cache, bt, cl, pc)
+    # cache A holds the first `cut` keys of every sequence, cache B the rest (own pages, own tables)
+    cuts = [160, 16, 1]
+    parts = []
+    for lo_hi in (lambda n, c: (0, min(c, n)), lambda n, c: (min(c, n), n)):
+        kc, vc = torch.zeros_like(k_cache), torch.zeros_like(v_cache)
+        local = []
+        for b, n in enumerate(lens):
+            lo, hi = lo_hi(n, cuts[b])
+            pages = bt[b, :(n + bs - 1) // bs].long()
+            rows_k = k_cache[pages].reshape(-1, Hkv, dk)[lo:hi]
+            rows_v = v_cache[pages].reshape(-1, Hkv, dk)[lo:hi]
+            dst = (pages[:, None] * bs + torch.arange(bs)[None, :]).reshape(-1)[:hi - lo]
+            kc.view(-1, Hkv, dk)[dst] = rows_k
+            vc.view(-1, Hkv, dk)[dst] = rows_v
+            local.append(hi - lo)
+        prepared = _params(device=torch.device("cuda"), **pg)
+        parts.append(polar_decode_partials(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), torch.tensor(local).cuda(), cl.cuda(),
+                                           prepared, num_splits=3))
+    stats = torch.cat([p[0] for p in parts], dim=2)
+    sums = torch.cat([p[1] for p in parts], dim=2)
+    c, m = polar_decode_merge(stats, sums, cl.cuda(), prepared, dtype)
+    if dtype == torch.float32:
+        assert max_abs(c, c_ref) < 1e-4 and max_abs(m, m_ref) < 1e-4
+    else:
+        assert max_rel(c, c_ref) < 2e-2 and max_abs(m, m_ref) < 2e-2
