@@ -32,8 +32,8 @@ __global__ void conv_step_kernel(const T* __restrict__ x, int64_t x_sb, const T*
 }
 
 // ---- packed prefill ------------------------------------------------------------------------
-// Thread = one channel x a run of TOK_PER_THREAD consecutive tokens; the last K-1 inputs slide
-// through registers so x is read once.  Left context that falls before the token's own
+// Scalar form (any channel count, stride or alignment): thread = one channel x a run of
+// kConvTokPerThread consecutive tokens.  Left context that falls before the token's own
 // sequence start is zero (fresh prompt) or comes from init_state (continuation chunk).
 constexpr int kConvTokPerThread = 16;
 
@@ -86,6 +86,147 @@ __global__ void packed_conv_kernel(const T* __restrict__ x, int64_t x_st, const 
   }
 }
 
+// Vector form (channel count and row strides multiples of 16 bytes, 16-byte aligned bases): thread =
+// 16 bytes of channels (8 for the 2-byte types, 4 for fp32) x a run of kVecTok consecutive tokens.
+// All kVecTok + K - 1 rows of the run are requested as 16-byte loads before the first use, so a thread
+// keeps 11 loads in flight and every input row is read once from memory (the K-1 rows of overlap with
+// the neighbouring run hit L2); the taps then index registers.  A run that lies inside one sequence and
+// does not close it skips the per-token sequence maps.  Same accumulation order as the scalar form.
+constexpr int kVecTok = 8;
+
+template <typename T> struct Vec16 {
+  static constexpr int N = 16 / sizeof(T);
+  union { uint4 u; T e[N]; };
+};
+
+// The rare rows of the vector form, kept out of line so that the common path stays small: a row that lies
+// before the sequence start (from init_state, channel-major [C][K-1], or zero), and the state write of a
+// token that closes its sequence.
+template <typename T, int K>
+__device__ __noinline__ uint4 conv_row_before_start(const T* __restrict__ init_state, int64_t base, int rows_before) {
+  Vec16<T> r;
+#pragma unroll
+  for (int n = 0; n < Vec16<T>::N; ++n)
+    r.e[n] = init_state != nullptr ? init_state[base + (int64_t)n * (K - 1) + (K - 1 - rows_before)] : from_f32<T>(0.f);
+  return r.u;
+}
+template <typename T, int K>
+__device__ __noinline__ void conv_state_write(T* __restrict__ dst, const uint4* keep) {
+#pragma unroll
+  for (int j = 0; j < K - 1; ++j) {
+    Vec16<T> r;
+    r.u = keep[j];
+#pragma unroll
+    for (int n = 0; n < Vec16<T>::N; ++n) dst[(int64_t)n * (K - 1) + j] = r.e[n];
+  }
+}
+
+template <typename T, int K>
+__global__ void __launch_bounds__(128)
+packed_conv_vec_kernel(const T* __restrict__ x, int64_t x_st, const T* __restrict__ w, T* __restrict__ out,
+                       int64_t out_st, T* __restrict__ state, const T* __restrict__ init_state, int64_t state_ss,
+                       const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_end,
+                       const int32_t* __restrict__ seq_slot, int total, int C, int residual) {
+  constexpr int N = Vec16<T>::N;
+  const int groups = C / N;
+  const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int cg = (int)(gid % groups);
+  const int64_t run = gid / groups;
+  if (run * kVecTok >= total) return;
+  const int t0 = (int)(run * kVecTok);
+  const int c0 = cg * N;
+  const int nt = min(kVecTok, total - t0);
+
+  Vec16<T> rows[kVecTok + K - 1];                     // rows[i] = packed row t0 - (K-1) + i
+#pragma unroll
+  for (int i = 0; i < kVecTok + K - 1; ++i) {
+    const int t = t0 - (K - 1) + i;
+    if (t >= 0 && t < total) rows[i].u = *reinterpret_cast<const uint4*>(x + (int64_t)t * x_st + c0);
+    else rows[i].u = make_uint4(0u, 0u, 0u, 0u);
+  }
+  // the thread's N x K weights are neighbours in memory ([C][K]): N*K*sizeof(T) bytes as 16-byte loads
+  float wt[N][K];
+  {
+    constexpr int kPieces = N * K * (int)sizeof(T) / 16;            // = K
+    Vec16<T> wv[kPieces];
+#pragma unroll
+    for (int i = 0; i < kPieces; ++i) wv[i].u = *reinterpret_cast<const uint4*>(w + (int64_t)c0 * K + i * N);
+#pragma unroll
+    for (int n = 0; n < N; ++n)
+#pragma unroll
+      for (int j = 0; j < K; ++j) wt[n][j] = to_f32(wv[(n * K + j) / N].e[(n * K + j) % N]);
+  }
+
+  const int sa = seq_start[t0], ea = seq_end[t0 + nt - 1], sla = seq_slot[t0];
+  const bool uniform = sa == seq_start[t0 + nt - 1] && ea > t0 + nt;   // one sequence, not closed inside the run
+  if (uniform && sa <= t0 - (K - 1)) {
+    // common case: the run and its K-1 rows of left context lie inside one sequence.  Each row is converted
+    // to fp32 once and slides through a K-row register window.
+    float win[K][N];
+#pragma unroll
+    for (int rl = 0; rl < kVecTok + K - 1; ++rl) {
+#pragma unroll
+      for (int n = 0; n < N; ++n) win[rl % K][n] = to_f32(rows[rl].e[n]);
+      if (rl >= K - 1 && rl - (K - 1) < nt) {
+        Vec16<T> o;
+#pragma unroll
+        for (int n = 0; n < N; ++n) {
+          float acc = 0.f;
+#pragma unroll
+          for (int j = 0; j < K; ++j) acc = fmaf(win[(rl - (K - 1) + j) % K][n], wt[n][j], acc);
+          if (residual) acc += win[rl % K][n];
+          o.e[n] = from_f32<T>(acc);
+        }
+        *reinterpret_cast<uint4*>(out + (int64_t)(t0 + rl - (K - 1)) * out_st + c0) = o.u;
+      }
+    }
+    return;
+  }
+#pragma unroll 1
+  for (int i = 0; i < nt; ++i) {
+    const int t = t0 + i;
+    const int s0 = uniform ? sa : seq_start[t], e0 = uniform ? ea : seq_end[t], sl = uniform ? sla : seq_slot[t];
+    Vec16<T> prev[K];                                 // prev[j] = the input K-1-j rows before t as this sequence sees it
+#pragma unroll
+    for (int j = 0; j < K; ++j) {
+      const int src = t - (K - 1 - j);
+      if (src >= s0) {
+        const int idx = i + j;                        // rows[] index; selected without dynamic register indexing
+        uint4 u = rows[0].u;
+#pragma unroll
+        for (int q = 1; q < kVecTok + K - 1; ++q) if (q == idx) u = rows[q].u;
+        prev[j].u = u;
+      } else {
+        prev[j].u = conv_row_before_start<T, K>(sl >= 0 ? init_state : nullptr,
+                                                (sl >= 0 ? sl * state_ss : 0) + (int64_t)c0 * (K - 1), s0 - src);
+      }
+    }
+    Vec16<T> o;
+#pragma unroll
+    for (int n = 0; n < N; ++n) {
+      float acc = 0.f;
+#pragma unroll
+      for (int j = 0; j < K; ++j) acc = fmaf(to_f32(prev[j].e[n]), wt[n][j], acc);
+      if (residual) acc += to_f32(prev[K - 1].e[n]);
+      o.e[n] = from_f32<T>(acc);
+    }
+    *reinterpret_cast<uint4*>(out + (int64_t)t * out_st + c0) = o.u;
+    if (t == e0 - 1 && sl >= 0) {                     // closes its sequence: keep the last K-1 inputs, oldest first
+      uint4 keep[K - 1];
+#pragma unroll
+      for (int j = 0; j < K - 1; ++j) keep[j] = prev[j + 1].u;
+      conv_state_write<T, K>(state + sl * state_ss + (int64_t)c0 * (K - 1), keep);
+    }
+  }
+}
+
+template <typename T>
+bool conv_vec_ok(const void* x, int64_t x_st, const void* w, const void* out, int64_t out_st, int C) {
+  constexpr int N = 16 / sizeof(T);
+  return C % N == 0 && x_st % N == 0 && out_st % N == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+         (reinterpret_cast<uintptr_t>(w) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+}
+
 template <typename T>
 int launch_conv_step(const void* x, int64_t x_sb, const void* w, const int64_t* slots, void* state,
                      int64_t state_ss, void* out, int64_t out_sb, int B, int D, int K,
@@ -109,6 +250,17 @@ int launch_packed_conv(const void* x, int64_t x_st, const void* w, void* out, in
                        void* state, const void* init_state, int64_t state_ss,
                        const int32_t* s0, const int32_t* e0, const int32_t* sl, int total, int C,
                        int K, int residual, cudaStream_t st) {
+  if (conv_vec_ok<T>(x, x_st, w, out, out_st, C)) {
+    const int64_t threads = (int64_t)(C / (16 / (int)sizeof(T))) * ((total + kVecTok - 1) / kVecTok);
+    dim3 grid((unsigned)((threads + 127) / 128)), block(128);
+    switch (K) {
+      case 2: packed_conv_vec_kernel<T, 2><<<grid, block, 0, st>>>((const T*)x, x_st, (const T*)w, (T*)out, out_st, (T*)state, (const T*)init_state, state_ss, s0, e0, sl, total, C, residual); break;
+      case 3: packed_conv_vec_kernel<T, 3><<<grid, block, 0, st>>>((const T*)x, x_st, (const T*)w, (T*)out, out_st, (T*)state, (const T*)init_state, state_ss, s0, e0, sl, total, C, residual); break;
+      case 4: packed_conv_vec_kernel<T, 4><<<grid, block, 0, st>>>((const T*)x, x_st, (const T*)w, (T*)out, out_st, (T*)state, (const T*)init_state, state_ss, s0, e0, sl, total, C, residual); break;
+      default: return fail(ATMA_ERR_UNSUPPORTED, "packed_causal_conv1d: kernel size %d not in 2..4", K);
+    }
+    return launch_status("packed_causal_conv1d");
+  }
   dim3 grid((total + kConvTokPerThread - 1) / kConvTokPerThread, (C + 127) / 128), block(128);
 #define ATMA_CASE(KK)                                                                            \
   case KK:                                                                                       \

@@ -403,6 +403,76 @@ def profile_case(which):
             ms = e0.elapsed_time(e1) / 5
             res[name] = {"ms": ms, "bytes_per_launch": nbytes, "gbs": nbytes / (ms * 1e-3) / 1e9}
         info = {"kernel": "sigmoid_gate_mul_kernel, rms_sigmoid_gate_kernel", "tokens": total, **res}
+    elif which in ("conv", "step", "prep_decode"):
+        def timed_gbs(fn, nbytes, iters=10):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda._sleep(20_000_000)                       # the host queues the launches while the GPU is busy
+            e0.record()
+            for _ in range(iters):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / iters
+            return {"ms": ms, "bytes_per_launch": nbytes, "gbs": nbytes / (ms * 1e-3) / 1e9}
+        res = {}
+        if which == "conv":
+            # packed prefill convs on 65,536 tokens in 8 sequences: the Canon conv of q (1024 channels, K=4, residual
+            # form) and the gated LFM2 conv (hidden 2048: a (tokens, 3*2048) projection in, (tokens, 2048) out)
+            from atma_b200.layer import PackedMaps
+            n_seqs, per = 8, 8192
+            total = n_seqs * per
+            maps = PackedMaps([per] * n_seqs, list(range(n_seqs)), dev)
+            for C in (H * DK, HKV * DK):
+                x = torch.randn(total, C, generator=g).bfloat16().to(dev)
+                w = (torch.randn(C, 4, generator=g) * 0.3).bfloat16().to(dev)
+                st = torch.zeros(n_seqs, C, 3, dtype=torch.bfloat16, device=dev)
+                res[f"packed_causal_conv1d_C{C}"] = timed_gbs(
+                    lambda: ab.packed_causal_conv1d(x, w, st, maps.token_seq_starts, maps.token_seq_ends, maps.token_seq_slots),
+                    2.0 * x.numel() * 2)
+            D = 2048
+            proj = torch.randn(total, 3 * D, generator=g).bfloat16().to(dev)
+            w = (torch.randn(D, 3, generator=g) * 0.3).bfloat16().to(dev)
+            st = torch.zeros(n_seqs, D, 2, dtype=torch.bfloat16, device=dev)
+            res["lfm2_conv_packed_D2048"] = timed_gbs(
+                lambda: ab.lfm2_conv_packed(proj, w, st, maps.token_seq_starts, maps.token_seq_ends, maps.token_seq_slots),
+                4.0 * total * D * 2)
+            dst = torch.empty_like(proj)
+            res["plain_copy_same_method"] = timed_gbs(lambda: dst.copy_(proj), 2.0 * proj.numel() * 2)
+            info = {"kernel": "packed_conv_vec_kernel, lfm2_conv_packed_vec_kernel", "tokens": total, **res}
+        elif which == "step":
+            # the memory step on a state table larger than L2: 256 sequences x 8 heads x 64 KB = 134 MB read and written
+            Bs = 256
+            state = torch.randn(Bs, H, DK, DK, device=dev) * 0.1
+            q = torch.randn(Bs, H, DK, device=dev, dtype=torch.bfloat16)
+            kn = torch.randn(Bs, HKV, DK, device=dev, dtype=torch.bfloat16)
+            vn = torch.randn(Bs, HKV, DK, device=dev, dtype=torch.bfloat16)
+            gamma = torch.rand(Bs, H, device=dev) * 0.1 + 0.9
+            beta = torch.rand(Bs, H, device=dev)
+            slots = torch.arange(Bs, device=dev)
+            res["gated_delta_step_wide_B256"] = timed_gbs(
+                lambda: ab.gated_delta_decode_step_fused(q, kn, vn, state, slots, gamma=gamma, beta=beta), 2.0 * state.numel() * 4)
+            dst = torch.empty_like(state)
+            res["plain_copy_same_method"] = timed_gbs(lambda: dst.copy_(state), 2.0 * state.numel() * 4)
+            info = {"kernel": "gated_delta_step_wide_kernel", "sequences": Bs, **res}
+        else:
+            # the decode glue of a global layer at 4096 rows (a launch-latency kernel at the decode batch of 64; this
+            # size shows its bandwidth): q half of q|gate, k, v read; q, k, v, two cache rows and 3 state rows r/w
+            Bs, K = 4096, 4
+            q_gate = torch.randn(Bs, H, 2 * DK, generator=g).bfloat16().to(dev)
+            k = torch.randn(Bs, HKV, DK, generator=g).bfloat16().to(dev)
+            v = torch.randn(Bs, HKV, DK, generator=g).bfloat16().to(dev)
+            w = [(torch.randn(C, K, generator=g) * 0.3).bfloat16().to(dev) for C in (H * DK, HKV * DK, HKV * DK)]
+            st = [torch.zeros(Bs, C, K - 1, dtype=torch.bfloat16, device=dev) for C in (H * DK, HKV * DK, HKV * DK)]
+            kc = torch.zeros(Bs, HKV, DK, dtype=torch.bfloat16, device=dev)
+            vc = torch.zeros_like(kc)
+            slots = torch.arange(Bs, device=dev)
+            sm = torch.randperm(Bs, generator=g).int().to(dev)
+            nbytes = Bs * DK * 2.0 * ((2 * H + 5 * HKV) + 2 * (K - 1) * (H + 2 * HKV))
+            res["qkv_prep_decode_B4096"] = timed_gbs(lambda: ab.qkv_prep_decode(q_gate, k, v, *w, *st, slots, kc, vc, sm), nbytes)
+            info = {"kernel": "qkv_prep_decode_kernel", "rows": Bs, **res}
     elif which == "prep":
         ms, nbytes, total = bench_prep(ab, dev, tokens=65536, n_seqs=8, iters=5)
         info = {"kernel": "qkv_prep_kernel", "tokens": total, "bytes_per_launch": nbytes, "ms": ms,
@@ -870,7 +940,7 @@ def main():
     ap.add_argument("--skip-long", action="store_true", help="N > 1: omit the 262,144-token leg")
     ap.add_argument("--skip-configs", action="store_true", help="N = 1: omit the BASELINE config 2 / config 3 legs")
     ap.add_argument("--skip-model", action="store_true", help="N = 1: omit the full-model legs (BASELINE configs 4 and 5)")
-    ap.add_argument("--profile", default=None, choices=["prefill", "decode", "scan", "prep", "epilogue"],
+    ap.add_argument("--profile", default=None, choices=["prefill", "decode", "scan", "prep", "epilogue", "conv", "step", "prep_decode"],
                     help="run a few launches of ONE kernel on a small case (a few hundred MB, larger than L2) "
                          "and exit; meant to be wrapped in ncu")
     args = ap.parse_args()

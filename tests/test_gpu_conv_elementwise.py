@@ -46,8 +46,9 @@ def test_conv_decode_step(kernel, dtype):
 
 # tests/test_decode_kernels.py:135-165 of the reference: lengths 1/3/7/17, 257 channels
 @pytest.mark.parametrize("kernel", [3, 4])
-def test_packed_conv_boundaries_and_states(kernel):
-    lengths, channels = [1, 3, 7, 17, 40], 257
+@pytest.mark.parametrize("channels", [257, 256])          # the scalar kernel; the 16-byte vector kernel
+def test_packed_conv_boundaries_and_states(kernel, channels):
+    lengths = [1, 3, 7, 17, 40]
     total = sum(lengths)
     x, weight = rand((total, channels), 8, torch.bfloat16), rand((channels, kernel), 9, torch.bfloat16)
     starts, ends, slots, p = [], [], [], 0
@@ -259,9 +260,10 @@ def test_lfm2_conv_decode_step_matches_the_op_by_op_oracle(dtype, K):
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("continued", [False, True])
-def test_lfm2_conv_packed_matches_the_op_by_op_oracle(dtype, continued):
+@pytest.mark.parametrize("D,K", [(256, 3), (100, 3), (256, 4)])   # 100 channels of bf16: the scalar kernel
+def test_lfm2_conv_packed_matches_the_op_by_op_oracle(dtype, continued, D, K):
     g = torch.Generator().manual_seed(12)
-    lens, slots, D, K, rows = [1, 40, 17, 2, 33], [3, 0, -1, 5, 1], 256, 3, 6
+    lens, slots, rows = [1, 40, 17, 2, 33], [3, 0, -1, 5, 1], 6
     total = sum(lens)
     proj = torch.randn(total, 3 * D, generator=g).to(dtype)
     w = (torch.randn(D, K, generator=g) * 0.5).to(dtype)
