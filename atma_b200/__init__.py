@@ -14,12 +14,13 @@ from .gated_delta import (gated_delta_decode_step, gated_delta_decode_step_fused
 from .causal_conv1d import causal_conv1d_decode_step, causal_conv1d_fn
 from .inference_ops import squared_relu_gate, packed_causal_conv1d, softcap_logits, linear_head_rms, qkv_prep_prefill, sigmoid_gate_mul, rms_sigmoid_gate, lfm2_conv_decode_step, lfm2_conv_packed, qkv_prep_decode, add_rms_norm
 from .kvcache import store_kvcache
+from ._lib import device_status
 
 __all__ = [
     "polar_attention_fwd", "polar_attention_packed_fwd", "polar_attention_decode", "polar_prefill_raw",
     "gated_delta_decode_step", "chunk_gated_delta_rule", "packed_gated_delta_prefill",
     "causal_conv1d_decode_step", "causal_conv1d_fn",
-    "squared_relu_gate", "packed_causal_conv1d", "softcap_logits", "linear_head_rms", "qkv_prep_prefill", "sigmoid_gate_mul", "rms_sigmoid_gate", "lfm2_conv_decode_step", "lfm2_conv_packed", "qkv_prep_decode", "add_rms_norm",
+    "device_status", "squared_relu_gate", "packed_causal_conv1d", "softcap_logits", "linear_head_rms", "qkv_prep_prefill", "sigmoid_gate_mul", "rms_sigmoid_gate", "lfm2_conv_decode_step", "lfm2_conv_packed", "qkv_prep_decode", "add_rms_norm",
     "gated_delta_decode_step_fused", "invalidate_param_cache",
     "store_kvcache",
 ]

@@ -176,3 +176,14 @@ def dtype_code(t):
 def require_cuda(t, what):
     if not t.is_cuda:
         raise RuntimeError(f"{what} requires CUDA tensors (atma_b200 has no CPU path)")
+
+
+def device_status():
+    """Synchronise the current device and return the status word of the tensor-core kernels: 0, or non-zero if a
+    bounded wait of a tcgen05 kernel (Polar prefill, gated-delta recurrence, chunk-local stage) ran out since the
+    last call (the word is cleared).  Results of launches since the last call are then not to be trusted."""
+    import ctypes
+    status = ctypes.c_int(-1)
+    check(load().atma_device_status(ctypes.byref(status)))
+    return status.value
+

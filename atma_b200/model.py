@@ -166,6 +166,103 @@ class AtmaModel:
             x, h = add_rms_norm(x, self._mlp(h, i), nxt, self.eps)
         return h if snaps is None else (h, snaps)
 
+    # ---- one long prompt over several GPUs ----------------------------------------------------------------------
+    @torch.no_grad()
+    def prefill_context_parallel(self, ids_parts, positions, state, slot, slot_mappings, *, group=None, polar_mode=None):
+        """The whole model over a context-parallel group: ONE prompt of T tokens, cut into 2N zig-zag segments, rank r
+        holding segments r and 2N-1-r (``context_parallel.zigzag_segments``).  Token-local work (embedding, norms,
+        projections, MLP, epilogues) runs on the rank's own 2L tokens as a packed batch of two pieces; what crosses
+        segment borders is handed over between ranks:
+          * the K-1 conv inputs before each segment (the gated LFM2 input; the normalised q, k and raw v of the three
+            Canon convs, one message per layer) - ``cp_conv_halos``;
+          * the Polar pass over the gathered (or ring-passed) K/V and the memory scan with its state prefix of affine
+            maps - ``cp_global_layer_prefill``.
+        ids_parts [lo, hi] (L,) token ids; ``positions`` [(a0, a1), (b0, b1)]; ``slot_mappings`` [lo, hi] (L,) rows of
+        THIS rank's K/V pages (every rank caches its own tokens: the layout ``cp_polar_decode`` reads).  At the end the
+        recurrent state of the whole prompt - final conv rows (held by the rank that owns the last segment) and memory
+        states - is made the same on every rank at row ``slot`` of ``state``, so that decode can go on replicated.
+        Returns [h_lo, h_hi] (L, D): the final-norm hidden states of this rank's tokens."""
+        import torch.distributed as dist
+        from . import context_parallel as cp
+        sd, dev, D, H, Hkv, dk = self.sd, self.device, self.D, self.H, self.Hkv, self.dk
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        L = ids_parts[0].numel()
+        if ids_parts[1].numel() != L or L % 64 != 0:
+            raise ValueError("both segments must have the same length, a multiple of 64 tokens")
+        maps = PackedMaps([L, L], [0, 1], dev)                       # the two segments as two packed pieces, rows 0 and 1
+        sm = torch.cat([m.to(dev, torch.int64) for m in slot_mappings])
+        last_owner = cp.segment_owner(2 * world - 1, world)          # its hi piece ends the prompt
+        finals = {}
+
+        def tail_rows(K):
+            return torch.cat([torch.arange(L - (K - 1), L, device=dev), torch.arange(2 * L - (K - 1), 2 * L, device=dev)])
+
+        x = sd["embed.weight"][torch.cat([i.to(dev) for i in ids_parts])]
+        x, h = add_rms_norm(x, None, sd["blocks.0.norm1.weight"], self.eps)
+        for i in range(self.L):
+            P = f"blocks.{i}."
+            if i in self.global_layers:
+                A = P + "attn."
+                q_gate = self._lin(h, A + "q").view(2 * L, H, 2 * dk)
+                k = self._lin(h, A + "k").view(2 * L, Hkv, dk)
+                v = self._lin(h, A + "v").view(2 * L, Hkv, dk)
+                w = [sd[A + f"canon_{n}.weight"].squeeze(1) for n in ("q", "k", "v")]
+                Kc = w[0].shape[1]
+                # conv inputs at the piece ends: normalised q and k, raw v, side by side so that one message carries all
+                eps32 = torch.finfo(torch.float32).eps
+                idx = tail_rows(Kc)
+                tail = torch.cat([F.rms_norm(q_gate[idx, :, :dk], (dk,), eps=eps32).reshape(idx.numel(), H * dk),
+                                  F.rms_norm(k[idx], (dk,), eps=eps32).reshape(idx.numel(), Hkv * dk),
+                                  v[idx].reshape(idx.numel(), Hkv * dk)], dim=1)
+                halo = torch.stack(cp.cp_conv_halos([tail[:Kc - 1], tail[Kc - 1:]], Kc, group=group))   # (2, Cq+2Ckv, K-1)
+                Cq, Ck = H * dk, Hkv * dk
+                init = [halo[:, :Cq].contiguous(), halo[:, Cq:Cq + Ck].contiguous(), halo[:, Cq + Ck:].contiguous()]
+                scratch = [torch.zeros_like(t) for t in init]
+                q, k, v = qkv_prep_prefill(q_gate, k, v, *w, *scratch, maps.token_seq_starts, maps.token_seq_ends,
+                                           maps.token_seq_slots, state.k_cache[i].view(-1, Hkv, dk),
+                                           state.v_cache[i].view(-1, Hkv, dk), sm, initial_states=init)
+                for n, t in zip(("q", "k", "v"), scratch):
+                    finals[f"attn_{i}_{n}"] = t[1]
+                g = F.logsigmoid(self._lin(h, A + "mem.w_gamma").float() + self.gamma_bias)
+                beta = torch.sigmoid(self._lin(h, A + "mem.w_beta").float() + self.beta_bias)
+                cut = lambda t: [t[:L][None], t[L:][None]]
+                shard = cp.GlobalLayerShard(q=cut(q), k=cut(k), v=cut(v), g=cut(g), beta=cut(beta), positions=list(positions))
+                pp = {n: sd[A + n] for n in POLAR_NAMES}
+                polar, o, S = cp.cp_global_layer_prefill(shard, pp, group=group, polar_mode=polar_mode, window=self.window)
+                c = torch.cat([pc[0][0].transpose(0, 1) for pc in polar]).contiguous()          # (2L, H, dk)
+                mag = torch.cat([pc[1][0].transpose(0, 1) for pc in polar]).contiguous()        # (2L, H)
+                r = torch.cat([oo[0] for oo in o]).contiguous()                                 # (2L, H, dk)
+                state.mem[i][slot] = S
+                gated = sigmoid_gate_mul(c, q_gate[..., dk:]).view(2 * L, H * dk)
+                mix = self._lin(gated, A + "proj") + self._lin(mag.to(self.dtype), A + "mu_proj")
+                mix = mix + self._lin(rms_sigmoid_gate(r, self._lin(h, A + "mem.gate")), A + "mem.proj")
+            else:
+                proj = self._lin(h, P + "attn.in_proj")
+                Kc = self.conv_k
+                idx = tail_rows(Kc)
+                tail = proj[idx, :D] * proj[idx, 2 * D:]             # the conv's inputs B * x' at the piece ends
+                init = torch.stack(cp.cp_conv_halos([tail[:Kc - 1], tail[Kc - 1:]], Kc, group=group))   # (2, D, K-1)
+                scratch = torch.zeros_like(init)
+                y = lfm2_conv_packed(proj, sd[P + "attn.conv.weight"].squeeze(1), scratch, maps.token_seq_starts,
+                                     maps.token_seq_ends, maps.token_seq_slots, initial_state=init)
+                finals[f"conv_{i}"] = scratch[1]
+                mix = self._lin(y, P + "attn.out_proj")
+            x, h = add_rms_norm(x, mix, sd[P + "norm2.weight"], self.eps)
+            nxt = sd[f"blocks.{i + 1}.norm1.weight"] if i + 1 < self.L else sd["norm.weight"]
+            x, h = add_rms_norm(x, self._mlp(h, i), nxt, self.eps)
+        # the final conv rows of the prompt live on the owner of the last segment: one broadcast for all layers
+        names = sorted(finals)
+        flat = torch.cat([finals[n].reshape(-1) for n in names])
+        if world > 1:
+            src = dist.get_global_rank(group, last_owner) if group is not None else last_owner
+            dist.broadcast(flat, src=src, group=group)
+        off = 0
+        for n in names:
+            t = finals[n]
+            state.conv[n][slot] = flat[off:off + t.numel()].view_as(t)
+            off += t.numel()
+        return [h[:L], h[L:]]
+
     @torch.no_grad()
     def prefill_from_prefix(self, ids_tail, prefix_len, slot, state, slot_mapping_tail, block_table_row, snapshots, index):
         """The rest of ONE prompt whose first ``prefix_len`` tokens (whole pages) are already in the K/V pages that
@@ -252,15 +349,19 @@ class AtmaModel:
                                           *(state.conv[f"attn_{i}_{n}"] for n in ("q", "k", "v")), seq_slots,
                                           state.k_cache[i], state.v_cache[i], slot_mapping)
                 act = torch.empty((B, 2 * H * dk + H), device=x.device, dtype=x.dtype)   # [c * sig(gate) | mag | norm(r) * sig(gate)]
-                polar_attention_decode(q, state.k_cache[i], state.v_cache[i], block_tables, context_lens, window=self.window,
-                                       gate=q_gate[..., dk:], out=(act[:, :H * dk].view(B, H, dk), act[:, H * dk:H * dk + H]),
-                                       **pk["polar"])
                 r_out = act[:, H * dk + H:]
                 mem_gate = z[:, pk["o_mg"]:]
+                # The memory branch shares nothing it writes with the attention branch (its slice of ``act``, its own
+                # state table), so it runs beside the paged attention on a second stream: fork here, join before W_out.
+                cur = torch.cuda.current_stream(x.device)
                 if dk == 128:
-                    gated_delta_decode_step_fused(q, k, v, state.mem[i], seq_slots,
-                                                  gate_logits=(z[:, pk["o_g"]:pk["o_b"]], z[:, pk["o_b"]:pk["o_mg"]]),
-                                                  gamma_bias=self.gamma_bias, beta_bias=self.beta_bias, gate=mem_gate, out=r_out)
+                    side = self._decode_side_stream()
+                    side.wait_stream(cur)
+                    with torch.cuda.stream(side):
+                        gated_delta_decode_step_fused(q, k, v, state.mem[i], seq_slots,
+                                                      gate_logits=(z[:, pk["o_g"]:pk["o_b"]], z[:, pk["o_b"]:pk["o_mg"]]),
+                                                      gamma_bias=self.gamma_bias, beta_bias=self.beta_bias, gate=mem_gate,
+                                                      out=r_out)
                 else:                                                            # other head sizes: the separate kernels
                     G = H // Hkv
                     gamma = torch.sigmoid(z[:, pk["o_g"]:pk["o_b"]].float() + self.gamma_bias)
@@ -268,6 +369,11 @@ class AtmaModel:
                     r = gated_delta_decode_step(q, k.repeat_interleave(G, 1), v.repeat_interleave(G, 1), gamma, beta,
                                                 state.mem[i], seq_slots)
                     r_out.copy_(rms_sigmoid_gate(r.to(x.dtype), mem_gate))
+                polar_attention_decode(q, state.k_cache[i], state.v_cache[i], block_tables, context_lens, window=self.window,
+                                       gate=q_gate[..., dk:], out=(act[:, :H * dk].view(B, H, dk), act[:, H * dk:H * dk + H]),
+                                       **pk["polar"])
+                if dk == 128:
+                    cur.wait_stream(side)                                        # join the memory branch
                 mix = F.linear(act, pk["w_out"], pk["b_out"])                          # W_o, W_mu and mem.proj in one product
             else:
                 proj = self._lin(h, P + "attn.in_proj")
@@ -277,6 +383,11 @@ class AtmaModel:
             nxt = sd[f"blocks.{i + 1}.norm1.weight"] if i + 1 < self.L else sd["norm.weight"]
             x, h = add_rms_norm(x, self._mlp(h, i), nxt, self.eps)
         return self.logits(h)
+
+    def _decode_side_stream(self):
+        if getattr(self, "_side", None) is None:
+            self._side = torch.cuda.Stream(device=self.device)
+        return self._side
 
     def decode_bytes(self, batch, context):
         """Algorithmic HBM bytes of one decode step: every weight once, the K/V rows of the context, the memory

@@ -183,10 +183,18 @@ def bench_decode(ab, device, steps, warmup, peaks):
     slots = torch.arange(DEC_B, device=device)
     params = default_polar_params(device)
 
+    side = torch.cuda.Stream(device=device)
+
     def step():
+        # the memory branch reads and writes nothing the attention branch touches: it runs beside it (fork / join),
+        # as the two branches of the reference's decode layer may (inference/models/atma.py:572-590)
+        cur = torch.cuda.current_stream(device)
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            r = ab.gated_delta_decode_step_fused(q, kn, vn, state, slots, gamma=gamma, beta=beta)   # un-expanded KV heads
         ab.store_kvcache(kn, vn, k_cache, v_cache, slot_map)
         c, mag = ab.polar_attention_decode(q, k_cache, v_cache, bt, cl, **params)
-        r = ab.gated_delta_decode_step_fused(q, kn, vn, state, slots, gamma=gamma, beta=beta)   # un-expanded KV heads
+        cur.wait_stream(side)
         return c, mag, r
 
     for _ in range(warmup):
@@ -211,11 +219,11 @@ def bench_decode(ab, device, steps, warmup, peaks):
     # the step as the engine runs it: captured once, replayed (inference/engine/model_runner.py:254-310)
     ms, graphed = eager_ms, False
     try:
-        side = torch.cuda.Stream(device=device)
-        side.wait_stream(torch.cuda.current_stream(device))
-        with torch.cuda.stream(side):
+        warm = torch.cuda.Stream(device=device)
+        warm.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(warm):
             step()
-        torch.cuda.current_stream(device).wait_stream(side)
+        torch.cuda.current_stream(device).wait_stream(warm)
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             step()
@@ -683,6 +691,12 @@ def run_context_parallel(args, ab, rank, local_rank, world, device, peaks):
     long_leg = None
     if not args.skip_long and T_PREFILL != 262144:
         long_leg = cp_long_prefill(cp, dist, rank, world, device, params, 262144, peaks)
+    config5 = None
+    if not args.skip_model and T_PREFILL != 262144:
+        config5 = cp_model_prefill(cp, dist, rank, world, device, peaks)
+    # non-zero on any rank = a bounded wait of a tensor-core kernel ran out during this run
+    status = torch.tensor([ab.device_status()], device=device, dtype=torch.int32)
+    dist.all_reduce(status, op=dist.ReduceOp.MAX)
     dist.barrier()
     dist.destroy_process_group()
     if rank != 0:
@@ -720,8 +734,63 @@ def run_context_parallel(args, ab, rank, local_rank, world, device, peaks):
         "cpu_baseline": None,
         "decode": decode,
         "prefill_256k": long_leg,
+        "config5_model_prefill": config5,
+        "device_status": int(status.item()),
     }
     emit(line)
+
+
+def cp_model_prefill(cp, dist, rank, world, device, peaks, tokens=262144, steps=2):
+    """BASELINE config 5 over the GPUs: the whole 16-layer model, ONE prompt of 262,144 uniform token ids cut into zig-zag
+    segments (``AtmaModel.prefill_context_parallel``: conv halos between neighbours, Polar over the all-gathered K/V,
+    memory state as an affine-map prefix), last-token logits on the rank that owns the last segment.  Device-timed,
+    max over ranks."""
+    from atma_b200.model import AtmaModel, random_state_dict
+    sd = random_state_dict(vocab=VOCAB, seed=4, device=device, **MODEL)
+    model = AtmaModel(sd, device=device, **MODEL)
+    del sd
+    (a0, a1), (b0, b1) = cp.zigzag_segments(tokens, world)[rank]
+    L = a1 - a0
+    bs = DEC_BLOCK
+    pages = 2 * L // bs
+    state = model.new_state(max_seqs=1, num_blocks=pages, block_size=bs)
+    ids = torch.randint(0, VOCAB, (tokens,), generator=torch.Generator().manual_seed(4))
+    parts = [ids[a0:a1].to(device), ids[b0:b1].to(device)]
+    bt = torch.randperm(pages, generator=torch.Generator().manual_seed(4 + rank))
+    pos = torch.arange(2 * L)
+    sm = (bt[pos // bs] * bs + pos % bs).to(device)
+    owns_last = cp.segment_owner(2 * world - 1, world) == rank
+
+    def step():
+        h = model.prefill_context_parallel(parts, [(a0, a1), (b0, b1)], state, 0, [sm[:L], sm[L:]])
+        return model.logits(h[1][-1:]) if owns_last else None
+
+    logits = step()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        logits = step()
+    e1.record()
+    dist.barrier()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / steps, 1.0 if (logits is None or bool(torch.isfinite(logits.float()).all())) else 0.0],
+                     device=device, dtype=torch.float64)
+    dist.all_reduce(t[:1], op=dist.ReduceOp.MAX)
+    dist.all_reduce(t[1:], op=dist.ReduceOp.MIN)
+    ms = float(t[0].item())
+    n_body = sum(x.numel() for n, x in model.sd.items() if n not in ("embed.weight", "proj.weight", "proj.bias"))
+    fl = len(model.global_layers) * polar_flops(tokens) + 2.0 * n_body * tokens + len(model.global_layers) * scan_flops(tokens)
+    tf = fl / (ms * 1e-3) / 1e12
+    del model, state
+    torch.cuda.empty_cache()
+    return {"workload": f"BASELINE config 5: full model, one {tokens}-token prompt context-parallel over {world} GPUs",
+            "ms_per_step": ms, "value": tokens / (ms * 1e-3), "unit": "tok/s", "steps": steps, "algorithmic_flops": fl,
+            "logits_finite": bool(t[1].item() > 0.5), "polar_mode": "gather",
+            "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["tf_sustained"] * world, "unit": "TFLOP/s",
+                         "frac": tf / (peaks["tf_sustained"] * world),
+                         "peak_source": peaks["source"] + f" sustained x {world} GPUs"}}
 
 
 def cp_long_prefill(cp, dist, rank, world, device, params, tokens, peaks, steps=5, warm=3):
@@ -1058,6 +1127,7 @@ def main():
         torch.cuda.empty_cache()
         config5 = bench_model_prefill(device, peaks)
         torch.cuda.empty_cache()
+    device_status = ab.device_status()       # non-zero = a bounded wait of a tensor-core kernel ran out during this run
     cpu = None
     if rank == 0 and world == 1 and not args.skip_cpu:
         threads = os.cpu_count() or 1
@@ -1120,6 +1190,7 @@ def main():
         "config3": config3,
         "config4_model_decode": config4,
         "config5_model_prefill_1gpu": config5,
+        "device_status": device_status,
     }
     emit(line)
 

@@ -149,3 +149,70 @@ def test_two_rank_context_parallel_matches_one_gpu():
     for rank in range(world):
         cd, md = ret[f"dec{rank}"]
         assert rel(cd, c1.float().cpu()) < 2e-2 and rel(md, m1.float().cpu()) < 2e-2
+
+
+# ---- the whole model over a context-parallel group -----------------------------------------------------------------
+MODEL_CFG = dict(layers=8, hidden=512, head_dim=128, num_kv_heads=1)
+MODEL_T, MODEL_BLOCK = 1024, 64
+
+
+def _model_worker(rank, world, port, ret):
+    import torch.distributed as dist
+    from atma_b200 import context_parallel as cp
+    from atma_b200.model import AtmaModel, random_state_dict
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        sd = random_state_dict(vocab=640, seed=5, device=dev, **MODEL_CFG)
+        model = AtmaModel(sd, device=dev, **MODEL_CFG)
+        ids = torch.randint(0, 640, (MODEL_T,), generator=torch.Generator().manual_seed(9))
+        # the single-GPU prefill of the whole prompt (every rank computes it for itself)
+        pages = MODEL_T // MODEL_BLOCK
+        ref_state = model.new_state(max_seqs=2, num_blocks=pages, block_size=MODEL_BLOCK)
+        h_ref = model.prefill(ids, [MODEL_T], [1], ref_state, torch.arange(MODEL_T))
+        # context-parallel: this rank's two zig-zag segments, K/V of its own tokens in its own pages
+        (a0, a1), (b0, b1) = cp.zigzag_segments(MODEL_T, world)[rank]
+        L = a1 - a0
+        state = model.new_state(max_seqs=2, num_blocks=2 * L // MODEL_BLOCK, block_size=MODEL_BLOCK)
+        h = model.prefill_context_parallel([ids[a0:a1], ids[b0:b1]], [(a0, a1), (b0, b1)], state, 1,
+                                           [torch.arange(L), torch.arange(L, 2 * L)])
+        torch.cuda.synchronize()
+        rel = lambda a, b: float((a.float() - b.float()).abs().max() / b.float().abs().max().clamp_min(1e-12))
+        out = dict(h=[rel(h[0], h_ref[a0:a1]), rel(h[1], h_ref[b0:b1])])
+        out["mem"] = max(rel(state.mem[i][1], ref_state.mem[i][1]) for i in model.global_layers)
+        out["conv"] = max(rel(state.conv[n][1], ref_state.conv[n][1]) for n in state.conv)
+        # K/V rows of this rank's tokens against the rows the single-GPU prefill cached
+        gl = model.global_layers[0]
+        mine = state.k_cache[gl].view(-1, model.Hkv, model.dk)
+        whole = ref_state.k_cache[gl].view(-1, model.Hkv, model.dk)
+        out["kv"] = max(rel(mine[:L], whole[a0:a1]), rel(mine[L:2 * L], whole[b0:b1]))
+        ret[rank] = out
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [1, 2])
+def test_context_parallel_model_prefill_matches_one_gpu(world):
+    """The whole model with one prompt cut over the ranks (conv halos, Polar over gathered K/V, memory state prefix)
+    against the packed single-GPU prefill of the same prompt: hidden states of every token, final conv and memory
+    states, cached K/V rows.  Same kernels on both sides; the differences are the order of the 16-bit roundings
+    around the segment borders."""
+    import torch.multiprocessing as mp
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    ret = mp.Manager().dict()
+    ctx = mp.spawn(_model_worker, args=(world, port, ret), nprocs=world, join=False)
+    deadline = time.time() + 150
+    while not ctx.join(timeout=5):
+        if time.time() > deadline:
+            for p in ctx.processes:
+                p.kill()
+            pytest.fail("context-parallel model ranks did not finish in time")
+    for rank in range(world):
+        r = ret[rank]
+        assert max(r["h"]) < 2e-2, r
+        assert r["mem"] < 2e-2 and r["conv"] < 1e-2 and r["kv"] < 1e-2, r
