@@ -309,3 +309,37 @@ def add_rms_norm(x, y, weight, eps=1e-6):
     _lib.check(lib.atma_add_rms_norm(_lib.ptr(x2), _lib.ptr(y2), _lib.ptr(w), _lib.ptr(x_out), _lib.ptr(h), x2.shape[0], D,
                                      float(eps), _lib.dtype_code(x), _lib.stream_ptr()))
     return (x if y is None else x_out.view(x.shape)), h.view(x.shape)
+
+
+
+DECODE_LINEAR_MAX_ROWS = 16
+
+
+def decode_linear_supported(x, weight, gated=False):
+    """Whether ``decode_linear`` serves this product: CUDA, 16-bit, 1..16 rows, K a multiple of 32, N a multiple of 16
+    (32 for the gated form), 16-byte aligned rows."""
+    return (x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and weight.dtype == x.dtype and x.ndim == 2 and
+            0 < x.shape[0] <= DECODE_LINEAR_MAX_ROWS and x.shape[1] % 32 == 0 and weight.shape[0] % (32 if gated else 16) == 0 and
+            weight.is_contiguous() and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0)
+
+
+@torch.no_grad()
+def decode_linear(x, weight, bias=None, gated=False):
+    """x @ weight.T + bias for a decode batch of up to 16 rows, the weights streamed once from HBM
+    (``F.linear`` at these sizes); ``gated``: weight is the MLP's fc projection (2F, K) and the result is
+    second_half * relu(first_half)^2, (rows, F) - the fc GEMM and ``squared_relu_gate`` of
+    inference/models/atma.py:87-97 in one launch.  x (rows, K), weight (N, K) contiguous, 16-bit."""
+    _lib.require_cuda(x, "decode_linear")
+    lib = _lib.load()
+    B, K = x.shape
+    N = weight.shape[0]
+    if weight.shape[1] != K or weight.dtype != x.dtype or not weight.is_contiguous():
+        raise ValueError("weight must be a contiguous (N, K) tensor in x's dtype")
+    if x.stride(1) != 1:
+        x = x.contiguous()
+    if bias is not None:
+        bias = bias.to(x.dtype).contiguous()
+    out = torch.empty((B, N // 2 if gated else N), device=x.device, dtype=x.dtype)
+    _lib.check(lib.atma_decode_linear(_lib.ptr(x), x.stride(0), _lib.ptr(weight), _lib.ptr(bias), _lib.ptr(out), out.stride(0),
+                                      B, N, K, 1 if gated else 0, _lib.dtype_code(x), _lib.stream_ptr()))
+    return out

@@ -35,8 +35,8 @@ import hashlib
 from .gated_delta import gated_delta_decode_step, gated_delta_decode_step_fused, packed_gated_delta_prefill
 from .inference_ops import qkv_prep_prefill, sigmoid_gate_mul
 from .polar import polar_attention_fwd
-from .inference_ops import (add_rms_norm, lfm2_conv_decode_step, lfm2_conv_packed, qkv_prep_decode, rms_sigmoid_gate,
-                            softcap_logits, squared_relu_gate)
+from .inference_ops import (add_rms_norm, decode_linear, decode_linear_supported, lfm2_conv_decode_step, lfm2_conv_packed,
+                            qkv_prep_decode, rms_sigmoid_gate, softcap_logits, squared_relu_gate)
 from .layer import PackedMaps, global_attention_prefill_packed
 from .polar import polar_attention_decode
 
@@ -70,6 +70,7 @@ class AtmaModel:
         self.global_layers = [i for i in range(layers) if i % 4 == 2]
         self.conv_k = sd["blocks.0.attn.conv.weight"].shape[-1] if "blocks.0.attn.conv.weight" in sd else 3
         self.attn_k = sd[f"blocks.{self.global_layers[0]}.attn.canon_q.weight"].shape[-1] if self.global_layers else 4
+        self.small_batch_linear = True          # decode batches <= 16: weight-streaming kernel instead of cuBLAS
         self._pack_decode_weights()
 
     # ---- weights packed for the decode step -------------------------------------------------------
@@ -108,12 +109,23 @@ class AtmaModel:
         return st
 
     def _lin(self, x, name):
-        return F.linear(x, self.sd[name + ".weight"], self.sd.get(name + ".bias"))
+        return self._linear(x, self.sd[name + ".weight"], self.sd.get(name + ".bias"))
+
+    def _linear(self, x, w, b):
+        """Decode batches of up to 16 rows stream the weights through this library's kernel; larger ones are cuBLAS."""
+        if self.small_batch_linear and decode_linear_supported(x, w):
+            return decode_linear(x, w, b)
+        return F.linear(x, w, b)
 
     def _mlp(self, h, i):
-        fc = self._lin(h, f"blocks.{i}.mlp.fc")
-        half = fc.shape[-1] // 2
-        return self._lin(squared_relu_gate(fc[:, :half], fc[:, half:]), f"blocks.{i}.mlp.proj")
+        w, b = self.sd[f"blocks.{i}.mlp.fc.weight"], self.sd.get(f"blocks.{i}.mlp.fc.bias")
+        if self.small_batch_linear and decode_linear_supported(h, w, gated=True):
+            act = decode_linear(h, w, b, gated=True)            # fc GEMM and the squared-ReLU gate in one launch
+        else:
+            fc = F.linear(h, w, b)
+            half = fc.shape[-1] // 2
+            act = squared_relu_gate(fc[:, :half], fc[:, half:])
+        return self._lin(act, f"blocks.{i}.mlp.proj")
 
     def logits(self, hidden):
         """LM head + soft-cap on already-normalised hidden rows (inference/models/atma.py:750-754)."""
@@ -341,7 +353,7 @@ class AtmaModel:
             P = f"blocks.{i}."
             if i in self.global_layers:
                 pk = self.packed[i]
-                z = F.linear(h, pk["w_in"], pk["b_in"])                              # every input projection at once
+                z = self._linear(h, pk["w_in"], pk["b_in"])                              # every input projection at once
                 q_gate = z[:, :pk["o_k"]].view(B, H, 2 * dk)
                 k = z[:, pk["o_k"]:pk["o_v"]].view(B, Hkv, dk)
                 v = z[:, pk["o_v"]:pk["o_g"]].view(B, Hkv, dk)
@@ -374,7 +386,7 @@ class AtmaModel:
                                        **pk["polar"])
                 if dk == 128:
                     cur.wait_stream(side)                                        # join the memory branch
-                mix = F.linear(act, pk["w_out"], pk["b_out"])                          # W_o, W_mu and mem.proj in one product
+                mix = self._linear(act, pk["w_out"], pk["b_out"])                          # W_o, W_mu and mem.proj in one product
             else:
                 proj = self._lin(h, P + "attn.in_proj")
                 y = lfm2_conv_decode_step(proj, sd[P + "attn.conv.weight"].squeeze(1), seq_slots, state.conv[f"conv_{i}"])

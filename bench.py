@@ -411,6 +411,40 @@ def profile_case(which):
             ms = e0.elapsed_time(e1) / 5
             res[name] = {"ms": ms, "bytes_per_launch": nbytes, "gbs": nbytes / (ms * 1e-3) / 1e9}
         info = {"kernel": "sigmoid_gate_mul_kernel, rms_sigmoid_gate_kernel", "tokens": total, **res}
+    elif which == "linear":
+        # the MLP of one layer at decode batch 8 (hidden 1024, 4x): fc + gate (16.8 MB of weights), proj (8.4 MB); the
+        # weights cycle through 12 copies (302 MB) so that every launch reads them from HBM, not from L2
+        import torch.nn.functional as F
+        Bs, D, Fh, copies = 8, 1024, 4096, 12
+        x = torch.randn(Bs, D, generator=g).bfloat16().to(dev)
+        a_in = torch.randn(Bs, Fh, generator=g).bfloat16().to(dev)
+        w_fc = [(torch.randn(2 * Fh, D, generator=g) / 32).bfloat16().to(dev) for _ in range(copies)]
+        w_pr = [(torch.randn(D, Fh, generator=g) / 64).bfloat16().to(dev) for _ in range(copies)]
+
+        def timed_ring(fn, nbytes, iters=24):
+            for i in range(copies):
+                fn(i)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda._sleep(20_000_000)
+            e0.record()
+            for i in range(iters):
+                fn(i % copies)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / iters
+            return {"ms": ms, "bytes_per_launch": nbytes, "gbs": nbytes / (ms * 1e-3) / 1e9}
+
+        def eager_fc(i):
+            y = F.linear(x, w_fc[i])
+            return ab.squared_relu_gate(y[:, :Fh], y[:, Fh:])
+        res = {
+            "decode_linear_fc_gated": timed_ring(lambda i: ab.decode_linear(x, w_fc[i], None, gated=True), 2.0 * 2 * Fh * D),
+            "cublas_fc_then_gate": timed_ring(eager_fc, 2.0 * 2 * Fh * D),
+            "decode_linear_proj": timed_ring(lambda i: ab.decode_linear(a_in, w_pr[i]), 2.0 * Fh * D),
+            "cublas_proj": timed_ring(lambda i: F.linear(a_in, w_pr[i]), 2.0 * Fh * D),
+        }
+        info = {"kernel": "decode_linear_kernel", "rows": Bs, **res}
     elif which in ("conv", "step", "prep_decode"):
         def timed_gbs(fn, nbytes, iters=10):
             for _ in range(3):
@@ -1009,7 +1043,7 @@ def main():
     ap.add_argument("--skip-long", action="store_true", help="N > 1: omit the 262,144-token leg")
     ap.add_argument("--skip-configs", action="store_true", help="N = 1: omit the BASELINE config 2 / config 3 legs")
     ap.add_argument("--skip-model", action="store_true", help="N = 1: omit the full-model legs (BASELINE configs 4 and 5)")
-    ap.add_argument("--profile", default=None, choices=["prefill", "decode", "scan", "prep", "epilogue", "conv", "step", "prep_decode"],
+    ap.add_argument("--profile", default=None, choices=["prefill", "decode", "scan", "prep", "epilogue", "conv", "step", "prep_decode", "linear"],
                     help="run a few launches of ONE kernel on a small case (a few hundred MB, larger than L2) "
                          "and exit; meant to be wrapped in ncu")
     args = ap.parse_args()

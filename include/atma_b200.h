@@ -219,6 +219,17 @@ int atma_qkv_prep_decode(const void* q_gate, int64_t qg_row, int64_t qg_head, co
 int atma_add_rms_norm(const void* x, const void* y, const void* weight, void* x_out, void* h_out, int rows, int D,
                       float eps, int dtype, void* stream);
 
+/* Weight-streaming linear layer for decode batches of up to 16 rows (16-bit types): out[b][n] =
+ * sum_k x[b][k] * weight[n][k] + bias[n] (bias may be NULL), weight [N][K] dense in torch's Linear
+ * layout, fp32 accumulation, one rounding to `dtype`.  gated != 0: the N outputs are the two halves
+ * [first | second] of the MLP's fc projection and out[b][f] = second[f] * relu(first[f])^2 for f < N/2
+ * (out has N/2 columns; bf16 rounds the square as eager execution does) - InferenceMLP.forward's
+ * fc GEMM and squared_relu_gate in one launch (inference/models/atma.py:87-97); the plain form serves
+ * its proj GEMM, the LFM2 in_proj / out_proj (:631-673) and the LM head at these batch sizes.
+ * K a multiple of 32, N of 16 (32 when gated); x rows 16-byte aligned. */
+int atma_decode_linear(const void* x, int64_t x_row_stride, const void* weight, const void* bias, void* out,
+                       int64_t out_row_stride, int B, int N, int K, int gated, int dtype, void* stream);
+
 /* ------------------------------------------------------------------------------------
  * Gated-delta chunked scan.  Replaces the third-party flash-linear-attention call
  * chunk_gated_delta_rule(q,k,v,g,beta,scale=1,initial_state,output_final_state,

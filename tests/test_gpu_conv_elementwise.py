@@ -2,6 +2,7 @@
 
 import pytest
 import torch
+import torch.nn.functional as F
 
 import atma_b200
 import oracle
@@ -305,3 +306,42 @@ def test_empty_inputs_are_accepted_by_the_fused_entries():
                                              torch.zeros(0, 4, device=dev), torch.zeros(1, dtype=torch.int32), table,
                                              torch.zeros(0, dtype=torch.long))
     assert o.shape == (0, 4, 128) and bool((table == 1).all())
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,N,K,gated,bias", [(1, 8192, 1024, True, True), (8, 8192, 1024, True, False), (16, 1024, 4096, False, True),
+                                               (13, 3072, 1024, False, False), (5, 50304, 1024, False, False),
+                                               (3, 48, 64, False, True), (9, 64, 96, True, True)])
+def test_decode_linear_matches_the_separate_ops(dtype, B, N, K, gated, bias):
+    """The weight-streaming linear for decode batches against F.linear (+ squared_relu_gate): same fp32 accumulation and
+    rounding points, so nearly every element is identical and none is off by more than an ulp or two of the 16-bit type."""
+    g = torch.Generator().manual_seed(N + K + B)
+    x = torch.randn(B, K, generator=g).to(dtype).cuda()
+    w = (torch.randn(N, K, generator=g) / K ** 0.5).to(dtype).cuda()
+    b = (torch.randn(N, generator=g) * 0.1).to(dtype).cuda() if bias else None
+    got = atma_b200.decode_linear(x, w, b, gated=gated)
+    y32 = F.linear(x.float(), w.float(), None if b is None else b.float())
+    want = F.linear(x, w, b)
+    if gated:
+        h = N // 2
+        want = atma_b200.squared_relu_gate(want[:, :h], want[:, h:])
+        y16 = y32.to(dtype).float()
+        sq = torch.relu(y16[:, :h]) ** 2
+        ref32 = y16[:, h:] * (sq.to(dtype).float() if dtype == torch.bfloat16 else sq)
+    else:
+        ref32 = y32
+    assert got.shape == want.shape
+    scale = float(ref32.abs().max())
+    assert float((got.float() - ref32).abs().max()) < 2e-2 * scale
+    assert float((got.float() - want.float()).abs().max()) < 2e-2 * scale
+    assert float((got != want).float().mean()) < 0.05
+
+
+def test_decode_linear_rejects_what_it_does_not_serve():
+    x = torch.zeros(17, 64, dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(32, 64, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ValueError):
+        atma_b200.decode_linear(x, w)                                     # more than 16 rows
+    with pytest.raises(ValueError):
+        atma_b200.decode_linear(x[:4, :48].contiguous(), w[:, :48].contiguous())   # K not a multiple of 32
+    assert atma_b200.decode_linear(x[:0], w).shape == (0, 32)
