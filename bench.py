@@ -415,9 +415,7 @@ def profile_case(which):
         # the MLP of one layer at decode batch 8 (hidden 1024, 4x): fc + gate (16.8 MB of weights), proj (8.4 MB); the
         # weights cycle through 12 copies (302 MB) so that every launch reads them from HBM, not from L2
         import torch.nn.functional as F
-        Bs, D, Fh, copies = 8, 1024, 4096, 12
-        x = torch.randn(Bs, D, generator=g).bfloat16().to(dev)
-        a_in = torch.randn(Bs, Fh, generator=g).bfloat16().to(dev)
+        D, Fh, copies = 1024, 4096, 12
         w_fc = [(torch.randn(2 * Fh, D, generator=g) / 32).bfloat16().to(dev) for _ in range(copies)]
         w_pr = [(torch.randn(D, Fh, generator=g) / 64).bfloat16().to(dev) for _ in range(copies)]
 
@@ -435,15 +433,21 @@ def profile_case(which):
             ms = e0.elapsed_time(e1) / iters
             return {"ms": ms, "bytes_per_launch": nbytes, "gbs": nbytes / (ms * 1e-3) / 1e9}
 
-        def eager_fc(i):
-            y = F.linear(x, w_fc[i])
-            return ab.squared_relu_gate(y[:, :Fh], y[:, Fh:])
-        res = {
-            "decode_linear_fc_gated": timed_ring(lambda i: ab.decode_linear(x, w_fc[i], None, gated=True), 2.0 * 2 * Fh * D),
-            "cublas_fc_then_gate": timed_ring(eager_fc, 2.0 * 2 * Fh * D),
-            "decode_linear_proj": timed_ring(lambda i: ab.decode_linear(a_in, w_pr[i]), 2.0 * Fh * D),
-            "cublas_proj": timed_ring(lambda i: F.linear(a_in, w_pr[i]), 2.0 * Fh * D),
-        }
+        res = {}
+        for Bs in (8, 16, 64):
+            x = torch.randn(Bs, D, generator=g).bfloat16().to(dev)
+            a_in = torch.randn(Bs, Fh, generator=g).bfloat16().to(dev)
+
+            def eager_fc(i):
+                y = F.linear(x, w_fc[i])
+                return ab.squared_relu_gate(y[:, :Fh], y[:, Fh:])
+            r = {"cublas_fc_then_gate": timed_ring(eager_fc, 2.0 * 2 * Fh * D),
+                 "cublas_proj": timed_ring(lambda i: F.linear(a_in, w_pr[i]), 2.0 * Fh * D)}
+            if Bs <= 16:
+                r["decode_linear_fc_gated"] = timed_ring(lambda i: ab.decode_linear(x, w_fc[i], None, gated=True), 2.0 * 2 * Fh * D)
+                r["decode_linear_proj"] = timed_ring(lambda i: ab.decode_linear(a_in, w_pr[i]), 2.0 * Fh * D)
+            res[f"rows_{Bs}"] = r
+        Bs = "8, 16, 64"
         info = {"kernel": "decode_linear_kernel", "rows": Bs, **res}
     elif which in ("conv", "step", "prep_decode"):
         def timed_gbs(fn, nbytes, iters=10):
@@ -725,8 +729,10 @@ def run_context_parallel(args, ab, rank, local_rank, world, device, peaks):
     long_leg = None
     if not args.skip_long and T_PREFILL != 262144:
         long_leg = cp_long_prefill(cp, dist, rank, world, device, params, 262144, peaks)
-    config5 = None
+    config4 = config5 = None
     if not args.skip_model and T_PREFILL != 262144:
+        config4 = bench_model_decode_sharded(device, peaks, world, dist)
+        torch.cuda.empty_cache()
         config5 = cp_model_prefill(cp, dist, rank, world, device, peaks)
     # non-zero on any rank = a bounded wait of a tensor-core kernel ran out during this run
     status = torch.tensor([ab.device_status()], device=device, dtype=torch.int32)
@@ -768,6 +774,7 @@ def run_context_parallel(args, ab, rank, local_rank, world, device, peaks):
         "cpu_baseline": None,
         "decode": decode,
         "prefill_256k": long_leg,
+        "config4_model_decode": config4,
         "config5_model_prefill": config5,
         "device_status": int(status.item()),
     }
@@ -927,7 +934,7 @@ MODEL = dict(layers=16, hidden=1024, head_dim=128, num_kv_heads=2)
 VOCAB = 50304
 
 
-def bench_model_decode(device, peaks, steps=20):
+def bench_model_decode(device, peaks, steps=20, batch=None):
     """BASELINE config 4 on one GPU: the whole 16-layer model (12 LFM2 conv + 4 Polar/gated-delta layers, 378M
     random-init bf16 weights, seed 3), one decode step for 64 sequences with 32,768 tokens of context each in the
     paged cache (256-token pages in shuffled order), replayed from one CUDA graph."""
@@ -935,7 +942,7 @@ def bench_model_decode(device, peaks, steps=20):
     sd = random_state_dict(vocab=VOCAB, seed=3, device=device, **MODEL)
     model = AtmaModel(sd, device=device, **MODEL)
     del sd
-    B, ctx, bs = DEC_B, DEC_CTX, DEC_BLOCK
+    B, ctx, bs = (batch or DEC_B), DEC_CTX, DEC_BLOCK
     pages = ctx // bs
     state = model.new_state(max_seqs=B, num_blocks=B * pages, block_size=bs)
     g = torch.Generator(device=device).manual_seed(3)
@@ -967,7 +974,24 @@ def bench_model_decode(device, peaks, steps=20):
                         f"pages of {bs}", "ms_per_step": ms, "value": B / (ms * 1e-3), "unit": "tok/s", "steps": steps,
             "cuda_graph": True, "logits_finite": finite, "algorithmic_bytes": nbytes,
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s", "frac": gbs / peaks["hbm"]},
-            "projections": "cuBLAS (F.linear); everything between them this library"}
+            "projections": ("this library's weight-streaming kernel (batches of up to 16 rows) where its shape rules allow, else cuBLAS"
+                            if B <= 16 else "cuBLAS (F.linear); everything between them this library")}
+
+
+def bench_model_decode_sharded(device, peaks, world, dist):
+    """BASELINE config 4 with its 64 sequences split over the ranks (no collective): every rank decodes 64/N sequences
+    through the whole model; the aggregate is 64 tokens per slowest-rank step."""
+    d = bench_model_decode(device, peaks, batch=DEC_B // world)
+    t = torch.tensor([d["ms_per_step"]], device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    d["ms_per_step"], d["value"] = ms, DEC_B / (ms * 1e-3)
+    d["batch_per_gpu"], d["sharding"] = DEC_B // world, "batch, no collective"
+    nbytes = d["algorithmic_bytes"]
+    d["roofline"]["achieved"] = nbytes / (ms * 1e-3) / 1e9
+    d["roofline"]["frac"] = d["roofline"]["achieved"] / peaks["hbm"]
+    d["roofline"]["note"] = "per GPU: this rank's bytes (all weights + its sequences' K/V and state) over the slowest rank's step"
+    return d
 
 
 def bench_model_prefill(device, peaks, tokens=262144, steps=2):

@@ -345,3 +345,4 @@ def test_decode_linear_rejects_what_it_does_not_serve():
     with pytest.raises(ValueError):
         atma_b200.decode_linear(x[:4, :48].contiguous(), w[:, :48].contiguous())   # K not a multiple of 32
     assert atma_b200.decode_linear(x[:0], w).shape == (0, 32)
+    assert atma_b200.device_status() == 0
