@@ -59,6 +59,21 @@ template <> __device__ __forceinline__ void load8<__half>(const __half* p, float
 #pragma unroll
   for (int i = 0; i < 4; ++i) { const float2 f = __half22float2(h[i]); o[2 * i] = f.x; o[2 * i + 1] = f.y; }
 }
+// eight 16-bit values held in a uint4 register quad -> fp32
+template <typename T> __device__ __forceinline__ void unpack8(const uint4& u, float (&o)[8]) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+      o[2 * i] = __uint_as_float(w[i] << 16);
+      o[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    } else {
+      const __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
+      const float2 f = __half22float2(h);
+      o[2 * i] = f.x; o[2 * i + 1] = f.y;
+    }
+  }
+}
 template <typename T> __device__ __forceinline__ void store8(T* p, const float (&v)[8]);
 template <> __device__ __forceinline__ void store8<float>(float* p, const float (&v)[8]) {
   *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
@@ -323,8 +338,184 @@ qkv_prep_kernel(const PrepArgs a) {
   }
 }
 
+// ---- direct form (16-bit types, head_dim 128) -------------------------------------------------------------
+// No shared-memory tile and no CTA-wide barrier: a half warp (16 lanes x 8 channels = one head row of 128
+// channels) owns a run of kDirTok consecutive tokens of one head; every lane requests the kDirTok + K - 1 rows
+// of its run as 16-byte loads before the first use (the halo rows are the neighbouring run's rows, i.e. cache
+// hits), normalises each row in registers (row sum by shuffles inside the half warp), slides an fp32 window of
+// K rows over them and writes q, k, v and the cache rows once.  Runs that touch a sequence start or end - two
+// per sequence and head - take a per-token path that re-reads and re-normalises its taps.  The two half warps of
+// a warp are independent: their shuffles name only their own sixteen lanes.
+constexpr int kDirTok = 8;
+
+template <typename T, int K>
+__global__ void __launch_bounds__(128, 4)
+qkv_prep_direct_kernel(const PrepArgs a, const int vec_weights) {
+  const int lane = threadIdx.x & 31;
+  const int li = lane & 15;
+  const int units = a.H + 2 * a.Hkv;
+  const int n_runs = (a.total + kDirTok - 1) / kDirTok;
+  const int64_t hw = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 4;     // half-warp index
+  const bool hw_on = hw < (int64_t)units * n_runs;
+  const int u = hw_on ? (int)(hw % units) : 0;
+  const int run = hw_on ? (int)(hw / units) : 0;
+  const int which = u < a.H ? 0 : (u < a.H + a.Hkv ? 1 : 2);
+  const int head = which == 0 ? u : (which == 1 ? u - a.H : u - a.H - a.Hkv);
+  const int heads = which == 0 ? a.H : a.Hkv;
+  const int dk = a.dk, c = li * 8, ch = head * dk + c;
+  const T* src = which == 0 ? (const T*)a.qg + (int64_t)head * a.qg_head + c
+                            : (which == 1 ? (const T*)a.k + head * dk + c : (const T*)a.v + head * dk + c);
+  const int64_t row_st = which == 0 ? a.qg_row : (which == 1 ? a.k_row : a.v_row);
+  const bool normalize = which != 2;
+  const float inv_dk = 1.0f / (float)dk;
+  T* dst = (T*)(which == 0 ? a.q_out : (which == 1 ? a.k_out : a.v_out)) + head * dk + c;
+  T* cache = (which == 0 || a.k_cache == nullptr) ? nullptr : (T*)(which == 1 ? a.k_cache : a.v_cache) + head * dk + c;
+  const int64_t dst_row = (int64_t)heads * dk, cache_row = (int64_t)a.Hkv * dk;
+  T* state = (T*)a.state[which];
+  const T* init = (const T*)a.init[which];
+  const int64_t state_ss = a.state_ss[which];
+  const int t0 = run * kDirTok;
+  const int nt = hw_on ? min(kDirTok, a.total - t0) : 0;
+
+  float wt[8][K];
+  {
+    const T* w = (const T*)a.w[which] + (int64_t)ch * K;
+    if (vec_weights) {
+      union { uint4 u4[K]; T e[8 * K]; } wv;
+#pragma unroll
+      for (int i = 0; i < K; ++i) wv.u4[i] = *reinterpret_cast<const uint4*>(w + i * 8);
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int kk = 0; kk < K; ++kk) wt[j][kk] = to_f32(wv.e[j * K + kk]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int kk = 0; kk < K; ++kk) wt[j][kk] = to_f32(w[j * K + kk]);
+    }
+  }
+  if (!hw_on) return;
+  const uint32_t half_mask = 0xffffu << (16 * (lane >> 4));
+  // normalise one row held as eight fp32 values (q and k; v passes through)
+  auto norm_row = [&](float (&x)[8]) {
+    if (normalize) {
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss = fmaf(x[j], x[j], ss);
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(half_mask, ss, o, 16);
+      const float rs = rsqrtf(ss * inv_dk + a.eps);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] *= rs;
+      round8<T>(x);                                              // the eager op rounds to T here
+    }
+  };
+
+  int sa = 0, ea = 0;
+  bool plain = false;
+  if (nt > 0) {
+    sa = a.seq_start[t0];
+    ea = a.seq_end[t0 + nt - 1];
+    plain = nt == kDirTok && sa == a.seq_start[t0 + nt - 1] && ea > t0 + nt && sa <= t0 - (K - 1);
+  }
+  if (plain) {
+    uint4 raw[kDirTok + K - 1];
+#pragma unroll
+    for (int rl = 0; rl < kDirTok + K - 1; ++rl)
+      raw[rl] = *reinterpret_cast<const uint4*>(src + (int64_t)(t0 - (K - 1) + rl) * row_st);
+    float win[K][8];
+#pragma unroll
+    for (int rl = 0; rl < kDirTok + K - 1; ++rl) {
+      float (&x)[8] = win[rl % K];
+      unpack8<T>(raw[rl], x);
+      norm_row(x);
+      if (rl >= K - 1) {
+        const int i = rl - (K - 1);
+        float y[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float acc = 0.f;
+#pragma unroll
+          for (int kk = 0; kk < K; ++kk) acc = fmaf(win[(rl - (K - 1) + kk) % K][j], wt[j][kk], acc);
+          y[j] = acc;
+        }
+        round8<T>(y);                                            // the conv rounded as eager does, then x + conv(x)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) y[j] += x[j];
+        store8<T>(dst + (int64_t)(t0 + i) * dst_row, y);
+        if (cache != nullptr) {
+          const long long cs = a.slot_mapping[t0 + i];
+          if (cs >= 0) store8<T>(cache + cs * cache_row, y);
+        }
+      }
+    }
+    return;
+  }
+  // ---- runs that touch a sequence border: token by token, tap by tap ---------------------------------------------
+#pragma unroll 1
+  for (int i = 0; i < kDirTok; ++i) {
+    const int t = t0 + i;
+    const bool t_on = t < a.total;                               // the same for the sixteen lanes
+    const int tc = t_on ? t : 0;
+    const int s0 = a.seq_start[tc], e0 = a.seq_end[tc], slot = a.seq_slot[tc];
+    const bool from_state = init != nullptr && slot >= 0;
+    float acc[8], cur[8], keep[K][8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < K; ++kk) {
+      const int back = K - 1 - kk, srow = tc - back;
+      float x[8];
+      load8<T>(src + (int64_t)max(srow, 0) * row_st, x);         // clamped; replaced below when before the start
+      norm_row(x);
+      if (srow < s0) {                                           // before the sequence start: saved state or zero
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          x[j] = from_state ? to_f32(init[slot * state_ss + (int64_t)(ch + j) * (K - 1) + (K - 1) - (s0 - srow)]) : 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { acc[j] = fmaf(x[j], wt[j][kk], acc[j]); keep[kk][j] = x[j]; }
+      if (kk == K - 1) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) cur[j] = x[j];
+      }
+    }
+    if (!t_on) continue;
+    round8<T>(acc);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] += cur[j];
+    store8<T>(dst + (int64_t)t * dst_row, acc);
+    if (cache != nullptr) {
+      const long long cs = a.slot_mapping[t];
+      if (cs >= 0) store8<T>(cache + cs * cache_row, acc);
+    }
+    if (t == e0 - 1 && state != nullptr && slot >= 0) {          // closes its sequence: its last K-1 conv inputs, oldest first
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int kk = 0; kk < K - 1; ++kk)
+          state[slot * state_ss + (int64_t)(ch + j) * (K - 1) + kk] = from_f32<T>(keep[kk + 1][j]);
+    }
+  }
+}
+
 template <typename T>
 int launch_prep(const PrepArgs& a, cudaStream_t st) {
+  if constexpr (sizeof(T) == 2) {
+    if (a.dk == 128) {                                           // the direct form: no shared-memory tile
+      const int64_t half_warps = (int64_t)(a.H + 2 * a.Hkv) * ((a.total + kDirTok - 1) / kDirTok);
+      const dim3 dgrid((unsigned)((half_warps * 16 + 127) / 128)), dblock(128);
+      const int vec_w = ((reinterpret_cast<uintptr_t>(a.w[0]) | reinterpret_cast<uintptr_t>(a.w[1]) |
+                          reinterpret_cast<uintptr_t>(a.w[2])) & 15) == 0 ? 1 : 0;
+      switch (a.K) {
+        case 2: qkv_prep_direct_kernel<T, 2><<<dgrid, dblock, 0, st>>>(a, vec_w); break;
+        case 3: qkv_prep_direct_kernel<T, 3><<<dgrid, dblock, 0, st>>>(a, vec_w); break;
+        default: qkv_prep_direct_kernel<T, 4><<<dgrid, dblock, 0, st>>>(a, vec_w); break;
+      }
+      return launch_status("qkv_prep_prefill");
+    }
+  }
   const int smem = (kPrepTok + a.K - 1) * kPrepHeads * a.dk * (int)sizeof(T);
   dim3 grid((a.total + kPrepTok - 1) / kPrepTok, a.nq + (2 * a.Hkv + kPrepHeads - 1) / kPrepHeads), block(kPrepThreads);
 #define ATMA_PREP_CASE(KK)                                                                                 \

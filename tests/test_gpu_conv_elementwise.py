@@ -148,14 +148,17 @@ def _prep_case(dtype, lens, H=4, Hkv=2, dk=128, K=4, seed=0, rows=6):
     return q_gate, k, v, w, states, i32(starts), i32(ends), i32(sl), k_cache, v_cache, slot_mapping
 
 
-@pytest.mark.parametrize("dtype,tol", [(torch.bfloat16, 2e-2), (torch.float32, 1e-4)])
+@pytest.mark.parametrize("dtype,tol,dk,lens", [(torch.bfloat16, 2e-2, 128, [2, 37, 1, 64, 29]),      # direct form, border runs
+                                                (torch.bfloat16, 2e-2, 128, [300, 5, 1, 260, 70]),    # direct form, long runs
+                                                (torch.float16, 4e-3, 128, [2, 37, 1, 64, 29]),
+                                                (torch.bfloat16, 2e-2, 64, [2, 37, 1, 64, 29]),       # shared-memory tile form
+                                                (torch.float32, 1e-4, 128, [2, 37, 1, 64, 29])])
 @pytest.mark.parametrize("continued", [False, True])
-def test_qkv_prep_prefill_matches_the_op_by_op_oracle(dtype, tol, continued):
+def test_qkv_prep_prefill_matches_the_op_by_op_oracle(dtype, tol, dk, lens, continued):
     """Ragged packed sequences (shorter than the kernel, crossing the 32-token tile, one without a
     state slot): the fused launch == rms_norm + x + conv(x) + state write + store_kvcache run op by
     op on the CPU; state rows and cache rows that nothing addresses stay as they were."""
-    lens = [2, 37, 1, 64, 29]
-    q_gate, k, v, w, states, s0, e0, sl, k_cache, v_cache, sm = _prep_case(dtype, lens, seed=3)
+    q_gate, k, v, w, states, s0, e0, sl, k_cache, v_cache, sm = _prep_case(dtype, lens, dk=dk, seed=3)
     init = [s.clone() for s in states] if continued else None
     ref_states = [s.clone() for s in states]
     ref_kc, ref_vc = k_cache.clone(), v_cache.clone()
