@@ -340,11 +340,18 @@ class AtmaModel:
 
     # ---- one decode step ---------------------------------------------------------------------------------
     @torch.no_grad()
-    def decode(self, ids, state, seq_slots, slot_mapping, block_tables, context_lens):
+    def decode(self, ids, state, seq_slots, slot_mapping, block_tables, context_lens, *, local_lens=None, group=None):
         """One token per sequence: ids (B,), seq_slots (B,) int64 state rows, slot_mapping (B,) int32 cache rows
         of the new token, block_tables (B, max_blocks) int32, context_lens (B,) int32 INCLUDING the new token.
         All arguments are device tensors with fixed shapes, nothing synchronises: the call can be captured in
-        a CUDA graph (inference/engine/model_runner.py:254-310).  Returns soft-capped logits (B, vocab)."""
+        a CUDA graph (inference/engine/model_runner.py:254-310).  Returns soft-capped logits (B, vocab).
+
+        ``local_lens`` (B,) int32: the step runs over a cache that a context-parallel prefill left spread over the
+        ranks of ``group``.  Every rank makes the same call with the same ids and state (the step is replicated);
+        ``block_tables`` and ``local_lens`` then describe THIS rank's pages and key count (the new token included on
+        the one rank whose ``slot_mapping`` entry is not -1, which stores its K/V row), ``context_lens`` stays the
+        whole context.  The attention of each global layer becomes ``cp_polar_decode``: local partial statistics,
+        one small all-gather, the single-GPU merge; full-context attention only."""
         sd, H, Hkv, dk, D = self.sd, self.H, self.Hkv, self.dk, self.D
         B = ids.shape[0]
         x = sd["embed.weight"][ids]
@@ -381,9 +388,18 @@ class AtmaModel:
                     r = gated_delta_decode_step(q, k.repeat_interleave(G, 1), v.repeat_interleave(G, 1), gamma, beta,
                                                 state.mem[i], seq_slots)
                     r_out.copy_(rms_sigmoid_gate(r.to(x.dtype), mem_gate))
-                polar_attention_decode(q, state.k_cache[i], state.v_cache[i], block_tables, context_lens, window=self.window,
-                                       gate=q_gate[..., dk:], out=(act[:, :H * dk].view(B, H, dk), act[:, H * dk:H * dk + H]),
-                                       **pk["polar"])
+                if local_lens is None:
+                    polar_attention_decode(q, state.k_cache[i], state.v_cache[i], block_tables, context_lens, window=self.window,
+                                           gate=q_gate[..., dk:], out=(act[:, :H * dk].view(B, H, dk), act[:, H * dk:H * dk + H]),
+                                           **pk["polar"])
+                else:
+                    from .context_parallel import cp_polar_decode
+                    if self.window is not None:
+                        raise ValueError("decode over a context-parallel cache is full-context attention only")
+                    c, mag = cp_polar_decode(q, state.k_cache[i], state.v_cache[i], block_tables, local_lens, context_lens,
+                                             pk["polar"], group=group)
+                    act[:, :H * dk] = sigmoid_gate_mul(c, q_gate[..., dk:]).view(B, H * dk)
+                    act[:, H * dk:H * dk + H] = mag
                 if dk == 128:
                     cur.wait_stream(side)                                        # join the memory branch
                 mix = self._linear(act, pk["w_out"], pk["b_out"])                          # W_o, W_mu and mem.proj in one product

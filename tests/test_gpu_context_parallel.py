@@ -170,13 +170,13 @@ def _model_worker(rank, world, port, ret):
         model = AtmaModel(sd, device=dev, **MODEL_CFG)
         ids = torch.randint(0, 640, (MODEL_T,), generator=torch.Generator().manual_seed(9))
         # the single-GPU prefill of the whole prompt (every rank computes it for itself)
-        pages = MODEL_T // MODEL_BLOCK
+        pages = MODEL_T // MODEL_BLOCK + 1
         ref_state = model.new_state(max_seqs=2, num_blocks=pages, block_size=MODEL_BLOCK)
         h_ref = model.prefill(ids, [MODEL_T], [1], ref_state, torch.arange(MODEL_T))
         # context-parallel: this rank's two zig-zag segments, K/V of its own tokens in its own pages
         (a0, a1), (b0, b1) = cp.zigzag_segments(MODEL_T, world)[rank]
         L = a1 - a0
-        state = model.new_state(max_seqs=2, num_blocks=2 * L // MODEL_BLOCK, block_size=MODEL_BLOCK)
+        state = model.new_state(max_seqs=2, num_blocks=2 * L // MODEL_BLOCK + 1, block_size=MODEL_BLOCK)
         h = model.prefill_context_parallel([ids[a0:a1], ids[b0:b1]], [(a0, a1), (b0, b1)], state, 1,
                                            [torch.arange(L), torch.arange(L, 2 * L)])
         torch.cuda.synchronize()
@@ -189,6 +189,23 @@ def _model_worker(rank, world, port, ret):
         mine = state.k_cache[gl].view(-1, model.Hkv, model.dk)
         whole = ref_state.k_cache[gl].view(-1, model.Hkv, model.dk)
         out["kv"] = max(rel(mine[:L], whole[a0:a1]), rel(mine[L:2 * L], whole[b0:b1]))
+        # decode three tokens over the distributed cache (every rank the same call; the owner of the last segment stores
+        # the new K/V rows behind its own) against the single-GPU decode that continues the single-GPU prefill
+        owner = cp.segment_owner(2 * world - 1, world) == rank
+        slot1 = torch.tensor([1], device=dev)
+        nxt = torch.randint(0, 640, (3,), generator=torch.Generator().manual_seed(11))
+        bt_local = torch.arange(state.k_cache[gl].shape[0], dtype=torch.int32, device=dev)[None]
+        bt_ref = torch.arange(ref_state.k_cache[gl].shape[0], dtype=torch.int32, device=dev)[None]
+        worst = 0.0
+        for t in range(3):
+            tok = nxt[t:t + 1].to(dev)
+            total = torch.tensor([MODEL_T + t + 1], dtype=torch.int32, device=dev)
+            lg_ref = model.decode(tok, ref_state, slot1, torch.tensor([MODEL_T + t], dtype=torch.int32, device=dev), bt_ref, total)
+            local = torch.tensor([2 * L + (t + 1 if owner else 0)], dtype=torch.int32, device=dev)
+            sm_new = torch.tensor([2 * L + t if owner else -1], dtype=torch.int32, device=dev)
+            lg = model.decode(tok, state, slot1, sm_new, bt_local, total, local_lens=local)
+            worst = max(worst, rel(lg, lg_ref))
+        out["decode"] = worst
         ret[rank] = out
     finally:
         dist.destroy_process_group()
@@ -216,3 +233,4 @@ def test_context_parallel_model_prefill_matches_one_gpu(world):
         r = ret[rank]
         assert max(r["h"]) < 2e-2, r
         assert r["mem"] < 2e-2 and r["conv"] < 1e-2 and r["kv"] < 1e-2, r
+        assert r["decode"] < 2e-2, r
