@@ -346,7 +346,8 @@ qkv_prep_kernel(const PrepArgs a) {
 // K rows over them and writes q, k, v and the cache rows once.  Runs that touch a sequence start or end - two
 // per sequence and head - take a per-token path that re-reads and re-normalises its taps.  The two half warps of
 // a warp are independent: their shuffles name only their own sixteen lanes.
-constexpr int kDirTok = 8;
+constexpr int kDirTok = 8;                      // tokens per group (all loads of a group in flight together)
+constexpr int kDirGroups = 4;                   // consecutive groups per half warp
 
 template <typename T, int K>
 __global__ void __launch_bounds__(128, 4)
@@ -354,7 +355,7 @@ qkv_prep_direct_kernel(const PrepArgs a, const int vec_weights) {
   const int lane = threadIdx.x & 31;
   const int li = lane & 15;
   const int units = a.H + 2 * a.Hkv;
-  const int n_runs = (a.total + kDirTok - 1) / kDirTok;
+  const int n_runs = (a.total + kDirTok * kDirGroups - 1) / (kDirTok * kDirGroups);
   const int64_t hw = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 4;     // half-warp index
   const bool hw_on = hw < (int64_t)units * n_runs;
   const int u = hw_on ? (int)(hw % units) : 0;
@@ -374,8 +375,6 @@ qkv_prep_direct_kernel(const PrepArgs a, const int vec_weights) {
   T* state = (T*)a.state[which];
   const T* init = (const T*)a.init[which];
   const int64_t state_ss = a.state_ss[which];
-  const int t0 = run * kDirTok;
-  const int nt = hw_on ? min(kDirTok, a.total - t0) : 0;
 
   float wt[8][K];
   {
@@ -412,46 +411,61 @@ qkv_prep_direct_kernel(const PrepArgs a, const int vec_weights) {
     }
   };
 
-  int sa = 0, ea = 0;
-  bool plain = false;
-  if (nt > 0) {
-    sa = a.seq_start[t0];
-    ea = a.seq_end[t0 + nt - 1];
-    plain = nt == kDirTok && sa == a.seq_start[t0 + nt - 1] && ea > t0 + nt && sa <= t0 - (K - 1);
-  }
+  // The half warp walks kDirGroups consecutive groups of kDirTok tokens.  After a group that lay inside one sequence
+  // the last K-1 normalised rows are still in registers and serve as the next group's left context, so only the
+  // first such group of a stretch pays for its halo rows.
+  float prevw[K - 1][8];                                          // the K-1 conv inputs before the next row, oldest first
+  bool have_prev = false;
+#pragma unroll 1
+  for (int gi = 0; gi < kDirGroups; ++gi) {
+  const int t0 = run * (kDirTok * kDirGroups) + gi * kDirTok;
+  if (t0 >= a.total) break;
+  const int nt = min(kDirTok, a.total - t0);
+  const int sa = a.seq_start[t0], ea = a.seq_end[t0 + nt - 1];
+  const bool plain = nt == kDirTok && sa == a.seq_start[t0 + nt - 1] && ea > t0 + nt && sa <= t0 - (K - 1);
   if (plain) {
-    uint4 raw[kDirTok + K - 1];
+    uint4 raw[kDirTok];
 #pragma unroll
-    for (int rl = 0; rl < kDirTok + K - 1; ++rl)
-      raw[rl] = *reinterpret_cast<const uint4*>(src + (int64_t)(t0 - (K - 1) + rl) * row_st);
-    float win[K][8];
+    for (int rl = 0; rl < kDirTok; ++rl) raw[rl] = *reinterpret_cast<const uint4*>(src + (int64_t)(t0 + rl) * row_st);
+    if (!have_prev) {
 #pragma unroll
-    for (int rl = 0; rl < kDirTok + K - 1; ++rl) {
-      float (&x)[8] = win[rl % K];
-      unpack8<T>(raw[rl], x);
-      norm_row(x);
-      if (rl >= K - 1) {
-        const int i = rl - (K - 1);
-        float y[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          float acc = 0.f;
-#pragma unroll
-          for (int kk = 0; kk < K; ++kk) acc = fmaf(win[(rl - (K - 1) + kk) % K][j], wt[j][kk], acc);
-          y[j] = acc;
-        }
-        round8<T>(y);                                            // the conv rounded as eager does, then x + conv(x)
-#pragma unroll
-        for (int j = 0; j < 8; ++j) y[j] += x[j];
-        store8<T>(dst + (int64_t)(t0 + i) * dst_row, y);
-        if (cache != nullptr) {
-          const long long cs = a.slot_mapping[t0 + i];
-          if (cs >= 0) store8<T>(cache + cs * cache_row, y);
-        }
+      for (int kk = 0; kk < K - 1; ++kk) {
+        load8<T>(src + (int64_t)(t0 - (K - 1) + kk) * row_st, prevw[kk]);
+        norm_row(prevw[kk]);
       }
     }
-    return;
+#pragma unroll
+    for (int rl = 0; rl < kDirTok; ++rl) {
+      float x[8];
+      unpack8<T>(raw[rl], x);
+      norm_row(x);
+      float y[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float acc = 0.f;
+#pragma unroll
+        for (int kk = 0; kk < K - 1; ++kk) acc = fmaf(prevw[kk][j], wt[j][kk], acc);
+        y[j] = fmaf(x[j], wt[j][K - 1], acc);
+      }
+      round8<T>(y);                                              // the conv rounded as eager does, then x + conv(x)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) y[j] += x[j];
+      store8<T>(dst + (int64_t)(t0 + rl) * dst_row, y);
+      if (cache != nullptr) {
+        const long long cs = a.slot_mapping[t0 + rl];
+        if (cs >= 0) store8<T>(cache + cs * cache_row, y);
+      }
+#pragma unroll
+      for (int kk = 0; kk + 1 < K - 1; ++kk)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) prevw[kk][j] = prevw[kk + 1][j];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) prevw[K - 2][j] = x[j];
+    }
+    have_prev = true;
+    continue;
   }
+  have_prev = false;
   // ---- runs that touch a sequence border: token by token, tap by tap ---------------------------------------------
 #pragma unroll 1
   for (int i = 0; i < kDirTok; ++i) {
@@ -498,13 +512,14 @@ qkv_prep_direct_kernel(const PrepArgs a, const int vec_weights) {
           state[slot * state_ss + (int64_t)(ch + j) * (K - 1) + kk] = from_f32<T>(keep[kk + 1][j]);
     }
   }
+  }                                                              // next group of the half warp
 }
 
 template <typename T>
 int launch_prep(const PrepArgs& a, cudaStream_t st) {
   if constexpr (sizeof(T) == 2) {
     if (a.dk == 128) {                                           // the direct form: no shared-memory tile
-      const int64_t half_warps = (int64_t)(a.H + 2 * a.Hkv) * ((a.total + kDirTok - 1) / kDirTok);
+      const int64_t half_warps = (int64_t)(a.H + 2 * a.Hkv) * ((a.total + kDirTok * kDirGroups - 1) / (kDirTok * kDirGroups));
       const dim3 dgrid((unsigned)((half_warps * 16 + 127) / 128)), dblock(128);
       const int vec_w = ((reinterpret_cast<uintptr_t>(a.w[0]) | reinterpret_cast<uintptr_t>(a.w[1]) |
                           reinterpret_cast<uintptr_t>(a.w[2])) & 15) == 0 ? 1 : 0;
