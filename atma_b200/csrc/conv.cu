@@ -92,7 +92,8 @@ __global__ void packed_conv_kernel(const T* __restrict__ x, int64_t x_st, const 
 // keeps 11 loads in flight and every input row is read once from memory (the K-1 rows of overlap with
 // the neighbouring run hit L2); the taps then index registers.  A run that lies inside one sequence and
 // does not close it skips the per-token sequence maps.  Same accumulation order as the scalar form.
-constexpr int kVecTok = 8;
+constexpr int kVecTok = 8;                          // tokens per group (all loads of a group in flight together)
+constexpr int kVecGroups = 4;                       // consecutive groups per thread
 
 template <typename T> struct Vec16 {
   static constexpr int N = 16 / sizeof(T);
@@ -122,7 +123,7 @@ __device__ __noinline__ void conv_state_write(T* __restrict__ dst, const uint4* 
 }
 
 template <typename T, int K>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 4)
 packed_conv_vec_kernel(const T* __restrict__ x, int64_t x_st, const T* __restrict__ w, T* __restrict__ out,
                        int64_t out_st, T* __restrict__ state, const T* __restrict__ init_state, int64_t state_ss,
                        const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_end,
@@ -132,18 +133,8 @@ packed_conv_vec_kernel(const T* __restrict__ x, int64_t x_st, const T* __restric
   const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int cg = (int)(gid % groups);
   const int64_t run = gid / groups;
-  if (run * kVecTok >= total) return;
-  const int t0 = (int)(run * kVecTok);
+  if (run * (kVecTok * kVecGroups) >= total) return;
   const int c0 = cg * N;
-  const int nt = min(kVecTok, total - t0);
-
-  Vec16<T> rows[kVecTok + K - 1];                     // rows[i] = packed row t0 - (K-1) + i
-#pragma unroll
-  for (int i = 0; i < kVecTok + K - 1; ++i) {
-    const int t = t0 - (K - 1) + i;
-    if (t >= 0 && t < total) rows[i].u = *reinterpret_cast<const uint4*>(x + (int64_t)t * x_st + c0);
-    else rows[i].u = make_uint4(0u, 0u, 0u, 0u);
-  }
   // the thread's N x K weights are neighbours in memory ([C][K]): N*K*sizeof(T) bytes as 16-byte loads
   float wt[N][K];
   {
@@ -156,31 +147,64 @@ packed_conv_vec_kernel(const T* __restrict__ x, int64_t x_st, const T* __restric
 #pragma unroll
       for (int j = 0; j < K; ++j) wt[n][j] = to_f32(wv[(n * K + j) / N].e[(n * K + j) % N]);
   }
-
+  // The thread walks kVecGroups consecutive groups of kVecTok tokens; after a group that lay inside one sequence its
+  // last K-1 rows are still in registers (fp32) and serve as the next group's left context.
+  float prevw[K - 1][N];
+  bool have_prev = false;
+#pragma unroll 1
+  for (int gi = 0; gi < kVecGroups; ++gi) {
+  const int64_t t0l = (run * kVecGroups + gi) * kVecTok;
+  if (t0l >= total) break;
+  const int t0 = (int)t0l;
+  const int nt = min(kVecTok, total - t0);
   const int sa = seq_start[t0], ea = seq_end[t0 + nt - 1], sla = seq_slot[t0];
-  const bool uniform = sa == seq_start[t0 + nt - 1] && ea > t0 + nt;   // one sequence, not closed inside the run
-  if (uniform && sa <= t0 - (K - 1)) {
-    // common case: the run and its K-1 rows of left context lie inside one sequence.  Each row is converted
-    // to fp32 once and slides through a K-row register window.
-    float win[K][N];
+  const bool uniform = sa == seq_start[t0 + nt - 1] && ea > t0 + nt;   // one sequence, not closed inside the group
+  if (uniform && nt == kVecTok && sa <= t0 - (K - 1)) {
+    // common case: the group and its K-1 rows of left context lie inside one sequence
+    Vec16<T> cur[kVecTok];
 #pragma unroll
-    for (int rl = 0; rl < kVecTok + K - 1; ++rl) {
+    for (int i = 0; i < kVecTok; ++i) cur[i].u = *reinterpret_cast<const uint4*>(x + (int64_t)(t0 + i) * x_st + c0);
+    if (!have_prev) {
 #pragma unroll
-      for (int n = 0; n < N; ++n) win[rl % K][n] = to_f32(rows[rl].e[n]);
-      if (rl >= K - 1 && rl - (K - 1) < nt) {
-        Vec16<T> o;
+      for (int j = 0; j < K - 1; ++j) {
+        Vec16<T> h;
+        h.u = *reinterpret_cast<const uint4*>(x + (int64_t)(t0 - (K - 1) + j) * x_st + c0);
 #pragma unroll
-        for (int n = 0; n < N; ++n) {
-          float acc = 0.f;
-#pragma unroll
-          for (int j = 0; j < K; ++j) acc = fmaf(win[(rl - (K - 1) + j) % K][n], wt[n][j], acc);
-          if (residual) acc += win[rl % K][n];
-          o.e[n] = from_f32<T>(acc);
-        }
-        *reinterpret_cast<uint4*>(out + (int64_t)(t0 + rl - (K - 1)) * out_st + c0) = o.u;
+        for (int n = 0; n < N; ++n) prevw[j][n] = to_f32(h.e[n]);
       }
     }
-    return;
+#pragma unroll
+    for (int i = 0; i < kVecTok; ++i) {
+      Vec16<T> o;
+      float xc[N];
+#pragma unroll
+      for (int n = 0; n < N; ++n) {
+        xc[n] = to_f32(cur[i].e[n]);
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < K - 1; ++j) acc = fmaf(prevw[j][n], wt[n][j], acc);
+        acc = fmaf(xc[n], wt[n][K - 1], acc);
+        if (residual) acc += xc[n];
+        o.e[n] = from_f32<T>(acc);
+      }
+      *reinterpret_cast<uint4*>(out + (int64_t)(t0 + i) * out_st + c0) = o.u;
+#pragma unroll
+      for (int j = 0; j + 1 < K - 1; ++j)
+#pragma unroll
+        for (int n = 0; n < N; ++n) prevw[j][n] = prevw[j + 1][n];
+#pragma unroll
+      for (int n = 0; n < N; ++n) prevw[K - 2][n] = xc[n];
+    }
+    have_prev = true;
+    continue;
+  }
+  have_prev = false;
+  Vec16<T> rows[kVecTok + K - 1];                     // rows[i] = packed row t0 - (K-1) + i
+#pragma unroll
+  for (int i = 0; i < kVecTok + K - 1; ++i) {
+    const int t = t0 - (K - 1) + i;
+    if (t >= 0 && t < total) rows[i].u = *reinterpret_cast<const uint4*>(x + (int64_t)t * x_st + c0);
+    else rows[i].u = make_uint4(0u, 0u, 0u, 0u);
   }
 #pragma unroll 1
   for (int i = 0; i < nt; ++i) {
@@ -218,6 +242,7 @@ packed_conv_vec_kernel(const T* __restrict__ x, int64_t x_st, const T* __restric
       conv_state_write<T, K>(state + sl * state_ss + (int64_t)c0 * (K - 1), keep);
     }
   }
+  }                                                   // next group of the thread
 }
 
 template <typename T>
@@ -251,7 +276,7 @@ int launch_packed_conv(const void* x, int64_t x_st, const void* w, void* out, in
                        const int32_t* s0, const int32_t* e0, const int32_t* sl, int total, int C,
                        int K, int residual, cudaStream_t st) {
   if (conv_vec_ok<T>(x, x_st, w, out, out_st, C)) {
-    const int64_t threads = (int64_t)(C / (16 / (int)sizeof(T))) * ((total + kVecTok - 1) / kVecTok);
+    const int64_t threads = (int64_t)(C / (16 / (int)sizeof(T))) * ((total + kVecTok * kVecGroups - 1) / (kVecTok * kVecGroups));
     dim3 grid((unsigned)((threads + 127) / 128)), block(128);
     switch (K) {
       case 2: packed_conv_vec_kernel<T, 2><<<grid, block, 0, st>>>((const T*)x, x_st, (const T*)w, (T*)out, out_st, (T*)state, (const T*)init_state, state_ss, s0, e0, sl, total, C, residual); break;
