@@ -193,6 +193,20 @@ scan_local_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
 #pragma unroll
           for (int cb = 0; cb < 2; ++cb)
             tma_load_4d(Vs + cb * 16384 + ci * 8192, &tmap_v, &bar.v_full, cb * 64, m.hk, (int)m.t0[ci], 0);
+        // the shared-memory tiles stay busy until this tile's last products; meanwhile bring the next tile's
+        // inputs into L2, so that its loads do not wait for DRAM
+        if (tile + gridDim.x < p.n_tiles) {
+          Meta mn;
+          tile_meta(p, tile + gridDim.x, mn);
+#pragma unroll
+          for (int ci = 0; ci < 2; ++ci)
+#pragma unroll
+            for (int cb = 0; cb < 2; ++cb) {
+              tma_prefetch_l2_4d(&tmap_k, cb * 64, mn.hk, (int)mn.t0[ci], 0);
+              tma_prefetch_l2_4d(&tmap_q, cb * 64, mn.h, (int)mn.t0[ci], 0);
+              tma_prefetch_l2_4d(&tmap_v, cb * 64, mn.hk, (int)mn.t0[ci], 0);
+            }
+        }
       }
     }
     __syncwarp();
