@@ -254,14 +254,46 @@ __global__ void polar_decode_merge_kernel(const float* __restrict__ scratch,
   const float* sacc = scratch + (int64_t)B * H * n_splits * 4 + (int64_t)bh * n_splits * dk;
   __shared__ float s_red[32];
   __shared__ float s_bc;
-
-  float M = kNegBig;
-  for (int s = 0; s < n_splits; ++s) M = fmaxf(M, stats[s * 4]);
-  float L = 0.f, Q2 = 0.f;
-  for (int s = 0; s < n_splits; ++s) {
-    const float w = __expf(stats[s * 4] - M);
-    L = fmaf(stats[s * 4 + 1], w, L);
-    Q2 = fmaf(stats[s * 4 + 2], w * w, Q2);
+  // The weights e^(m_i - M) of the partials are worked out once, by the first warp, from one round of independent
+  // 16-byte loads, and kept in shared memory; every thread then sums its channels over the partials with loads
+  // that do not depend on one another.  (More than kMergeStaged partials: the plain loops.)
+  constexpr int kMergeStaged = 128;
+  __shared__ float s_w[kMergeStaged];
+  __shared__ float s_mlq[3];
+  const bool staged = n_splits <= kMergeStaged;
+  float M = kNegBig, L = 0.f, Q2 = 0.f;
+  if (staged) {
+    if (tid < 32) {
+      float4 st[kMergeStaged / 32];
+      float m = kNegBig;
+#pragma unroll
+      for (int i = 0; i < kMergeStaged / 32; ++i) {
+        const int sp = tid + 32 * i;
+        st[i] = sp < n_splits ? *reinterpret_cast<const float4*>(stats + sp * 4) : make_float4(kNegBig, 0.f, 0.f, 0.f);
+        m = fmaxf(m, st[i].x);
+      }
+      m = warp_max(m);
+      float l = 0.f, q2 = 0.f;
+#pragma unroll
+      for (int i = 0; i < kMergeStaged / 32; ++i) {
+        const int sp = tid + 32 * i;
+        const float w = __expf(st[i].x - m);
+        if (sp < n_splits) s_w[sp] = w;
+        l = fmaf(st[i].y, w, l);
+        q2 = fmaf(st[i].z, w * w, q2);
+      }
+      l = warp_sum(l); q2 = warp_sum(q2);
+      if (tid == 0) { s_mlq[0] = m; s_mlq[1] = l; s_mlq[2] = q2; }
+    }
+    __syncthreads();
+    M = s_mlq[0]; L = s_mlq[1]; Q2 = s_mlq[2];
+  } else {
+    for (int sp = 0; sp < n_splits; ++sp) M = fmaxf(M, stats[sp * 4]);
+    for (int sp = 0; sp < n_splits; ++sp) {
+      const float w = __expf(stats[sp * 4] - M);
+      L = fmaf(stats[sp * 4 + 1], w, L);
+      Q2 = fmaf(stats[sp * 4 + 2], w * w, Q2);
+    }
   }
   int n = context_lens[b];
   n = max(0, min(n, max_ctx));
@@ -279,7 +311,19 @@ __global__ void polar_decode_merge_kernel(const float* __restrict__ scratch,
   int cnt = 0;
   for (int d = tid; d < dk; d += blockDim.x, ++cnt) {
     float s = 0.f;
-    for (int sp = 0; sp < n_splits; ++sp) s = fmaf(sacc[sp * dk + d], __expf(stats[sp * 4] - M), s);
+    if (staged) {
+      int sp = 0;
+      for (; sp + 8 <= n_splits; sp += 8) {               // eight independent loads in flight
+        float x[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) x[u] = sacc[(sp + u) * dk + d];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) s = fmaf(x[u], s_w[sp + u], s);
+      }
+      for (; sp < n_splits; ++sp) s = fmaf(sacc[sp * dk + d], s_w[sp], s);
+    } else {
+      for (int sp = 0; sp < n_splits; ++sp) s = fmaf(sacc[sp * dk + d], __expf(stats[sp * 4] - M), s);
+    }
     s = s * al + p_n * v_null[h * dk + d];
     sv[cnt] = s; sq = fmaf(s, s, sq);
   }
@@ -319,7 +363,7 @@ int launch_decode(const atma_polar_decode_args& a, cudaStream_t st) {
   if (polar_decode_mma_supported(a)) {
     int rc = polar_decode_split_mma(a, st);
     if (rc != ATMA_OK || a.skip_merge) return rc;
-    polar_decode_merge_kernel<T><<<a.B * a.H, 64, 0, st>>>(
+    polar_decode_merge_kernel<T><<<a.B * a.H, 128, 0, st>>>(
         a.scratch, a.context_lens, a.v_null, a.spg, a.null_base, a.sps, a.beta, (T*)a.c, (T*)a.mag,
         a.B, a.H, a.dk, a.n_splits, a.window, a.max_blocks * a.block_size, a.eps, (const T*)a.gate, a.gate_sb, a.gate_sh,
         a.c_sb, a.mag_sb);
@@ -343,7 +387,7 @@ int launch_decode(const atma_polar_decode_args& a, cudaStream_t st) {
 #undef ATMA_LAUNCH
   int rc = launch_status("polar_decode (split)");
   if (rc != ATMA_OK || a.skip_merge) return rc;
-  polar_decode_merge_kernel<T><<<a.B * a.H, 64, 0, st>>>(
+  polar_decode_merge_kernel<T><<<a.B * a.H, 128, 0, st>>>(
       a.scratch, a.context_lens, a.v_null, a.spg, a.null_base, a.sps, a.beta, (T*)a.c, (T*)a.mag,
       a.B, a.H, a.dk, a.n_splits, a.window, a.max_blocks * a.block_size, a.eps, (const T*)a.gate, a.gate_sb, a.gate_sh,
       a.c_sb, a.mag_sb);
@@ -386,7 +430,7 @@ extern "C" int atma_polar_decode_merge(const atma_polar_decode_args* args, void*
   ATMA_REQUIRE(a.dk >= 1 && a.dk <= 256, "polar_decode_merge: head_dim %d", a.dk);
   if (a.B <= 0) return ATMA_OK;
   ATMA_DISPATCH_DTYPE(a.dtype, T, {
-    polar_decode_merge_kernel<T><<<a.B * a.H, 64, 0, (cudaStream_t)stream>>>(
+    polar_decode_merge_kernel<T><<<a.B * a.H, 128, 0, (cudaStream_t)stream>>>(
         a.scratch, a.context_lens, a.v_null, a.spg, a.null_base, a.sps, a.beta, (T*)a.c, (T*)a.mag, a.B, a.H, a.dk, a.n_splits,
         a.window, 0x7fffffff, a.eps, (const T*)a.gate, a.gate_sb, a.gate_sh, a.c_sb, a.mag_sb);
   });
