@@ -33,9 +33,43 @@ struct PrepDecodeArgs {
   float eps;
 };
 
-template <typename T, int CPL>
+// Loads of CPL consecutive 16-bit values as one access when CPL * 2 bytes is 8 or 16 (the lane's channels,
+// their K taps and their K-1 state values are each contiguous), else element by element.
+template <typename T, int N>
+__device__ __forceinline__ void load_run(const T* p, T (&o)[N]) {
+  if constexpr (N * sizeof(T) == 16) {
+    *reinterpret_cast<uint4*>(o) = *reinterpret_cast<const uint4*>(p);
+  } else if constexpr (N * sizeof(T) == 8) {
+    *reinterpret_cast<uint2*>(o) = *reinterpret_cast<const uint2*>(p);
+  } else if constexpr (N * sizeof(T) % 8 == 0) {
+#pragma unroll
+    for (int i = 0; i < (int)(N * sizeof(T) / 8); ++i) reinterpret_cast<uint2*>(o)[i] = reinterpret_cast<const uint2*>(p)[i];
+  } else {
+#pragma unroll
+    for (int i = 0; i < N; ++i) o[i] = p[i];
+  }
+}
+template <typename T, int N>
+__device__ __forceinline__ void store_run(T* p, const T (&v)[N]) {
+  if constexpr (N * sizeof(T) == 16) {
+    *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(v);
+  } else if constexpr (N * sizeof(T) == 8) {
+    *reinterpret_cast<uint2*>(p) = *reinterpret_cast<const uint2*>(v);
+  } else if constexpr (N * sizeof(T) % 8 == 0) {
+#pragma unroll
+    for (int i = 0; i < (int)(N * sizeof(T) / 8); ++i) reinterpret_cast<uint2*>(p)[i] = reinterpret_cast<const uint2*>(v)[i];
+  } else {
+#pragma unroll
+    for (int i = 0; i < N; ++i) p[i] = v[i];
+  }
+}
+
+// K is a template parameter so that the lane's K taps and K-1 state values per channel form compile-time runs:
+// everything the lane needs (its channels of the token row, their taps, their state) is requested up front in a
+// handful of wide loads, then normalised, convolved and written.  `wide`: pointers and strides allow the wide form.
+template <typename T, int CPL, int K>
 __global__ void __launch_bounds__(128)
-qkv_prep_decode_kernel(const PrepDecodeArgs a) {
+qkv_prep_decode_kernel(const PrepDecodeArgs a, const int wide) {
   const int lane = threadIdx.x & 31;
   const int unit = blockIdx.x * 4 + (threadIdx.x >> 5);
   const int units = a.H + 2 * a.Hkv;
@@ -48,9 +82,27 @@ qkv_prep_decode_kernel(const PrepDecodeArgs a) {
                             : (which == 1 ? static_cast<const T*>(a.k) + b * a.k_row + head * a.dk
                                           : static_cast<const T*>(a.v) + b * a.v_row + head * a.dk);
   const int c0 = lane * CPL;                                      // channel inside the head
+  const int64_t slot = a.slots[b];
+  const T* wp = static_cast<const T*>(a.w[which]) + (int64_t)(head * a.dk + c0) * K;
+  T* st = slot >= 0 ? static_cast<T*>(a.state[which]) + slot * a.state_ss[which] + (int64_t)(head * a.dk + c0) * (K - 1) : nullptr;
+  T xr[CPL], wr[CPL * K], sr[CPL * (K - 1)];
+  if (wide) {
+    load_run<T, CPL>(src + c0, xr);
+    load_run<T, CPL * K>(wp, wr);
+    if (st != nullptr) load_run<T, CPL * (K - 1)>(st, sr);
+  } else {
+#pragma unroll
+    for (int j = 0; j < CPL; ++j) xr[j] = src[c0 + j];
+#pragma unroll
+    for (int j = 0; j < CPL * K; ++j) wr[j] = wp[j];
+    if (st != nullptr) {
+#pragma unroll
+      for (int j = 0; j < CPL * (K - 1); ++j) sr[j] = st[j];
+    }
+  }
   float x[CPL];
 #pragma unroll
-  for (int j = 0; j < CPL; ++j) x[j] = to_f32(src[c0 + j]);
+  for (int j = 0; j < CPL; ++j) x[j] = to_f32(xr[j]);
   if (which != 2) {                                               // per-head RMSNorm of q and k (affine-free)
     float ss = 0.f;
 #pragma unroll
@@ -60,33 +112,40 @@ qkv_prep_decode_kernel(const PrepDecodeArgs a) {
 #pragma unroll
     for (int j = 0; j < CPL; ++j) x[j] = round_through<T>(x[j] * rs);
   }
-  const int64_t slot = a.slots[b];
-  const int K = a.K;
-  const T* w = static_cast<const T*>(a.w[which]) + (int64_t)(head * a.dk + c0) * K;
-  T* st = slot >= 0 ? static_cast<T*>(a.state[which]) + slot * a.state_ss[which] + (int64_t)(head * a.dk + c0) * (K - 1) : nullptr;
-  float y[CPL];
+  T yo[CPL], sn[CPL * (K - 1)];
 #pragma unroll
   for (int j = 0; j < CPL; ++j) {
-    float acc = x[j] * to_f32(w[j * K + K - 1]);
+    float acc = x[j] * to_f32(wr[j * K + K - 1]);
     if (st != nullptr) {
-      T old[kMaxConvK - 1];
-      for (int t = 0; t < K - 1; ++t) old[t] = st[j * (K - 1) + t];
-      for (int t = 0; t < K - 1; ++t) acc = fmaf(to_f32(old[t]), to_f32(w[j * K + t]), acc);
-      for (int t = 0; t + 1 < K - 1; ++t) st[j * (K - 1) + t] = old[t + 1];
-      st[j * (K - 1) + K - 2] = from_f32<T>(x[j]);
+#pragma unroll
+      for (int t = 0; t < K - 1; ++t) acc = fmaf(to_f32(sr[j * (K - 1) + t]), to_f32(wr[j * K + t]), acc);
+#pragma unroll
+      for (int t = 0; t + 1 < K - 1; ++t) sn[j * (K - 1) + t] = sr[j * (K - 1) + t + 1];
+      sn[j * (K - 1) + K - 2] = from_f32<T>(x[j]);
     }
-    y[j] = round_through<T>(x[j] + round_through<T>(acc));      // x + conv(x)
+    yo[j] = from_f32<T>(x[j] + round_through<T>(acc));           // x + conv(x)
   }
   T* dst = (which == 0 ? static_cast<T*>(a.q_out) : (which == 1 ? static_cast<T*>(a.k_out) : static_cast<T*>(a.v_out))) +
            ((int64_t)b * heads + head) * a.dk + c0;
-#pragma unroll
-  for (int j = 0; j < CPL; ++j) dst[j] = from_f32<T>(y[j]);
+  T* cr = nullptr;
   if (which != 0 && a.k_cache != nullptr) {
     const int cs = a.slot_mapping[b];
-    if (cs >= 0) {
-      T* cr = (which == 1 ? static_cast<T*>(a.k_cache) : static_cast<T*>(a.v_cache)) + ((int64_t)cs * a.Hkv + head) * a.dk + c0;
+    if (cs >= 0) cr = (which == 1 ? static_cast<T*>(a.k_cache) : static_cast<T*>(a.v_cache)) + ((int64_t)cs * a.Hkv + head) * a.dk + c0;
+  }
+  if (wide) {
+    if (st != nullptr) store_run<T, CPL * (K - 1)>(st, sn);
+    store_run<T, CPL>(dst, yo);
+    if (cr != nullptr) store_run<T, CPL>(cr, yo);
+  } else {
+    if (st != nullptr) {
 #pragma unroll
-      for (int j = 0; j < CPL; ++j) cr[j] = from_f32<T>(y[j]);
+      for (int j = 0; j < CPL * (K - 1); ++j) st[j] = sn[j];
+    }
+#pragma unroll
+    for (int j = 0; j < CPL; ++j) dst[j] = yo[j];
+    if (cr != nullptr) {
+#pragma unroll
+      for (int j = 0; j < CPL; ++j) cr[j] = yo[j];
     }
   }
 }
@@ -123,6 +182,49 @@ add_rms_norm_kernel(const T* __restrict__ x, const T* __restrict__ y, const T* _
   }
 }
 
+// The same for rows whose length is a multiple of eight 16-bit values (16-byte aligned): one CTA per row, one
+// 16-byte piece per thread, so that a row is one round of loads, a block reduction and one round of stores -
+// the latency of a decode step's 2 x layers launches of this kernel, not its bandwidth, is what counts.
+template <typename T>
+__global__ void __launch_bounds__(512)
+add_rms_norm_row_kernel(const T* __restrict__ x, const T* __restrict__ y, const T* __restrict__ w, T* __restrict__ x_out,
+                        T* __restrict__ h_out, int D, float eps) {
+  __shared__ float s_part[16];
+  const int row = blockIdx.x, tid = threadIdx.x;
+  const int c = tid * 8;
+  const bool on = c < D;
+  const int64_t base = (int64_t)row * D + c;
+  union V8 { uint4 u; T e[8]; };
+  V8 xv, yv, wv;
+  xv.u = on ? *reinterpret_cast<const uint4*>(x + base) : make_uint4(0u, 0u, 0u, 0u);
+  if (y != nullptr) yv.u = on ? *reinterpret_cast<const uint4*>(y + base) : make_uint4(0u, 0u, 0u, 0u);
+  if (w != nullptr) wv.u = on ? *reinterpret_cast<const uint4*>(w + c) : make_uint4(0u, 0u, 0u, 0u);
+  float v[8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    float t = to_f32(xv.e[i]);
+    if (y != nullptr) t = round_through<T>(t + to_f32(yv.e[i]));
+    v[i] = t;
+    ss = fmaf(t, t, ss);
+  }
+  ss = warp_sum(ss);
+  if ((tid & 31) == 0) s_part[tid >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+  for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += s_part[i];
+  const float rs = rsqrtf(tot / (float)D + eps);
+  if (!on) return;
+  V8 xo, ho;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    xo.e[i] = from_f32<T>(v[i]);
+    ho.e[i] = from_f32<T>(v[i] * rs * (w != nullptr ? to_f32(wv.e[i]) : 1.f));
+  }
+  if (x_out != nullptr) *reinterpret_cast<uint4*>(x_out + base) = xo.u;
+  *reinterpret_cast<uint4*>(h_out + base) = ho.u;
+}
+
 }  // namespace
 }  // namespace atma
 
@@ -153,14 +255,28 @@ extern "C" int atma_qkv_prep_decode(const void* q_gate, int64_t qg_row, int64_t 
   const int units = B * (H + 2 * Hkv);
   const dim3 grid((units + 3) / 4), block(128);
   cudaStream_t st = (cudaStream_t)stream;
+  // the wide form needs aligned runs: CPL * 2 bytes per lane of every row, CPL * K * 2 of taps, CPL * (K-1) * 2 of state
+  auto al = [](const void* p, int n) { return (reinterpret_cast<uintptr_t>(p) & (uintptr_t)(n - 1)) == 0; };
+  const bool two_byte = dtype != ATMA_F32;
+  const int wide = (two_byte && (dk == 128 || dk == 256) && qg_row % 8 == 0 && qg_head % 8 == 0 && k_row % 8 == 0 && v_row % 8 == 0 &&
+                    ss_q % 8 == 0 && ss_k % 8 == 0 && ss_v % 8 == 0 && al(q_gate, 16) && al(k, 16) && al(v, 16) && al(w_q, 16) &&
+                    al(w_k, 16) && al(w_v, 16) && al(state_q, 16) && al(state_k, 16) && al(state_v, 16) && al(q_out, 16) &&
+                    al(k_out, 16) && al(v_out, 16) && al(k_cache, 16) && al(v_cache, 16)) ? 1 : 0;
+#define ATMA_PD(CPLV)                                                                        \
+  switch (K) {                                                                               \
+    case 2: qkv_prep_decode_kernel<T, CPLV, 2><<<grid, block, 0, st>>>(a, wide); break;      \
+    case 3: qkv_prep_decode_kernel<T, CPLV, 3><<<grid, block, 0, st>>>(a, wide); break;      \
+    default: qkv_prep_decode_kernel<T, CPLV, 4><<<grid, block, 0, st>>>(a, wide); break;     \
+  }
   ATMA_DISPATCH_DTYPE(dtype, T, {
     switch (dk) {
-      case 32: qkv_prep_decode_kernel<T, 1><<<grid, block, 0, st>>>(a); break;
-      case 64: qkv_prep_decode_kernel<T, 2><<<grid, block, 0, st>>>(a); break;
-      case 128: qkv_prep_decode_kernel<T, 4><<<grid, block, 0, st>>>(a); break;
-      default: qkv_prep_decode_kernel<T, 8><<<grid, block, 0, st>>>(a); break;
+      case 32: ATMA_PD(1) break;
+      case 64: ATMA_PD(2) break;
+      case 128: ATMA_PD(4) break;
+      default: ATMA_PD(8) break;
     }
   });
+#undef ATMA_PD
   return launch_status("qkv_prep_decode");
 }
 
@@ -170,8 +286,19 @@ extern "C" int atma_add_rms_norm(const void* x, const void* y, const void* weigh
   ATMA_REQUIRE(D >= 1 && D <= 4096, "add_rms_norm: D=%d outside 1..4096", D);
   ATMA_REQUIRE(x != nullptr && h_out != nullptr, "add_rms_norm: x and h_out are required");
   if (rows <= 0) return ATMA_OK;
-  const dim3 grid((rows + 3) / 4), block(128);
   cudaStream_t st = (cudaStream_t)stream;
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (dtype != ATMA_F32 && D % 8 == 0 && al16(x) && al16(y) && al16(weight) && al16(x_out) && al16(h_out)) {
+    const int threads = ((D / 8 + 31) / 32) * 32;                // <= 512 for D <= 4096
+    if (dtype == ATMA_BF16)
+      add_rms_norm_row_kernel<__nv_bfloat16><<<rows, threads, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)y,
+          (const __nv_bfloat16*)weight, (__nv_bfloat16*)x_out, (__nv_bfloat16*)h_out, D, eps);
+    else
+      add_rms_norm_row_kernel<__half><<<rows, threads, 0, st>>>((const __half*)x, (const __half*)y, (const __half*)weight,
+                                                                (__half*)x_out, (__half*)h_out, D, eps);
+    return launch_status("add_rms_norm");
+  }
+  const dim3 grid((rows + 3) / 4), block(128);
   const int vpl = (D + 31) / 32;
   ATMA_DISPATCH_DTYPE(dtype, T, {
     const T* xp = (const T*)x; const T* yp = (const T*)y; const T* wp = (const T*)weight;
