@@ -38,6 +38,54 @@ __global__ void lfm2_conv_step_kernel(const T* __restrict__ proj, int64_t proj_s
   out[b * out_sb + d] = from_f32<T>(cv * round_through<T>(acc));
 }
 
+// Wide form of the decode step (D a multiple of 8, 16-bit types, 16-byte aligned rows): a thread owns eight channels
+// and asks for everything it needs up front - the B, C and x' pieces of the projection row, the 8 x K taps and the
+// 8 x (K-1) state values, each a contiguous run - so a step is one round of loads, the arithmetic and one round of
+// stores.  Same rounding points as the channel-per-thread form.
+template <typename T, int K>
+__global__ void __launch_bounds__(128)
+lfm2_conv_step_wide_kernel(const T* __restrict__ proj, int64_t proj_sb, const T* __restrict__ w,
+                           const int64_t* __restrict__ slots, T* __restrict__ state, int64_t state_ss,
+                           T* __restrict__ out, int64_t out_sb, int D) {
+  const int b = blockIdx.x;
+  const int d0 = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (d0 >= D) return;
+  union V8 { uint4 u; T e[8]; };
+  const T* p = proj + b * proj_sb;
+  V8 bv, cv, xv;
+  bv.u = *reinterpret_cast<const uint4*>(p + d0);
+  cv.u = *reinterpret_cast<const uint4*>(p + D + d0);
+  xv.u = *reinterpret_cast<const uint4*>(p + 2 * D + d0);
+  T wr[8 * K], sr[8 * (K - 1)], sn[8 * (K - 1)];
+#pragma unroll
+  for (int i = 0; i < K; ++i) reinterpret_cast<uint4*>(wr)[i] = *reinterpret_cast<const uint4*>(w + (int64_t)d0 * K + 8 * i);
+  const int64_t slot = slots[b];
+  T* st = slot >= 0 ? state + slot * state_ss + (int64_t)d0 * (K - 1) : nullptr;
+  if (st != nullptr) {
+#pragma unroll
+    for (int i = 0; i < K - 1; ++i) reinterpret_cast<uint4*>(sr)[i] = *reinterpret_cast<const uint4*>(st + 8 * i);
+  }
+  V8 o;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const T xg = from_f32<T>(to_f32(bv.e[j]) * to_f32(xv.e[j]));        // the gated conv input, as eager materialises it
+    float acc = to_f32(xg) * to_f32(wr[j * K + K - 1]);
+    if (st != nullptr) {
+#pragma unroll
+      for (int t = 0; t < K - 1; ++t) acc = fmaf(to_f32(sr[j * (K - 1) + t]), to_f32(wr[j * K + t]), acc);
+#pragma unroll
+      for (int t = 0; t + 1 < K - 1; ++t) sn[j * (K - 1) + t] = sr[j * (K - 1) + t + 1];
+      sn[j * (K - 1) + K - 2] = xg;
+    }
+    o.e[j] = from_f32<T>(to_f32(cv.e[j]) * round_through<T>(acc));
+  }
+  if (st != nullptr) {
+#pragma unroll
+    for (int i = 0; i < K - 1; ++i) *reinterpret_cast<uint4*>(st + 8 * i) = reinterpret_cast<const uint4*>(sn)[i];
+  }
+  *reinterpret_cast<uint4*>(out + b * out_sb + d0) = o.u;
+}
+
 // ---- packed prefill: thread = one channel x a run of consecutive tokens ---------------------------------
 constexpr int kLfmTokPerThread = 16;
 
@@ -244,6 +292,19 @@ lfm2_conv_packed_vec_kernel(const T* __restrict__ proj, int64_t proj_st, const T
 template <typename T>
 int launch_lfm2_step(const void* proj, int64_t proj_sb, const void* w, const int64_t* slots, void* state,
                      int64_t state_ss, void* out, int64_t out_sb, int B, int D, int K, cudaStream_t st) {
+  if constexpr (sizeof(T) == 2) {
+    auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    if (D % 8 == 0 && proj_sb % 8 == 0 && out_sb % 8 == 0 && state_ss % 8 == 0 && al(proj) && al(w) && al(state) && al(out)) {
+      dim3 wgrid(B, (D / 8 + 127) / 128), wblock(128);
+      switch (K) {
+        case 2: lfm2_conv_step_wide_kernel<T, 2><<<wgrid, wblock, 0, st>>>((const T*)proj, proj_sb, (const T*)w, slots, (T*)state, state_ss, (T*)out, out_sb, D); break;
+        case 3: lfm2_conv_step_wide_kernel<T, 3><<<wgrid, wblock, 0, st>>>((const T*)proj, proj_sb, (const T*)w, slots, (T*)state, state_ss, (T*)out, out_sb, D); break;
+        case 4: lfm2_conv_step_wide_kernel<T, 4><<<wgrid, wblock, 0, st>>>((const T*)proj, proj_sb, (const T*)w, slots, (T*)state, state_ss, (T*)out, out_sb, D); break;
+        default: return fail(ATMA_ERR_UNSUPPORTED, "lfm2_conv_decode_step: kernel size %d not in 2..4", K);
+      }
+      return launch_status("lfm2_conv_decode_step");
+    }
+  }
   dim3 grid(B, (D + 255) / 256), block(256);
   switch (K) {
     case 2: lfm2_conv_step_kernel<T, 2><<<grid, block, 0, st>>>((const T*)proj, proj_sb, (const T*)w, slots, (T*)state, state_ss, (T*)out, out_sb, D); break;
