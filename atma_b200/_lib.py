@@ -53,6 +53,8 @@ class PolarDecodeArgs(Structure):
         ("window", c_int), ("eps", c_float),
         ("gate", c_void_p), ("gate_sb", c_int64), ("gate_sh", c_int64), ("c_sb", c_int64), ("mag_sb", c_int64),
         ("temp_lens", c_void_p), ("skip_merge", c_int),
+        ("append_k", c_void_p), ("append_v", c_void_p), ("append_k_stride", c_int64), ("append_v_stride", c_int64),
+        ("append_slots", c_void_p),
     ]
 
 
@@ -65,6 +67,7 @@ _SIGNATURES = {
     "atma_polar_decode_scratch_floats": (c_int64, [c_int, c_int, c_int, c_int]),
     "atma_polar_decode": (c_int, [POINTER(PolarDecodeArgs), c_void_p]),
     "atma_polar_decode_merge": (c_int, [POINTER(PolarDecodeArgs), c_void_p]),
+    "atma_polar_decode_appends": (c_int, [POINTER(PolarDecodeArgs)]),
     "atma_polar_decode_static_max_floats": (c_int64, []),
     "atma_polar_decode_static": (c_int, [POINTER(PolarDecodeArgs), c_void_p]),
     "atma_gated_delta_decode_step": (c_int, [c_void_p] * 3 + [c_int64] * 6 + [c_int, c_void_p, c_void_p,

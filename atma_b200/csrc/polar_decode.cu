@@ -354,6 +354,7 @@ __global__ void polar_decode_merge_kernel(const float* __restrict__ scratch,
 
 // tensor-core split kernel for 16-bit caches (polar_decode_mma.cu)
 bool polar_decode_mma_supported(const atma_polar_decode_args& a);
+bool polar_decode_mma_appends(const atma_polar_decode_args& a);
 int polar_decode_split_mma(const atma_polar_decode_args& a, cudaStream_t st);
 
 template <typename T>
@@ -400,6 +401,10 @@ using namespace atma;
 
 extern "C" int64_t atma_polar_decode_scratch_floats(int B, int H, int dk, int n_splits) {
   return (int64_t)B * H * n_splits * (4 + dk);
+}
+
+extern "C" int atma_polar_decode_appends(const atma_polar_decode_args* args) {
+  return (args != nullptr && atma::polar_decode_mma_appends(*args)) ? 1 : 0;
 }
 
 extern "C" int atma_polar_decode(const atma_polar_decode_args* args, void* stream) {

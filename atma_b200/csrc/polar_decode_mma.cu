@@ -40,7 +40,9 @@ polar_decode_split_mma_kernel(const uint16_t* __restrict__ q, const uint16_t* __
                               const uint16_t* __restrict__ v_cache, const int32_t* __restrict__ block_tables,
                               int64_t bt_stride, const int32_t* __restrict__ context_lens, const int32_t* __restrict__ temp_lens,
                               const float* __restrict__ spg, float* __restrict__ scratch, int B, int H, int Hkv,
-                              int block_size, int max_blocks, int num_blocks, int n_splits, int window) {
+                              int block_size, int max_blocks, int num_blocks, int n_splits, int window,
+                              const uint16_t* __restrict__ append_k, int64_t append_k_st, const uint16_t* __restrict__ append_v,
+                              int64_t append_v_st, const int32_t* __restrict__ append_slots) {
   constexpr int KS = DK / 16;                 // k-steps of K Q^T
   constexpr int MT = DK / 16;                 // m-tiles of V^T P^T
   constexpr int CH = DK / 8;                  // 16-byte chunks per row
@@ -64,6 +66,22 @@ polar_decode_split_mma_kernel(const uint16_t* __restrict__ q, const uint16_t* __
   const int lo = lo_w + split * chunk;
   const int hi = min(lo + chunk, n);
 
+  // The token being decoded: the CTA whose key range ends with it stores its K and V rows before anything of
+  // the cache is read (16 bytes per thread; the fence and the barrier order the stores before this CTA's loads;
+  // no other CTA of the launch reads that row, because the key ranges are disjoint).
+  if (append_slots != nullptr) {
+    if (hi == n && lo < hi && g0 == 0 && tid < 2 * CH) {
+      const int cs = append_slots[b];
+      if (cs >= 0) {
+        const int isv = tid / CH, ch = tid % CH;
+        const uint16_t* src = (isv ? append_v + b * append_v_st : append_k + b * append_k_st) + kvh * DK + ch * 8;
+        uint16_t* dst = const_cast<uint16_t*>(isv ? v_cache : k_cache) + ((int64_t)cs * Hkv + kvh) * DK + ch * 8;
+        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+        __threadfence();
+      }
+    }
+    __syncthreads();
+  }
   float* stats = scratch;
   float* sacc = scratch + (int64_t)B * H * n_splits * 4;
   if (lo >= hi) {                             // empty range: neutral partial
@@ -259,18 +277,29 @@ bool polar_decode_mma_supported(const atma_polar_decode_args& a) {
   return (a.dtype == ATMA_BF16 || a.dtype == ATMA_F16) && (a.dk == 128 || a.dk == 64) && G <= 16;
 }
 
+// Whether the key-range kernel stores the token's own K/V rows (one CTA group per KV head, so that no other CTA
+// reads the row that is being written).
+bool polar_decode_mma_appends(const atma_polar_decode_args& a) {
+  return polar_decode_mma_supported(a) && a.append_k != nullptr && a.append_v != nullptr && a.append_slots != nullptr &&
+         a.H / a.Hkv <= 8 && (reinterpret_cast<uintptr_t>(a.append_k) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.append_v) & 15) == 0 &&
+         a.append_k_stride % 8 == 0 && a.append_v_stride % 8 == 0;
+}
+
 int polar_decode_split_mma(const atma_polar_decode_args& a, cudaStream_t st) {
   const int G = a.H / a.Hkv;
   dim3 grid(a.n_splits, a.Hkv * ((G + 7) / 8), a.B);
   constexpr int kStages = 3;                  // 3 x 32 KB per CTA, two CTAs per SM: ~200 KB of loads in flight per SM
   const int smem = kStages * 2 * kTileKeys * a.dk * 2;
+  const void* ak = polar_decode_mma_appends(a) ? a.append_k : nullptr;
 #define ATMA_LAUNCH(BF, DKK)                                                                                    \
   do {                                                                                                          \
     auto kern = polar_decode_split_mma_kernel<BF, DKK, kStages>;                                                \
     ATMA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));                \
     kern<<<grid, 128, smem, st>>>((const uint16_t*)a.q, (const uint16_t*)a.k_cache, (const uint16_t*)a.v_cache, \
                                   a.block_tables, a.bt_stride, a.context_lens, a.temp_lens, a.spg, a.scratch, a.B, a.H,      \
-                                  a.Hkv, a.block_size, a.max_blocks, a.num_blocks, a.n_splits, a.window);       \
+                                  a.Hkv, a.block_size, a.max_blocks, a.num_blocks, a.n_splits, a.window,        \
+                                  (const uint16_t*)ak, a.append_k_stride, (const uint16_t*)a.append_v, a.append_v_stride, \
+                                  ak ? a.append_slots : nullptr);                                               \
   } while (0)
   if (a.dtype == ATMA_BF16) { if (a.dk == 128) ATMA_LAUNCH(true, 128); else ATMA_LAUNCH(true, 64); }
   else { if (a.dk == 128) ATMA_LAUNCH(false, 128); else ATMA_LAUNCH(false, 64); }

@@ -242,7 +242,7 @@ def _decode_scratch(device, nfloats):
 def polar_attention_decode(q, k_cache, v_cache, block_tables, context_lens, *,
                            v_null, null_base, null_slope_raw, len_gain_raw, mag_beta_raw,
                            eps=1e-6, block_n=None, num_warps=None, num_stages=None, window=None,
-                           num_splits=None, gate=None, out=None):
+                           num_splits=None, gate=None, out=None, append=None):
     """Paged Polar decode.  q (B,H,dk); caches (num_blocks, block_size, Hkv, dk) contiguous;
     block_tables (B,max_blocks) int32; context_lens (B,) int32 including the current token.
     Returns c (B,H,dk), mag (B,H) in q's dtype.  ``block_n``, ``num_warps``, ``num_stages``
@@ -252,7 +252,10 @@ def polar_attention_decode(q, k_cache, v_cache, block_tables, context_lens, *,
     strides - c comes back as c * sigmoid(gate), the operand of the output projection
     (inference/models/atma.py:246-252), from the merge kernel itself; ``out`` = (c_view, mag_view),
     preallocated views with a dense last dimension (e.g. two column ranges of one activation
-    buffer) that receive the results instead of fresh tensors."""
+    buffer) that receive the results instead of fresh tensors; ``append`` = (k_new (B,Hkv,dk), v_new, slot_mapping
+    (B,) int32): the K/V rows of the token being decoded and their cache rows - the call stores them before it
+    reads the cache, i.e. it replaces the ``store_kvcache`` that precedes the decode call in the reference's
+    attention layer (inference/layers/attention.py:85-97); one launch less per step."""
     _lib.require_cuda(q, "polar_attention_decode")
     lib = _lib.load()
     B, H, dk = q.shape
@@ -292,6 +295,22 @@ def polar_attention_decode(q, k_cache, v_cache, block_tables, context_lens, *,
     a.B, a.H, a.Hkv, a.dk, a.block_size = B, H, Hkv, dk, block_size
     a.max_blocks, a.num_blocks, a.n_splits = max_blocks, num_blocks, n_splits
     a.dtype, a.window, a.eps = _lib.dtype_code(q), (0 if window is None else int(window)), float(eps)
+    if append is not None:
+        k_new, v_new, slot_mapping = append
+        if k_new.shape != (B, Hkv, dk) or v_new.shape != (B, Hkv, dk) or k_new.dtype != q.dtype or v_new.dtype != q.dtype:
+            raise ValueError("append = (k_new (B,Hkv,dk), v_new (B,Hkv,dk), slot_mapping (B,)) in q's dtype")
+        if k_new.stride(2) != 1 or k_new.stride(1) != dk:
+            k_new = k_new.contiguous()
+        if v_new.stride(2) != 1 or v_new.stride(1) != dk:
+            v_new = v_new.contiguous()
+        slot_mapping = slot_mapping.to(torch.int32).contiguous()
+        a.append_k, a.append_v = _lib.ptr(k_new), _lib.ptr(v_new)
+        a.append_k_stride, a.append_v_stride = k_new.stride(0), v_new.stride(0)
+        a.append_slots = _lib.ptr(slot_mapping)
+        if not lib.atma_polar_decode_appends(byref(a)):          # this shape is not served in-kernel: the separate scatter
+            from .kvcache import store_kvcache
+            store_kvcache(k_new, v_new, k_cache, v_cache, slot_mapping)
+            a.append_k = a.append_v = a.append_slots = None
     _lib.check(lib.atma_polar_decode(byref(a), _lib.stream_ptr()))
     return c, mag
 

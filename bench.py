@@ -164,8 +164,8 @@ def prefill_step(ab, t, n_keys, params, events=None, ready=None):
 
 
 def bench_decode(ab, device, steps, warmup, peaks):
-    """Decode of one global layer's mixing at batch 64 x 32K context: KV scatter of the new
-    token, paged Polar decode, gated-delta state step.  Context larger than L2 by 17x."""
+    """Decode of one global layer's mixing at batch 64 x 32K context: paged Polar decode that first stores the
+    new token's K/V rows, gated-delta state step beside it.  Context larger than L2 by 17x."""
     g = torch.Generator().manual_seed(3)
     nblk_seq = DEC_CTX // DEC_BLOCK
     num_blocks = DEC_B * nblk_seq
@@ -192,8 +192,8 @@ def bench_decode(ab, device, steps, warmup, peaks):
         side.wait_stream(cur)
         with torch.cuda.stream(side):
             r = ab.gated_delta_decode_step_fused(q, kn, vn, state, slots, gamma=gamma, beta=beta)   # un-expanded KV heads
-        ab.store_kvcache(kn, vn, k_cache, v_cache, slot_map)
-        c, mag = ab.polar_attention_decode(q, k_cache, v_cache, bt, cl, **params)
+        # the new token's K/V rows are stored by the decode call itself (the key-range CTA that ends with them)
+        c, mag = ab.polar_attention_decode(q, k_cache, v_cache, bt, cl, append=(kn, vn, slot_map), **params)
         cur.wait_stream(side)
         return c, mag, r
 
@@ -204,9 +204,8 @@ def bench_decode(ab, device, steps, warmup, peaks):
     pe = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(steps)]
     e0.record()
     for i in range(steps):
-        ab.store_kvcache(kn, vn, k_cache, v_cache, slot_map)
         pe[i][0].record()
-        ab.polar_attention_decode(q, k_cache, v_cache, bt, cl, **params)
+        ab.polar_attention_decode(q, k_cache, v_cache, bt, cl, append=(kn, vn, slot_map), **params)
         pe[i][1].record()
         pe[i][2].record()
         ab.gated_delta_decode_step_fused(q, kn, vn, state, slots, gamma=gamma, beta=beta)

@@ -130,11 +130,22 @@ typedef struct {
    * fields.  Windowed attention is not available in this form. */
   const int32_t* temp_lens;
   int skip_merge;
+  /* Optional: the K/V rows of the token being decoded, [B][Hkv][dk] with row strides in elements, and their
+   * cache rows append_slots[B] (int32, negative = skip).  The key-range kernel then stores them itself before
+   * it reads the cache (the CTA whose key range ends with the new token does it), which replaces the
+   * store_kvcache launch that precedes the decode call (inference/layers/attention.py:30-56,85-97).  Honoured
+   * for 16-bit caches with head_dim 64 or 128 and at most 8 query heads per KV head; callers check
+   * atma_polar_decode_appends() and otherwise call atma_store_kvcache first. */
+  const void* append_k; const void* append_v;
+  int64_t append_k_stride, append_v_stride;
+  const int32_t* append_slots;
 } atma_polar_decode_args;
 
 int64_t atma_polar_decode_scratch_floats(int B, int H, int dk, int n_splits);
 int atma_polar_decode(const atma_polar_decode_args* args, void* stream);
 int atma_polar_decode_merge(const atma_polar_decode_args* args, void* stream);
+/* 1 if atma_polar_decode would store the append_* rows itself for this dtype / head_dim / head grouping, else 0. */
+int atma_polar_decode_appends(const atma_polar_decode_args* args);
 
 /* ------------------------------------------------------------------------------------
  * Paged Polar decode for callers that cannot allocate device memory.  (No counterpart in

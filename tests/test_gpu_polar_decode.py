@@ -193,3 +193,31 @@ def test_partials_of_two_caches_merge_to_the_decode_of_the_whole_context(dtype):
         assert max_abs(c, c_ref) < 1e-4 and max_abs(m, m_ref) < 1e-4
     else:
         assert max_rel(c, c_ref) < 2e-2 and max_abs(m, m_ref) < 2e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("ctx", [[1, 70, 513, 64], [300, 2, 129, 1000]])
+def test_decode_that_stores_the_new_token_itself_equals_scatter_then_decode(dtype, ctx):
+    """``append=``: the decode call stores the new token's K/V rows before it reads the cache (16-bit: inside the
+    key-range kernel; fp32: by the separate scatter): cache contents and outputs equal store_kvcache + decode."""
+    g = torch.Generator().manual_seed(sum(ctx))
+    B, H, Hkv, dk, bs = len(ctx), 8, 2, 128, 64
+    per = (max(ctx) + bs - 1) // bs
+    nblk = B * per + 2
+    kc = torch.randn(nblk, bs, Hkv, dk, generator=g).to(dtype).cuda()
+    vc = torch.randn(nblk, bs, Hkv, dk, generator=g).to(dtype).cuda()
+    bt = torch.randperm(nblk, generator=g)[:B * per].view(B, per).int().cuda()
+    cl = torch.tensor(ctx, dtype=torch.int32).cuda()
+    q = torch.randn(B, H, dk, generator=g).to(dtype).cuda()
+    kn = torch.randn(B, Hkv, dk, generator=g).to(dtype).cuda()
+    vn = torch.randn(B, Hkv, dk, generator=g).to(dtype).cuda()
+    last = cl.long() - 1
+    sm = (bt.long()[torch.arange(B), last // bs] * bs + last % bs).int()
+    _, P = polar_params(H, dk, 4)
+    kc1, vc1 = kc.clone(), vc.clone()
+    atma_b200.store_kvcache(kn, vn, kc1, vc1, sm)
+    c1, m1 = atma_b200.polar_attention_decode(q, kc1, vc1, bt, cl, **P)
+    kc2, vc2 = kc.clone(), vc.clone()
+    c2, m2 = atma_b200.polar_attention_decode(q, kc2, vc2, bt, cl, append=(kn, vn, sm), **P)
+    assert torch.equal(kc1, kc2) and torch.equal(vc1, vc2)
+    assert torch.equal(c1, c2) and torch.equal(m1, m2)
