@@ -38,7 +38,7 @@ struct RecMap {                 // recurrence i walks the chunk records of batch
   int zero_u0[kMaxRec];         // yields a segment's state-transfer matrix)
   int c_begin[kMaxRec];         // chunk range [c_begin, c_end) of the records that recurrence i walks
   int c_end[kMaxRec];           // (c_end = 0 means "all NC chunks")
-  int o_row[kMaxRec];           // batch row of the output tensor that recurrence i writes
+  int o_row[kMaxRec];           // batch row of the output tensor that recurrence i writes (negative: no output)
   int state_row[kMaxRec];       // plane of initial_state / final_state that recurrence i reads / writes
 };
 

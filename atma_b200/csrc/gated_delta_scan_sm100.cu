@@ -110,14 +110,14 @@ scan_recur_sm100_kernel(const __grid_constant__ CUtensorMap tmap_rec, const __gr
     tok_base = p.var.cu_seqlens[b]; tok_end = p.var.cu_seqlens[b + 1];
   } else {
     c_begin = p.map.c_begin[b]; c_end = p.map.c_end[b] > 0 ? p.map.c_end[b] : p.NC;
-    const int64_t orow0 = (int64_t)p.map.o_row[b] * p.Tlen;          // the batch row of o this recurrence writes
+    const int64_t orow0 = (int64_t)max(p.map.o_row[b], 0) * p.Tlen;  // the batch row of o this recurrence writes
     tok_base = orow0 + (int64_t)c_begin * kC;
     tok_end = orow0 + min((int64_t)p.Tlen, (int64_t)c_end * kC);
   }
   const int n_chunks = max(c_end - c_begin, 0);
   const int64_t rec0 = ((int64_t)rb * p.H + h) * p.NC + c_begin;     // first record of this recurrence
   const float* gcs = p.gcs + rec0;
-  const bool want_o = p.o != nullptr;
+  const bool want_o = p.o != nullptr && (packed || p.map.o_row[b] >= 0);   // a negative row: this recurrence only carries state
 
   if (tid == 0) {
     for (int i = 0; i < kStages; ++i) {

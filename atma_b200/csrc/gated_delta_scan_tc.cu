@@ -79,13 +79,21 @@ seg_compose_kernel(const float* __restrict__ fin1, float* __restrict__ init2, fl
     const float* Q = plane(fin1, b * per_row + 2 * s) + k * kD + 16 * slab + c0;
 #pragma unroll
     for (int c = 0; c < 8; ++c) acc[c] = Q[c];
-    for (int m = 0; m < kD; m += 4) {
-      const float4 pv = *reinterpret_cast<const float4*>(P + m);
-      const float pm[4] = {pv.x, pv.y, pv.z, pv.w};
+    // the row of P in four batches of eight independent 16-byte loads (the chain of segments is serial, so the
+    // load latency of every step counts)
+#pragma unroll 1
+    for (int m0 = 0; m0 < kD; m0 += 32) {
+      float4 pv[8];
 #pragma unroll
-      for (int e = 0; e < 4; ++e)
+      for (int u = 0; u < 8; ++u) pv[u] = __ldg(reinterpret_cast<const float4*>(P + m0 + 4 * u));
 #pragma unroll
-        for (int c = 0; c < 8; ++c) acc[c] = fmaf(pm[e], Ss[m + e][c0 + c], acc[c]);
+      for (int u = 0; u < 8; ++u) {
+        const float pm[4] = {pv[u].x, pv[u].y, pv[u].z, pv[u].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+#pragma unroll
+          for (int c = 0; c < 8; ++c) acc[c] = fmaf(pm[e], Ss[m0 + 4 * u + e][c0 + c], acc[c]);
+      }
     }
   }
 }
@@ -235,20 +243,13 @@ int gated_delta_scan_mma(const void* q, const void* k, const void* v, int dtype,
     const bool bf = dtype == ATMA_BF16;
     rc = launch_status("gated_delta_scan (segment setup)");
     if (rc != ATMA_OK) return rc;
-    // pass 1 as two launches, because outputs are per launch: the segment-0 recurrences write o, the
-    // (P, Q) recurrences only their final states; state_row keeps recurrence i on plane i of init1 / fin1
-    RecMap m1a{}, m1b{};
-    int na = 0, nb = 0;
+    // pass 1 is one launch: the segment-0 recurrences write o, the (P, Q) recurrences carry state only
+    // (o_row < 0); state_row keeps recurrence i on plane i of init1 / fin1
     for (int i = 0; i < n1; ++i) {
-      const bool first = (i % per_row) == 0;
-      RecMap& dst = first ? m1a : m1b;
-      int& n = first ? na : nb;
-      dst.rec[n] = m1.rec[i]; dst.o_row[n] = m1.o_row[i]; dst.zero_u0[n] = m1.zero_u0[i];
-      dst.c_begin[n] = m1.c_begin[i]; dst.c_end[n] = m1.c_end[i]; dst.state_row[n] = i;
-      ++n;
+      m1.state_row[i] = i;
+      if ((i % per_row) != 0) m1.o_row[i] = -1;
     }
-    rc = gated_delta_recur_sm100(recs, gcs, bf, (int64_t)B * H * NC, init1, o, fin1, T, H, NC, na, m1a, VarLen{}, st);
-    if (rc == ATMA_OK) rc = gated_delta_recur_sm100(recs, gcs, bf, (int64_t)B * H * NC, init1, nullptr, fin1, T, H, NC, nb, m1b, VarLen{}, st);
+    rc = gated_delta_recur_sm100(recs, gcs, bf, (int64_t)B * H * NC, init1, o, fin1, T, H, NC, n1, m1, VarLen{}, st);
     if (rc != ATMA_OK) return rc;
     seg_compose_kernel<<<dim3(kD / 16, H, B), 256, 0, st>>>(fin1, init2, final_state, H, NS);
     rc = launch_status("gated_delta_scan (segment states)");
