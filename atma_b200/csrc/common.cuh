@@ -38,6 +38,19 @@ inline int launch_status(const char* what) {
   return ATMA_OK;
 }
 
+// SM count of the calling thread's current device (148 when the query fails); read once per device.
+inline int sm_count_of_current_device() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 148;
+    cached[dev] = n;                     // the same value from every host thread
+  }
+  return cached[dev];
+}
+
 inline size_t dtype_size(int dt) { return dt == ATMA_F32 ? 4 : 2; }
 inline bool dtype_ok(int dt) { return dt == ATMA_F32 || dt == ATMA_BF16 || dt == ATMA_F16; }
 

@@ -15,7 +15,10 @@
 // branches.  Four CTAs per SM (39 KB of shared memory, 128 registers each) overlap one tile's
 // copies with another's arithmetic; each projection element comes from DRAM once (the K-1 halo
 // rows of a tile are its neighbour's rows, i.e. cache hits) and every output goes out once.
+#include <algorithm>
+
 #include "common.cuh"
+#include "mma_sync.cuh"
 
 namespace atma {
 
@@ -103,6 +106,38 @@ template <typename T> __device__ __forceinline__ void round8(float (&v)[8]) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) { const float2 f = __half22float2(__floats2half2_rn(v[2 * i], v[2 * i + 1])); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
   }
+}
+
+// The same on channel pairs: the straight-line path keeps a row as four float2 so that its multiplies, adds and
+// fused multiply-adds issue as packed two-lane fp32 instructions (each lane rounds exactly as the scalar form).
+template <typename T> __device__ __forceinline__ void unpack8(const uint4& u, float2 (&o)[4]) {
+  float f[8];
+  unpack8<T>(u, f);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) o[i] = make_float2(f[2 * i], f[2 * i + 1]);
+}
+template <typename T> __device__ __forceinline__ void round8(float2 (&v)[4]) {
+  if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = __bfloat1622float2(__floats2bfloat162_rn(v[i].x, v[i].y));
+  } else if constexpr (std::is_same<T, __half>::value) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = __half22float2(__floats2half2_rn(v[i].x, v[i].y));
+  }
+}
+template <typename T> __device__ __forceinline__ void store8(T* p, const float2 (&v)[4]) {
+  static_assert(sizeof(T) == 2, "pairs are stored for the 16-bit types only");
+  uint4 u;
+  if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[i].x, v[i].y);
+  } else {
+    __half2* h = reinterpret_cast<__half2*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(v[i].x, v[i].y);
+  }
+  *reinterpret_cast<uint4*>(p) = u;
 }
 
 // 16-byte asynchronous copy global -> shared; src_bytes = 0 zero-fills the destination
@@ -339,27 +374,38 @@ qkv_prep_kernel(const PrepArgs a) {
 }
 
 // ---- direct form (16-bit types, head_dim 128) -------------------------------------------------------------
-// No shared-memory tile and no CTA-wide barrier: a half warp (16 lanes x 8 channels = one head row of 128
-// channels) owns a run of kDirTok consecutive tokens of one head; every lane requests the kDirTok + K - 1 rows
-// of its run as 16-byte loads before the first use (the halo rows are the neighbouring run's rows, i.e. cache
-// hits), normalises each row in registers (row sum by shuffles inside the half warp), slides an fp32 window of
-// K rows over them and writes q, k, v and the cache rows once.  Runs that touch a sequence start or end - two
-// per sequence and head - take a per-token path that re-reads and re-normalises its taps.  The two half warps of
-// a warp are independent: their shuffles name only their own sixteen lanes.
+// No tile shared between threads and no CTA-wide barrier.  A half warp (16 lanes x 8 channels = one head row of
+// 128 channels) owns a stretch of consecutive groups of kDirTok tokens of one head; a warp is two head rows that
+// are neighbours in memory, over the same tokens, so its control flow is the same in both halves and the row sums
+// use full-mask shuffles of width 16.  The rows of the next group travel to a lane-private slot of shared memory
+// while the current group is worked on (asynchronous 16-byte copies: in flight without holding registers).  Each
+// row is normalised in registers, an fp32 window of K rows slides over the stretch (the K-1 rows at the end of a
+// group are the next group's left context, so only the first group of a stretch reads halo rows), the arithmetic
+// runs on channel pairs with the packed two-lane fp32 instructions, and q, k, v and the cache rows are written
+// once.  Groups that touch a sequence start or end - two per sequence and head - take a per-token path that
+// re-reads and re-normalises its taps.
 constexpr int kDirTok = 8;                      // tokens per group (all loads of a group in flight together)
 constexpr int kDirGroups = 4;                   // consecutive groups per half warp
 
 template <typename T, int K>
 __global__ void __launch_bounds__(128, 4)
-qkv_prep_direct_kernel(const PrepArgs a, const int vec_weights) {
+qkv_prep_direct_kernel(const PrepArgs a, const int vec_weights, const int parts) {
   const int lane = threadIdx.x & 31;
   const int li = lane & 15;
   const int units = a.H + 2 * a.Hkv;
-  const int n_runs = (a.total + kDirTok * kDirGroups - 1) / (kDirTok * kDirGroups);
-  const int64_t hw = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 4;     // half-warp index
-  const bool hw_on = hw < (int64_t)units * n_runs;
-  const int u = hw_on ? (int)(hw % units) : 0;
-  const int run = hw_on ? (int)(hw / units) : 0;
+  const int n_groups = (a.total + kDirTok - 1) / kDirTok;
+  // A warp = two head rows (neighbours in memory) over the same stretch of tokens, so its control flow is the same
+  // in both halves and the row sums can use full-mask shuffles of width 16.  With an odd number of head rows the
+  // last warp's second half shadows its partner: same loads and arithmetic, no stores.
+  const int n_pairs = (units + 1) / 2;
+  const int64_t wid = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (wid >= (int64_t)n_pairs * parts) return;                   // whole warps leave together
+  const int u_raw = 2 * (int)(wid % n_pairs) + (lane >> 4);
+  const bool active = u_raw < units;
+  const int u = active ? u_raw : units - 1;
+  const int part = (int)(wid / n_pairs);
+  // this half warp's stretch of consecutive groups: the head row's groups cut into `parts` near-equal pieces
+  const int g_begin = (int)((int64_t)part * n_groups / parts), g_end = (int)((int64_t)(part + 1) * n_groups / parts);
   const int which = u < a.H ? 0 : (u < a.H + a.Hkv ? 1 : 2);
   const int head = which == 0 ? u : (which == 1 ? u - a.H : u - a.H - a.Hkv);
   const int heads = which == 0 ? a.H : a.Hkv;
@@ -370,14 +416,15 @@ qkv_prep_direct_kernel(const PrepArgs a, const int vec_weights) {
   const bool normalize = which != 2;
   const float inv_dk = 1.0f / (float)dk;
   T* dst = (T*)(which == 0 ? a.q_out : (which == 1 ? a.k_out : a.v_out)) + head * dk + c;
-  T* cache = (which == 0 || a.k_cache == nullptr) ? nullptr : (T*)(which == 1 ? a.k_cache : a.v_cache) + head * dk + c;
+  T* cache = (which == 0 || a.k_cache == nullptr || !active) ? nullptr : (T*)(which == 1 ? a.k_cache : a.v_cache) + head * dk + c;
   const int64_t dst_row = (int64_t)heads * dk, cache_row = (int64_t)a.Hkv * dk;
-  T* state = (T*)a.state[which];
+  T* state = active ? (T*)a.state[which] : nullptr;
   const T* init = (const T*)a.init[which];
   const int64_t state_ss = a.state_ss[which];
 
-  float wt[8][K];
+  float2 wt2[4][K];                                               // the taps of channel pairs (2j, 2j+1)
   {
+    float wt[8][K];
     const T* w = (const T*)a.w[which] + (int64_t)ch * K;
     if (vec_weights) {
       union { uint4 u4[K]; T e[8 * K]; } wv;
@@ -393,64 +440,89 @@ qkv_prep_direct_kernel(const PrepArgs a, const int vec_weights) {
 #pragma unroll
         for (int kk = 0; kk < K; ++kk) wt[j][kk] = to_f32(w[j * K + kk]);
     }
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int kk = 0; kk < K; ++kk) wt2[j][kk] = make_float2(wt[2 * j][kk], wt[2 * j + 1][kk]);
   }
-  if (!hw_on) return;
-  const uint32_t half_mask = 0xffffu << (16 * (lane >> 4));
-  // normalise one row held as eight fp32 values (q and k; v passes through)
+  // normalise one row held as eight fp32 values.  v passes through the same instructions with a scale of one:
+  // x * 1 and the rounding of a value that came from T leave it as it was, and the warp stays converged.
   auto norm_row = [&](float (&x)[8]) {
-    if (normalize) {
-      float ss = 0.f;
+    float ss = 0.f;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) ss = fmaf(x[j], x[j], ss);
+    for (int j = 0; j < 8; ++j) ss = fmaf(x[j], x[j], ss);
 #pragma unroll
-      for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(half_mask, ss, o, 16);
-      const float rs = rsqrtf(ss * inv_dk + a.eps);
+    for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o, 16);
+    const float rs = normalize ? rsqrtf(ss * inv_dk + a.eps) : 1.0f;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) x[j] *= rs;
-      round8<T>(x);                                              // the eager op rounds to T here
-    }
+    for (int j = 0; j < 8; ++j) x[j] *= rs;
+    round8<T>(x);                                                // the eager op rounds to T here
   };
 
   // The half warp walks kDirGroups consecutive groups of kDirTok tokens.  After a group that lay inside one sequence
   // the last K-1 normalised rows are still in registers and serve as the next group's left context, so only the
   // first such group of a stretch pays for its halo rows.
-  float prevw[K - 1][8];                                          // the K-1 conv inputs before the next row, oldest first
-  bool have_prev = false;
-#pragma unroll 1
-  for (int gi = 0; gi < kDirGroups; ++gi) {
-  const int t0 = run * (kDirTok * kDirGroups) + gi * kDirTok;
-  if (t0 >= a.total) break;
-  const int nt = min(kDirTok, a.total - t0);
-  const int sa = a.seq_start[t0], ea = a.seq_end[t0 + nt - 1];
-  const bool plain = nt == kDirTok && sa == a.seq_start[t0 + nt - 1] && ea > t0 + nt && sa <= t0 - (K - 1);
-  if (plain) {
-    uint4 raw[kDirTok];
+  auto norm_row2 = [&](float2 (&x)[4]) {                          // norm_row on channel pairs, same summation order
+    float ss = 0.f;
 #pragma unroll
-    for (int rl = 0; rl < kDirTok; ++rl) raw[rl] = *reinterpret_cast<const uint4*>(src + (int64_t)(t0 + rl) * row_st);
+    for (int j = 0; j < 4; ++j) ss = fmaf(x[j].y, x[j].y, fmaf(x[j].x, x[j].x, ss));
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o, 16);
+    const float rs = normalize ? rsqrtf(ss * inv_dk + a.eps) : 1.0f;
+    const float2 rs2 = make_float2(rs, rs);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) x[j] = __fmul2_rn(x[j], rs2);
+    round8<T>(x);
+  };
+  float2 prevw[K - 1][4];                                         // the K-1 conv inputs before the next row, oldest first
+  bool have_prev = false;
+  // The rows of the next group travel to a lane-private slot of shared memory while this group is worked on
+  // (asynchronous 16-byte copies: in flight without holding registers).  A lane reads back only what it copied
+  // itself, so waiting for its own copy group is all the synchronisation there is.
+  __shared__ uint4 s_next[2][kDirTok][128];
+  auto request_group = [&](int g) {
+    const int tn = g * kDirTok;
+    if (g < g_end) {
+#pragma unroll
+      for (int rl = 0; rl < kDirTok; ++rl)
+        if (tn + rl < a.total)
+          mma::cp_async16(mma::smem_u32(&s_next[g & 1][rl][threadIdx.x]), src + (int64_t)(tn + rl) * row_st, true);
+    }
+    mma::cp_async_commit();
+  };
+  request_group(g_begin);
+#pragma unroll 1
+  for (int gi = g_begin; gi < g_end; ++gi) {
+  const int t0 = gi * kDirTok;
+  request_group(gi + 1);
+  const int nt = min(kDirTok, a.total - t0);
+  const int sa = a.seq_start[t0], sl = a.seq_start[t0 + nt - 1], ea = a.seq_end[t0 + nt - 1];
+  const bool plain = nt == kDirTok && sa == sl && ea > t0 + nt && sa <= t0 - (K - 1);
+  if (plain) {
     if (!have_prev) {
 #pragma unroll
       for (int kk = 0; kk < K - 1; ++kk) {
-        load8<T>(src + (int64_t)(t0 - (K - 1) + kk) * row_st, prevw[kk]);
-        norm_row(prevw[kk]);
+        unpack8<T>(*reinterpret_cast<const uint4*>(src + (int64_t)(t0 - (K - 1) + kk) * row_st), prevw[kk]);
+        norm_row2(prevw[kk]);
       }
     }
+    mma::cp_async_wait<1>();                                       // this group's rows have landed (the next may be in flight)
 #pragma unroll
     for (int rl = 0; rl < kDirTok; ++rl) {
-      float x[8];
-      unpack8<T>(raw[rl], x);
-      norm_row(x);
-      float y[8];
+      float2 x[4], y[4];
+      unpack8<T>(s_next[gi & 1][rl][threadIdx.x], x);
+      norm_row2(x);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        float acc = 0.f;
+      for (int j = 0; j < 4; ++j) {
+        float2 acc = make_float2(0.f, 0.f);
 #pragma unroll
-        for (int kk = 0; kk < K - 1; ++kk) acc = fmaf(prevw[kk][j], wt[j][kk], acc);
-        y[j] = fmaf(x[j], wt[j][K - 1], acc);
+        for (int kk = 0; kk < K - 1; ++kk) acc = __ffma2_rn(prevw[kk][j], wt2[j][kk], acc);
+        y[j] = __ffma2_rn(x[j], wt2[j][K - 1], acc);
       }
       round8<T>(y);                                              // the conv rounded as eager does, then x + conv(x)
 #pragma unroll
-      for (int j = 0; j < 8; ++j) y[j] += x[j];
-      store8<T>(dst + (int64_t)(t0 + rl) * dst_row, y);
+      for (int j = 0; j < 4; ++j) y[j] = __fadd2_rn(y[j], x[j]);
+      if (active) store8<T>(dst + (int64_t)(t0 + rl) * dst_row, y);
       if (cache != nullptr) {
         const long long cs = a.slot_mapping[t0 + rl];
         if (cs >= 0) store8<T>(cache + cs * cache_row, y);
@@ -458,9 +530,9 @@ qkv_prep_direct_kernel(const PrepArgs a, const int vec_weights) {
 #pragma unroll
       for (int kk = 0; kk + 1 < K - 1; ++kk)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) prevw[kk][j] = prevw[kk + 1][j];
+        for (int j = 0; j < 4; ++j) prevw[kk][j] = prevw[kk + 1][j];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) prevw[K - 2][j] = x[j];
+      for (int j = 0; j < 4; ++j) prevw[K - 2][j] = x[j];
     }
     have_prev = true;
     continue;
@@ -489,7 +561,10 @@ qkv_prep_direct_kernel(const PrepArgs a, const int vec_weights) {
           x[j] = from_state ? to_f32(init[slot * state_ss + (int64_t)(ch + j) * (K - 1) + (K - 1) - (s0 - srow)]) : 0.f;
       }
 #pragma unroll
-      for (int j = 0; j < 8; ++j) { acc[j] = fmaf(x[j], wt[j][kk], acc[j]); keep[kk][j] = x[j]; }
+      for (int j = 0; j < 8; ++j) {
+        acc[j] = fmaf(x[j], (j & 1) ? wt2[j >> 1][kk].y : wt2[j >> 1][kk].x, acc[j]);
+        keep[kk][j] = x[j];
+      }
       if (kk == K - 1) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) cur[j] = x[j];
@@ -499,7 +574,7 @@ qkv_prep_direct_kernel(const PrepArgs a, const int vec_weights) {
     round8<T>(acc);
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] += cur[j];
-    store8<T>(dst + (int64_t)t * dst_row, acc);
+    if (active) store8<T>(dst + (int64_t)t * dst_row, acc);
     if (cache != nullptr) {
       const long long cs = a.slot_mapping[t];
       if (cs >= 0) store8<T>(cache + cs * cache_row, acc);
@@ -513,20 +588,25 @@ qkv_prep_direct_kernel(const PrepArgs a, const int vec_weights) {
     }
   }
   }                                                              // next group of the half warp
+  mma::cp_async_wait<0>();
 }
 
 template <typename T>
 int launch_prep(const PrepArgs& a, cudaStream_t st) {
   if constexpr (sizeof(T) == 2) {
     if (a.dk == 128) {                                           // the direct form: no shared-memory tile
-      const int64_t half_warps = (int64_t)(a.H + 2 * a.Hkv) * ((a.total + kDirTok * kDirGroups - 1) / (kDirTok * kDirGroups));
-      const dim3 dgrid((unsigned)((half_warps * 16 + 127) / 128)), dblock(128);
+      // every head row's groups are cut into stretches of about kDirGroups consecutive groups, one per half warp
+      const int units = a.H + 2 * a.Hkv;
+      const int n_groups = (a.total + kDirTok - 1) / kDirTok;
+      const int parts = std::max(1, (n_groups + kDirGroups - 1) / kDirGroups);
+      const int64_t warps = (int64_t)((units + 1) / 2) * parts;  // two head rows per warp
+      const dim3 dgrid((unsigned)((warps + 3) / 4)), dblock(128);
       const int vec_w = ((reinterpret_cast<uintptr_t>(a.w[0]) | reinterpret_cast<uintptr_t>(a.w[1]) |
                           reinterpret_cast<uintptr_t>(a.w[2])) & 15) == 0 ? 1 : 0;
       switch (a.K) {
-        case 2: qkv_prep_direct_kernel<T, 2><<<dgrid, dblock, 0, st>>>(a, vec_w); break;
-        case 3: qkv_prep_direct_kernel<T, 3><<<dgrid, dblock, 0, st>>>(a, vec_w); break;
-        default: qkv_prep_direct_kernel<T, 4><<<dgrid, dblock, 0, st>>>(a, vec_w); break;
+        case 2: qkv_prep_direct_kernel<T, 2><<<dgrid, dblock, 0, st>>>(a, vec_w, parts); break;
+        case 3: qkv_prep_direct_kernel<T, 3><<<dgrid, dblock, 0, st>>>(a, vec_w, parts); break;
+        default: qkv_prep_direct_kernel<T, 4><<<dgrid, dblock, 0, st>>>(a, vec_w, parts); break;
       }
       return launch_status("qkv_prep_prefill");
     }

@@ -155,10 +155,21 @@ def _prep_case(dtype, lens, H=4, Hkv=2, dk=128, K=4, seed=0, rows=6):
                                                 (torch.float32, 1e-4, 128, [2, 37, 1, 64, 29])])
 @pytest.mark.parametrize("continued", [False, True])
 def test_qkv_prep_prefill_matches_the_op_by_op_oracle(dtype, tol, dk, lens, continued):
+    _check_prep_against_oracle(dtype, tol, dk, lens, continued)
+
+
+@pytest.mark.parametrize("H,Hkv", [(3, 1), (5, 2), (1, 1)])
+def test_qkv_prep_prefill_with_an_odd_number_of_head_rows(H, Hkv):
+    """The direct form pairs head rows two to a warp; with H + 2 Hkv odd the last pair is half empty and
+    with H odd a q head shares its warp with a k head.  Same check as above on those shapes."""
+    _check_prep_against_oracle(torch.bfloat16, 2e-2, 128, [300, 5, 1, 260, 70], True, H=H, Hkv=Hkv)
+
+
+def _check_prep_against_oracle(dtype, tol, dk, lens, continued, H=4, Hkv=2):
     """Ragged packed sequences (shorter than the kernel, crossing the 32-token tile, one without a
     state slot): the fused launch == rms_norm + x + conv(x) + state write + store_kvcache run op by
     op on the CPU; state rows and cache rows that nothing addresses stay as they were."""
-    q_gate, k, v, w, states, s0, e0, sl, k_cache, v_cache, sm = _prep_case(dtype, lens, dk=dk, seed=3)
+    q_gate, k, v, w, states, s0, e0, sl, k_cache, v_cache, sm = _prep_case(dtype, lens, H=H, Hkv=Hkv, dk=dk, seed=3)
     init = [s.clone() for s in states] if continued else None
     ref_states = [s.clone() for s in states]
     ref_kc, ref_vc = k_cache.clone(), v_cache.clone()
