@@ -211,6 +211,8 @@ polar_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
   volatile int* abort_flag = &s_abort;
 
   if (warp < 4) {
+  // Register hand-over: 88 x 128 + 208 x 256 = 168 x 384, the pool this CTA is launched with (ptxas -v: 168 registers
+  // under __launch_bounds__(384, 1)).  The sum must not exceed that pool, or the last setmaxnreg.inc never returns.
   asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
   if (warp == 0) {
     // =============================== TMA producer ================================================

@@ -124,3 +124,21 @@ def test_compat_shim_resolves_the_reference_import_paths():
         for k in [m for m in sys.modules if m.split(".")[0] in ("kernel", "fla")]:
             del sys.modules[k]
         sys.modules.update(saved_mods)
+
+
+def test_prefill_kernel_register_hand_over_fits_the_launch_pool():
+    """The tcgen05 prefill kernel re-divides its registers between warpgroups with setmaxnreg.  The counts it
+    asks for must add up to no more than the CTA is launched with (registers per thread as compiled x threads),
+    or the last warpgroup's request never returns.  Checked against the compiler's own report of the build."""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    log = os.path.join(root, "atma_b200", "build", "polar_prefill_sm100.o.log")
+    src = open(os.path.join(root, "atma_b200", "csrc", "polar_prefill_sm100.cu")).read()
+    if not os.path.exists(log):
+        pytest.skip("no compiler report (the library was not built in this tree)")
+    used = [int(x) for x in re.findall(r"Used (\d+) registers", open(log).read())]
+    threads = int(re.search(r"constexpr int kThreads = (\d+);", src).group(1))
+    dec = int(re.search(r"setmaxnreg\.dec\.sync\.aligned\.u32 (\d+);", src).group(1))
+    inc = int(re.search(r"setmaxnreg\.inc\.sync\.aligned\.u32 (\d+);", src).group(1))
+    assert used and threads % 128 == 0
+    asked = dec * 128 + inc * (threads - 128)                     # the first warpgroup shrinks, the others grow
+    assert all(asked <= n * threads for n in used), (asked, used, threads)
