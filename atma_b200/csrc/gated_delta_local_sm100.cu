@@ -39,7 +39,7 @@ namespace {
 
 __device__ int g_local_status = 0;
 
-constexpr int kThreads = 320, kWorkers = 256;
+constexpr int kThreads = 320;                     // TMA warp, MMA warp, eight worker warps
 constexpr int kTile = 2 * kD * 128;               // a [128][128] 16-bit tile = two 64-column boxes of 16 KiB
 constexpr int kLd = 68;                           // fp32 row stride of the A and T matrices
 constexpr int kOffK = 0, kOffQ = kTile, kOffV = 2 * kTile, kOffTu = 3 * kTile, kOffAf = 4 * kTile,
@@ -286,7 +286,6 @@ scan_local_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
       const Meta m = m_next;
       const bool valid = pr < m.rows[ci];
       const bool have = m.rec[ci] >= 0;
-      uint8_t* rec = p.recs + (have ? m.rec[ci] : 0) * (int64_t)kRecBytes;
 
       worker_sync();                                     // every warp is done with the previous tile's arrays
       // ---- decay prefix and beta: one row per thread of the first column half ---------------------

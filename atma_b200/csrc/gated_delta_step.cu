@@ -169,7 +169,6 @@ gated_delta_step_wide_kernel(const StepWideArgs a) {
   __shared__ float s_q[D], s_k[D];
   __shared__ __align__(16) float s_red[NW][D];
   __shared__ float s_part[2][NW];
-  __shared__ float s_r[D];
 
   const int64_t slot = a.slots[b];
   if (slot < 0) {                                       // padded batch row: no state, defined output
