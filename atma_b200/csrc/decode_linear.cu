@@ -158,11 +158,7 @@ extern "C" int atma_decode_linear(const void* x, int64_t x_row_stride, const voi
   a.B = B; a.N = N; a.K = K;
   a.units = (gated ? N / 2 : N) / 16;
   // K splits per unit: as many as give every split whole 32-k blocks and keep the grid within one wave
-  static int sm_count[64] = {0};
-  int dev = 0;
-  ATMA_CUDA_OK(cudaGetDevice(&dev));
-  if (dev < 64 && sm_count[dev] == 0) ATMA_CUDA_OK(cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev));
-  const int sms = (dev < 64 && sm_count[dev] > 0) ? sm_count[dev] : 148;
+  const int sms = sm_count_of_current_device();
   int ks = kWarps;
   while (ks > 1 && (K % (32 * ks) != 0 || (int64_t)a.units * ks / kWarps > sms)) ks >>= 1;
   a.ks = ks;

@@ -578,9 +578,7 @@ int gated_delta_local_sm100(const void* q, const void* k, const void* v, int is_
   p.n_pairs = (NC + 1) / 2;
   p.n_tiles = (int64_t)(var.cu_seqlens != nullptr ? 1 : B) * p.n_pairs * H;
   p.var = var;
-  int dev = 0, sms = 148;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int sms = sm_count_of_current_device();
   const int grid = (int)(p.n_tiles < sms ? p.n_tiles : sms);
   if (is_bf16) {
     ATMA_CUDA_OK(cudaFuncSetAttribute(scan_local_sm100_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));

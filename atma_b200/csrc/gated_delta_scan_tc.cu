@@ -104,8 +104,7 @@ seg_compose_kernel(const float* __restrict__ fin1, float* __restrict__ init2, fl
 // machine: the first pass runs 2 recurrences per later segment (transfer matrix and offset), so
 // B * H * 2 * NS CTAs should fit the SM count; a segment should still be at least 32 chunks long.
 int gated_delta_scan_segments(int B, int H, int NC, int requested) {
-  int sms = 148, dev = 0;
-  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int sms = sm_count_of_current_device();
   int ns = requested > 0 ? requested : sms / (2 * B * H);
   if (ns > 16) ns = 16;
   if (ns > NC / 32) ns = NC / 32;
