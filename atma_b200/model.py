@@ -38,7 +38,7 @@ from .polar import polar_attention_fwd
 from .inference_ops import (add_rms_norm, decode_linear, decode_linear_supported, lfm2_conv_decode_step, lfm2_conv_packed,
                             qkv_prep_decode, rms_sigmoid_gate, softcap_logits, squared_relu_gate)
 from .layer import PackedMaps, global_attention_prefill_packed
-from .polar import polar_attention_decode
+from .polar import DECODE_BESIDE_MAX_ROWS, polar_attention_decode
 
 POLAR_NAMES = ("v_null", "null_base", "null_slope_raw", "len_gain_raw", "mag_beta_raw")
 
@@ -372,15 +372,24 @@ class AtmaModel:
                 mem_gate = z[:, pk["o_mg"]:]
                 # The memory branch shares nothing it writes with the attention branch (its slice of ``act``, its own
                 # state table), so it runs beside the paged attention on a second stream: fork here, join before W_out.
+                # Small batches hand it to the decode call instead, which runs it beside the merge launch: the key-range
+                # launch then has the machine to itself (polar.DECODE_BESIDE_MAX_ROWS).
                 cur = torch.cuda.current_stream(x.device)
-                if dk == 128:
+
+                def memory_step():
+                    return gated_delta_decode_step_fused(q, k, v, state.mem[i], seq_slots,
+                                                         gate_logits=(z[:, pk["o_g"]:pk["o_b"]], z[:, pk["o_b"]:pk["o_mg"]]),
+                                                         gamma_bias=self.gamma_bias, beta_bias=self.beta_bias, gate=mem_gate,
+                                                         out=r_out)
+                beside = dk == 128 and local_lens is None and B <= DECODE_BESIDE_MAX_ROWS
+                forked = dk == 128 and not beside
+                if forked:
                     side = self._decode_side_stream()
                     side.wait_stream(cur)
                     with torch.cuda.stream(side):
-                        gated_delta_decode_step_fused(q, k, v, state.mem[i], seq_slots,
-                                                      gate_logits=(z[:, pk["o_g"]:pk["o_b"]], z[:, pk["o_b"]:pk["o_mg"]]),
-                                                      gamma_bias=self.gamma_bias, beta_bias=self.beta_bias, gate=mem_gate,
-                                                      out=r_out)
+                        memory_step()
+                elif beside:
+                    pass                                                         # launched by the decode call below
                 else:                                                            # other head sizes: the separate kernels
                     G = H // Hkv
                     gamma = torch.sigmoid(z[:, pk["o_g"]:pk["o_b"]].float() + self.gamma_bias)
@@ -391,7 +400,7 @@ class AtmaModel:
                 if local_lens is None:
                     polar_attention_decode(q, state.k_cache[i], state.v_cache[i], block_tables, context_lens, window=self.window,
                                            gate=q_gate[..., dk:], out=(act[:, :H * dk].view(B, H, dk), act[:, H * dk:H * dk + H]),
-                                           **pk["polar"])
+                                           beside=memory_step if beside else None, **pk["polar"])
                 else:
                     from .context_parallel import cp_polar_decode
                     if self.window is not None:
@@ -400,7 +409,7 @@ class AtmaModel:
                                              pk["polar"], group=group)
                     act[:, :H * dk] = sigmoid_gate_mul(c, q_gate[..., dk:]).view(B, H * dk)
                     act[:, H * dk:H * dk + H] = mag
-                if dk == 128:
+                if forked:
                     cur.wait_stream(side)                                        # join the memory branch
                 mix = self._linear(act, pk["w_out"], pk["b_out"])                          # W_o, W_mu and mem.proj in one product
             else:

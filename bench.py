@@ -185,9 +185,16 @@ def bench_decode(ab, device, steps, warmup, peaks):
 
     side = torch.cuda.Stream(device=device)
 
+    from atma_b200.polar import DECODE_BESIDE_MAX_ROWS
+
     def step():
-        # the memory branch reads and writes nothing the attention branch touches: it runs beside it (fork / join),
-        # as the two branches of the reference's decode layer may (inference/models/atma.py:572-590)
+        # the memory branch reads and writes nothing the attention branch touches: it runs beside it, as the two
+        # branches of the reference's decode layer may (inference/models/atma.py:572-590) - for small batches beside
+        # the merge launch (the decode call's own hook), else beside the whole call (fork / join)
+        if DEC_B <= DECODE_BESIDE_MAX_ROWS:
+            return ab.polar_attention_decode(
+                q, k_cache, v_cache, bt, cl, append=(kn, vn, slot_map),
+                beside=lambda: ab.gated_delta_decode_step_fused(q, kn, vn, state, slots, gamma=gamma, beta=beta), **params)
         cur = torch.cuda.current_stream(device)
         side.wait_stream(cur)
         with torch.cuda.stream(side):

@@ -221,3 +221,40 @@ def test_decode_that_stores_the_new_token_itself_equals_scatter_then_decode(dtyp
     c2, m2 = atma_b200.polar_attention_decode(q, kc2, vc2, bt, cl, append=(kn, vn, sm), **P)
     assert torch.equal(kc1, kc2) and torch.equal(vc1, vc2)
     assert torch.equal(c1, c2) and torch.equal(m1, m2)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_side_work_runs_between_the_key_range_and_merge_launches(dtype):
+    """``beside=``: the callable's work goes to a side stream after the key-range kernel and is joined before the
+    call returns; c, mag equal the plain call (also with ``append`` and ``gate``), the callable's result comes back,
+    and what it wrote is complete once the current stream is synchronised."""
+    g = torch.Generator().manual_seed(11)
+    ctx = [300, 2, 129, 1000]
+    B, H, Hkv, dk, bs = len(ctx), 8, 2, 128, 64
+    per = (max(ctx) + bs - 1) // bs
+    nblk = B * per + 2
+    kc = torch.randn(nblk, bs, Hkv, dk, generator=g).to(dtype).cuda()
+    vc = torch.randn(nblk, bs, Hkv, dk, generator=g).to(dtype).cuda()
+    bt = torch.randperm(nblk, generator=g)[:B * per].view(B, per).int().cuda()
+    cl = torch.tensor(ctx, dtype=torch.int32).cuda()
+    q = torch.randn(B, H, dk, generator=g).to(dtype).cuda()
+    kn = torch.randn(B, Hkv, dk, generator=g).to(dtype).cuda()
+    vn = torch.randn(B, Hkv, dk, generator=g).to(dtype).cuda()
+    gate = torch.randn(B, H, dk, generator=g).to(dtype).cuda()
+    last = cl.long() - 1
+    sm = (bt.long()[torch.arange(B), last // bs] * bs + last % bs).int()
+    _, P = polar_params(H, dk, 4)
+    state = (torch.randn(B, H, dk, dk, generator=g) * 0.1).cuda()
+    gamma, beta = torch.rand(B, H, generator=g).cuda(), torch.rand(B, H, generator=g).cuda()
+    slots = torch.arange(B).cuda()
+    kc1, vc1, st1 = kc.clone(), vc.clone(), state.clone()
+    c1, m1 = atma_b200.polar_attention_decode(q, kc1, vc1, bt, cl, append=(kn, vn, sm), gate=gate, **P)
+    r1 = atma_b200.gated_delta_decode_step_fused(q, kn, vn, st1, slots, gamma=gamma, beta=beta)
+    kc2, vc2, st2 = kc.clone(), vc.clone(), state.clone()
+    c2, m2, r2 = atma_b200.polar_attention_decode(
+        q, kc2, vc2, bt, cl, append=(kn, vn, sm), gate=gate,
+        beside=lambda: atma_b200.gated_delta_decode_step_fused(q, kn, vn, st2, slots, gamma=gamma, beta=beta), **P)
+    torch.cuda.current_stream().synchronize()
+    assert torch.equal(c1, c2) and torch.equal(m1, m2) and torch.equal(kc1, kc2) and torch.equal(vc1, vc2)
+    assert torch.equal(r1, r2) and torch.equal(st1, st2)
+    assert atma_b200.device_status() == 0
