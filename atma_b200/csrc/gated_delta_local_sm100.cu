@@ -184,15 +184,15 @@ scan_local_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
         for (int ci = 0; ci < 2; ++ci)
 #pragma unroll
           for (int cb = 0; cb < 2; ++cb) {
-            tma_load_4d(Ks + cb * 16384 + ci * 8192, &tmap_k, &bar.kq_full, cb * 64, m.hk, (int)m.t0[ci], 0);
-            tma_load_4d(Qs + cb * 16384 + ci * 8192, &tmap_q, &bar.kq_full, cb * 64, m.h, (int)m.t0[ci], 0);
+            tma_load_4d(Ks + cb * 16384 + ci * 8192, &tmap_k, &bar.kq_full, cb * 64, m.hk, (int)(ci ? m.t0[1] : m.t0[0]), 0);
+            tma_load_4d(Qs + cb * 16384 + ci * 8192, &tmap_q, &bar.kq_full, cb * 64, m.h, (int)(ci ? m.t0[1] : m.t0[0]), 0);
           }
         mbar_arrive_expect_tx(&bar.v_full, kTile);
 #pragma unroll
         for (int ci = 0; ci < 2; ++ci)
 #pragma unroll
           for (int cb = 0; cb < 2; ++cb)
-            tma_load_4d(Vs + cb * 16384 + ci * 8192, &tmap_v, &bar.v_full, cb * 64, m.hk, (int)m.t0[ci], 0);
+            tma_load_4d(Vs + cb * 16384 + ci * 8192, &tmap_v, &bar.v_full, cb * 64, m.hk, (int)(ci ? m.t0[1] : m.t0[0]), 0);
         // the shared-memory tiles stay busy until this tile's last products; meanwhile bring the next tile's
         // inputs into L2, so that its loads do not wait for DRAM
         if (tile + gridDim.x < p.n_tiles) {
@@ -274,8 +274,8 @@ scan_local_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
       if (tile < p.n_tiles) {
         tile_meta(p, tile, m_next);
         if (half == 0) {
-          const bool v = pr < m_next.rows[ci];
-          const int64_t gi = (m_next.t0[ci] + pr) * p.H + m_next.h;
+          const bool v = pr < (ci ? m_next.rows[1] : m_next.rows[0]);
+          const int64_t gi = ((ci ? m_next.t0[1] : m_next.t0[0]) + pr) * p.H + m_next.h;
           g_pre = v ? p.g[gi] : 0.f;
           b_pre = v ? p.beta[gi] : 0.f;
         }
@@ -284,8 +284,8 @@ scan_local_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
     prefetch_tile(blockIdx.x);
     for (int64_t tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x, ++it) {
       const Meta m = m_next;
-      const bool valid = pr < m.rows[ci];
-      const bool have = m.rec[ci] >= 0;
+      const bool valid = pr < (ci ? m.rows[1] : m.rows[0]);
+      const bool have = (ci ? m.rec[1] : m.rec[0]) >= 0;
 
       worker_sync();                                     // every warp is done with the previous tile's arrays
       // ---- decay prefix and beta: one row per thread of the first column half ---------------------
@@ -328,7 +328,7 @@ scan_local_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
         if (quad & 1) run += s_wsum[quad - 1];           // second warp of the chunk
         s_lg[row] = run;
         s_kinv[row] = kinv_p;
-        if (pr == kC - 1 && have) p.gcs[m.rec[ci]] = __expf(run);
+        if (pr == kC - 1 && have) p.gcs[(ci ? m.rec[1] : m.rec[0])] = __expf(run);
       }
       worker_sync();
       const float lg_p = s_lg[row], bt_p = s_bt[row], lg_C = s_lg[64 * ci + 63];
@@ -344,8 +344,8 @@ scan_local_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int r = (wtid >> 4) + 16 * i, ch = wtid & 15, rc = r >> 6;
-        if (m.rec[rc] >= 0) {
-          uint8_t* rrec = p.recs + m.rec[rc] * (int64_t)kRecBytes;
+        if ((rc ? m.rec[1] : m.rec[0]) >= 0) {
+          uint8_t* rrec = p.recs + (rc ? m.rec[1] : m.rec[0]) * (int64_t)kRecBytes;
           const float sq = s_qsc[r], sk = s_ksc[r];
           const uint4 uk = *reinterpret_cast<const uint4*>(Ks + (ch >> 3) * 16384 + box_off(r, ch & 7));
           const uint4 uq = *reinterpret_cast<const uint4*>(Qs + (ch >> 3) * 16384 + box_off(r, ch & 7));
@@ -405,8 +405,8 @@ scan_local_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
 #pragma unroll
       for (int i = 0; i < 4; ++i) {                      // 16 KiB out, 512 contiguous bytes per warp instruction
         const int idx = wtid + 256 * i, r = idx >> 3, ch = idx & 7, rc = r >> 6;
-        if (m.rec[rc] >= 0)
-          *reinterpret_cast<uint4*>(p.recs + m.rec[rc] * (int64_t)kRecBytes + kRecRq + (r & 63) * 128 + ch * 16) =
+        if ((rc ? m.rec[1] : m.rec[0]) >= 0)
+          *reinterpret_cast<uint4*>(p.recs + (rc ? m.rec[1] : m.rec[0]) * (int64_t)kRecBytes + kRecRq + (r & 63) * 128 + ch * 16) =
               *reinterpret_cast<const uint4*>(Tus + box_off(r, ch));
       }
 
@@ -531,15 +531,15 @@ scan_local_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
 #pragma unroll
         for (int i = 0; i < 8; ++i) {                    // -W: 32 KiB out
           const int idx = wtid + 256 * i, r2 = idx >> 4, ch = idx & 15, rc = r2 >> 6;
-          if (m.rec[rc] >= 0)
-            *reinterpret_cast<uint4*>(p.recs + m.rec[rc] * (int64_t)kRecBytes + kRecW + (r2 & 63) * 256 + ch * 16) =
+          if ((rc ? m.rec[1] : m.rec[0]) >= 0)
+            *reinterpret_cast<uint4*>(p.recs + (rc ? m.rec[1] : m.rec[0]) * (int64_t)kRecBytes + kRecW + (r2 & 63) * 256 + ch * 16) =
                 *reinterpret_cast<const uint4*>(stage_w + r2 * 256 + ((ch ^ (r2 & 7)) << 4));
         }
 #pragma unroll
         for (int i = 0; i < 8; ++i) {                    // U0^T of both chunks: 2 x 16 KiB out
           const int idx = wtid + 256 * i, rc = idx >> 10, v = (idx >> 3) & 127, ch = idx & 7;
-          if (m.rec[rc] >= 0)
-            *reinterpret_cast<uint4*>(p.recs + m.rec[rc] * (int64_t)kRecBytes + kRecU0 + v * 128 + ch * 16) =
+          if ((rc ? m.rec[1] : m.rec[0]) >= 0)
+            *reinterpret_cast<uint4*>(p.recs + (rc ? m.rec[1] : m.rec[0]) * (int64_t)kRecBytes + kRecU0 + v * 128 + ch * 16) =
                 *reinterpret_cast<const uint4*>(stage_u + rc * 16384 + box_off(v, ch));
         }
       }
